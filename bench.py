@@ -1,0 +1,317 @@
+#!/usr/bin/env python
+"""Decode benchmark for the fused quantized decode path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+Workload (default): Qwen2.5-0.5B architecture, random-init, Q8_0 (block 32, fp16 scales), fp16 KV,
+batch 1: a 32-token prompt fed one position at a time, then K greedy decode steps.  A "step" is one
+decode token.  Prints ONE JSON line (see README / DESIGN.md for the fields).
+
+  value     tokens/s with everything resident in HBM: K greedy steps enqueued back to back
+            (argmax fed back on the device), timed with CUDA events on the engine's stream.
+  e2e       tokens/s through the reference-facing call PartialStep(hiddenIn, pos, 0, L, nil, logitsOut)
+            with pinned HOST buffers: each step uploads the hidden vector and downloads the logits.
+  roofline  the decode step as a whole (it is one graph launch): algorithmic bytes per token
+            (quantized weights + fp16 KV read at the mean context) / step time, against the measured
+            HBM copy peak in MEASURED_PEAKS.json.
+
+With N > 1 (launched under torchrun, one rank per GPU) every rank decodes its own independent
+sequence on its own replica of the weights: no data-path collective, weak scaling.
+
+--impl reference times the CPU port of the reference's pure-Go engine (oracle/oracle.c,
+oracle_cpu_engine_step_token) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from mongoose_b200 import configs as mc  # noqa: E402
+from mongoose_b200 import synthetic  # noqa: E402
+
+PROMPT_LEN = 32
+WORKLOADS = {
+    "qwen2.5-0.5b-q8_0-b1": mc.QWEN25_05B,
+    "qwen2.5-0.5b-q4_0-b1": mc.QWEN25_05B_Q4,
+    "tiny-q8_0-b1": mc.TINY,
+}
+FMT_NAME = {mc.FMT_Q8_0: "q8_0", mc.FMT_Q4_0: "q4_0", mc.FMT_F16: "f16"}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="qwen2.5-0.5b-q8_0-b1", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-steps", type=int, default=0, help="steps of the CPU baseline sample (0 = auto)")
+    return ap.parse_args()
+
+
+def algorithmic_bytes_per_token(cfg, first_pos: int, steps: int) -> float:
+    """Quantized weight bytes + fp16 KV bytes read at the mean context of the timed window."""
+    mean_ctx = first_pos + 1 + (steps - 1) / 2.0      # positions attended to, averaged over the window
+    return mc.weight_bytes_per_token(cfg) + mc.kv_bytes_per_position(cfg) * mean_ctx
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clocks and throttle reasons during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------
+# CPU baseline (the only place this file touches oracle/)
+# ---------------------------------------------------------------------------
+def cpu_baseline_run(cfg, max_steps: int, nthreads: int, budget_s: float = 25.0, seed: int = 0):
+    """Times decode tokens of the CPU-engine port on a freshly generated model: one probe token, then
+    as many tokens as fit in about `budget_s` seconds (at most max_steps).
+    Returns (tok_per_s, seconds, threads, steps)."""
+    from oracle import oracle as O
+    om = O.OracleModel(cfg)
+    for idx, kind, rows, cols, fmt in synthetic.model_slots(cfg):
+        if kind == "norm":
+            om.set_weight(idx, synthetic.norm_vector(seed, idx, cols), 0)
+        else:
+            om.set_weight(idx, O.quantize(fmt, synthetic.tensor_f32(seed, idx, rows, cols)), fmt)
+    prompt = synthetic.prompt_ids(seed, PROMPT_LEN, cfg.vocab)
+    nthreads = max(1, min(nthreads, O.max_threads()))
+    tok = int(prompt[0])
+    om.cpu_engine_step_token(tok, 0, nthreads)          # pages the weights in
+    t0 = time.perf_counter()
+    logits = om.cpu_engine_step_token(tok, 1, nthreads)
+    probe = time.perf_counter() - t0
+    steps = max(1, min(max_steps, cfg.max_seq - 2, int(budget_s / max(probe, 1e-4))))
+    tok = int(np.argmax(logits))
+    t0 = time.perf_counter()
+    for i in range(steps):
+        logits = om.cpu_engine_step_token(tok, 2 + i, nthreads)
+        tok = int(np.argmax(logits))
+    dt = time.perf_counter() - t0
+    om.close()
+    return steps / dt, dt, nthreads, steps
+
+
+def run_reference_arm(args, cfg, rank):
+    """The reference's CPU implementation of the path, timed on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    ncores = os.cpu_count() or 1
+    cfg = cfg.with_(max_seq=max(cfg.max_seq, args.steps + 2))
+    tps, dt, threads, sample = cpu_baseline_run(cfg, args.steps, ncores, budget_s=40.0)
+    line = {
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": tps, "unit": "tok/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / tps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": FMT_NAME[cfg.layer_fmt], "data": "synthetic",
+        "config": {"workload": args.workload, "prompt_len": PROMPT_LEN, "batch": 1},
+        "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
+                         "sample": f"{sample} decode tokens ({dt:.1f} s) after a 2-token prompt, rows split over "
+                                   f"{threads} OpenMP threads (the Go engine itself is single-threaded)"},
+        "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# B200 arm
+# ---------------------------------------------------------------------------
+def run_b200_arm(args, cfg, rank, world, local_rank):
+    import torch
+    from mongoose_b200.fused_infer import CUDAFusedInference
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for this path")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    K, W = args.steps, max(args.warmup, 3)
+    cfg = cfg.with_(max_seq=max(cfg.max_seq, PROMPT_LEN + K))
+    eng = CUDAFusedInference(cfg, device=local_rank)
+    seed = 0                                            # same weights on every replica
+    synthetic.load_engine(eng, cfg, seed=seed)
+    eng.BuildFusedDispatch()
+    prompt = synthetic.prompt_ids(rank, PROMPT_LEN, cfg.vocab)    # each rank decodes its own sequence
+    stream = torch.cuda.ExternalStream(eng.stream, device=local_rank)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def feed_prompt():
+        """The prompt goes through the decode path one position at a time (the reference has no
+        batched prefill); the last prompt step yields the first generated token."""
+        eng.ResetKV()
+        tok = -1
+        for pos, t in enumerate(prompt):
+            tok = eng.StepToken(int(t), pos)
+        eng.SetCursor(tok, PROMPT_LEN)
+        return PROMPT_LEN
+
+    # ---- warm-up: W greedy steps on the same graph, then start over ----
+    feed_prompt()
+    eng.EnqueueGreedy(min(W, cfg.max_seq - PROMPT_LEN))
+    eng.Sync()
+
+    # ---- timed: device-resident greedy decode ----
+    first_pos = feed_prompt()
+    sampler = ClockSampler(local_rank)
+    launches0 = eng.LaunchCount()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    ev0.record(stream)
+    eng.EnqueueGreedy(K)
+    ev1.record(stream)
+    eng.Sync()
+    barrier()
+    clocks = sampler.stop()
+    ms = ev0.elapsed_time(ev1)
+    launches = eng.LaunchCount() - launches0
+    tok_last, pos_last = eng.GetCursor()
+    assert pos_last == first_pos + K, (pos_last, first_pos, K)
+
+    # ---- e2e: PartialStep with pinned host buffers (hidden in, logits out) ----
+    # The token sequence is the one just generated, so no host-side sampling sits in the timed loop;
+    # the caller-side embedding rows (dequantized lm_head rows) are prepared beforehand.
+    gen_tokens = eng.Generate(prompt, K)                # g0 .. g(K-1): the inputs of the K decode steps
+    seq = np.concatenate([prompt, gen_tokens])
+    head_idx = cfg.n_layers * 12 + 1
+    hid = torch.empty((len(seq), cfg.dim), dtype=torch.float32).pin_memory()
+    for i, t in enumerate(seq):
+        hid[i] = torch.from_numpy(eng.DequantRows(head_idx, int(t), 1, cfg.dim)[0])
+    logits_host = torch.empty(cfg.vocab, dtype=torch.float32).pin_memory()
+    eng.ResetKV()
+    for i in range(PROMPT_LEN):
+        eng.PartialStep(hid[i], i, 0, cfg.n_layers, None, logits_host)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(PROMPT_LEN, PROMPT_LEN + K):
+        eng.PartialStep(hid[i], i, 0, cfg.n_layers, None, logits_host)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    e2e_last_tok = int(torch.argmax(logits_host))
+    barrier()
+
+    # max over ranks
+    tms = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms_max, e2e_ms_max = float(tms[0]), float(tms[1])
+
+    if rank == 0:
+        tps = world * K / (ms_max / 1e3)
+        bytes_tok = algorithmic_bytes_per_token(cfg, first_pos, K)
+        peak, peak_src = measured_peak_gbs()
+        achieved = bytes_tok * (K / (ms_max / 1e3)) / 1e9          # per GPU
+        line = {
+            "metric": "decode_tokens_per_s", "value": tps, "unit": "tok/s", "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": FMT_NAME[cfg.layer_fmt], "data": "synthetic",
+            "config": {"workload": args.workload, "prompt_len": PROMPT_LEN, "batch": 1,
+                       "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+                       "l2": "inputs larger than L2 (weights streamed per token: %d MB)" %
+                             (mc.weight_bytes_per_token(cfg) // 2 ** 20),
+                       "timing": "CUDA events on the engine stream, max over ranks"},
+            "e2e": {"value": world * K / (e2e_ms_max / 1e3), "unit": "tok/s",
+                    "h2d_bytes_per_step": cfg.dim * 4 + 8, "d2h_bytes_per_step": cfg.vocab * 4,
+                    "api": "PartialStep(hiddenIn, pos, 0, L, nil, logitsOut) with pinned host buffers",
+                    "last_token_matches_device_loop": bool(e2e_last_tok == tok_last)},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "whole decode step (one CUDA graph of fused kernels)",
+                         "algorithmic_bytes_per_token": bytes_tok, "frac_of_8TBs": achieved / 8000.0},
+            "clocks": clocks,
+            "tokens_tail": [int(x) for x in gen_tokens[-4:]],
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            ctps, cdt, cth, n = cpu_baseline_run(cfg.with_(max_seq=64), args.cpu_steps or 60, 1, budget_s=15.0)
+            line["cpu_baseline"] = {"value": ctps, "unit": "tok/s", "cores": cth, "kind": "port",
+                                    "sample": f"{n} decode tokens of the same model on the single-threaded "
+                                              f"CPU-engine port ({cdt:.1f} s)"}
+        print(json.dumps(line), flush=True)
+    eng.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    cfg = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, cfg, rank)
+        return
+    run_b200_arm(args, cfg, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,205 @@
+// Matvecs on caller-owned RAW quantized blocks (GGUF Q4_0 18-byte blocks,
+// Q8_0 34-byte blocks), the int8-activation (dp4a) family, and the fused
+// per-token dispatch over caller-owned buffers.
+//
+// The Go side declares these entry points (kernels.go:62-67, 206-211;
+// cuda_graph.go:211-234) but the reference ships no source for them; the
+// block layout is the one cuda_q4_0.go:13-17 uploads.  Raw blocks are only
+// 2-byte aligned, so these kernels read them with 16-bit loads; the engine
+// (mg_*) re-packs blocks at upload and does not use this file's kernels.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/mongoose_kernels.h"
+#include "mg_common.cuh"
+
+using namespace mg;
+
+namespace {
+
+struct __align__(8) ActBlock {   // 40 bytes per 32 activations
+    float d;                     // amax / 127
+    float s;                     // d * sum(q)
+    int8_t q[32];
+};
+static_assert(sizeof(ActBlock) == 40, "activation block is 40 bytes");
+
+// ---------------- fp32-activation matvecs on raw blocks ----------------
+// One warp per row; lane handles blocks lane, lane+32, ...
+template <int FMT>
+__global__ void __launch_bounds__(256) raw_block_matvec_kernel(const float* __restrict__ act,
+                                                              const uint8_t* __restrict__ w, float* out, int N,
+                                                              int K) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= N) return;
+    const int nb = K / 32;
+    constexpr int BB = FMT == FMT_Q8_0 ? 34 : 18;
+    const uint8_t* wr = w + (size_t)row * nb * BB;
+    float acc = 0.f;
+    for (int b = lane; b < nb; b += 32) {
+        const unsigned short* p = reinterpret_cast<const unsigned short*>(wr + (size_t)b * BB);
+        const float d = half_bits_to_float(p[0]);
+        const float* x = act + (size_t)b * 32;
+        float s = 0.f;
+        if (FMT == FMT_Q8_0) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const unsigned short v = p[1 + i];
+                s = fmaf(x[2 * i], (float)(int8_t)(v & 0xFF), s);
+                s = fmaf(x[2 * i + 1], (float)(int8_t)(v >> 8), s);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const unsigned short v = p[1 + i];
+                const int b0 = v & 0xFF, b1 = v >> 8;
+                s = fmaf(x[2 * i], (float)((b0 & 0xF) - 8), s);
+                s = fmaf(x[2 * i + 16], (float)((b0 >> 4) - 8), s);
+                s = fmaf(x[2 * i + 1], (float)((b1 & 0xF) - 8), s);
+                s = fmaf(x[2 * i + 17], (float)((b1 >> 4) - 8), s);
+            }
+        }
+        acc = fmaf(d, s, acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[row] = acc;
+}
+
+// ---------------- activation quantizer: one warp per block of 32 ----------------
+__global__ void __launch_bounds__(256) quantize_act_kernel(const float* __restrict__ act, ActBlock* out,
+                                                          int nblocks_total) {
+    const int lane = threadIdx.x & 31;
+    const int blk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (blk >= nblocks_total) return;
+    const float v = act[(size_t)blk * 32 + lane];
+    const float amax = warp_max(fabsf(v));
+    const float d = amax / 127.0f;
+    const int q = amax > 0.f ? __float2int_rn(v / d) : 0;
+    int sum = q;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(MG_FULL_MASK, sum, o);
+    out[blk].q[lane] = (int8_t)q;
+    if (lane == 0) {
+        out[blk].d = d;
+        out[blk].s = d * (float)sum;
+    }
+}
+
+// ---------------- Q4_0 x int8 activations, integer dot products ----------------
+// out[b][row] = sum_blocks d_w * (d_a * sum_j nib_j * qa_j - 8 * s_a)
+__global__ void __launch_bounds__(256) q4_0_dp4a_kernel(const uint8_t* __restrict__ w,
+                                                       const ActBlock* __restrict__ q8, float* out, int N, int K,
+                                                       int B) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= N) return;
+    const int nb = K / 32;
+    const uint8_t* wr = w + (size_t)row * nb * 18;
+    for (int bi = 0; bi < B; bi++) {
+        const ActBlock* qa = q8 + (size_t)bi * nb;
+        float acc = 0.f;
+        for (int b = lane; b < nb; b += 32) {
+            const unsigned short* p = reinterpret_cast<const unsigned short*>(wr + (size_t)b * 18);
+            const float dw = half_bits_to_float(p[0]);
+            const int* aq = reinterpret_cast<const int*>(qa[b].q);
+            int sumi = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t word = (uint32_t)p[1 + 2 * i] | ((uint32_t)p[2 + 2 * i] << 16);
+                const int lo = (int)(word & 0x0f0f0f0fu), hi = (int)((word >> 4) & 0x0f0f0f0fu);
+                sumi = __dp4a(lo, aq[i], sumi);
+                sumi = __dp4a(hi, aq[4 + i], sumi);
+            }
+            acc = fmaf(dw, qa[b].d * (float)sumi - 8.0f * qa[b].s, acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) out[(size_t)bi * N + row] = acc;
+    }
+}
+
+inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace
+
+extern "C" {
+
+void mongoose_q4_0_matvec(const float* act, const void* w_blocks, float* out, int N, int K, cudaStream_t stream) {
+    if (N <= 0 || K < 32) return;
+    raw_block_matvec_kernel<FMT_Q4_0><<<cdiv(N, 8), 256, 0, stream>>>(act, (const uint8_t*)w_blocks, out, N, K);
+}
+
+void mongoose_q8_0_matvec(const float* act, const void* w_blocks, float* out, int N, int K, cudaStream_t stream) {
+    if (N <= 0 || K < 32) return;
+    raw_block_matvec_kernel<FMT_Q8_0><<<cdiv(N, 8), 256, 0, stream>>>(act, (const uint8_t*)w_blocks, out, N, K);
+}
+
+void mongoose_q8_quantize_act(const float* act, void* q8_out, int K, cudaStream_t stream) {
+    if (K < 32) return;
+    quantize_act_kernel<<<cdiv(K / 32, 8), 256, 0, stream>>>(act, (ActBlock*)q8_out, K / 32);
+}
+
+void mongoose_q8_quantize_act_batch(const float* acts, void* q8_out, int K, int B, cudaStream_t stream) {
+    if (K < 32 || B <= 0) return;
+    const int total = (K / 32) * B;
+    quantize_act_kernel<<<cdiv(total, 8), 256, 0, stream>>>(acts, (ActBlock*)q8_out, total);
+}
+
+void mongoose_q4_0_matvec_dp4a_preq(const void* w_blocks, const void* q8, float* out, int N, int K,
+                                    cudaStream_t stream) {
+    if (N <= 0 || K < 32) return;
+    q4_0_dp4a_kernel<<<cdiv(N, 8), 256, 0, stream>>>((const uint8_t*)w_blocks, (const ActBlock*)q8, out, N, K, 1);
+}
+
+void mongoose_q4_0_matvec_dp4a_batch(const void* w_blocks, const void* q8, float* out, int N, int K, int B,
+                                     cudaStream_t stream) {
+    if (N <= 0 || K < 32 || B <= 0) return;
+    q4_0_dp4a_kernel<<<cdiv(N, 8), 256, 0, stream>>>((const uint8_t*)w_blocks, (const ActBlock*)q8, out, N, K, B);
+}
+
+void mongoose_q4_0_matvec_dp4a(const float* act, const void* w_blocks, float* out, int N, int K, void* scratch,
+                               cudaStream_t stream) {
+    if (N <= 0 || K < 32 || !scratch) return;
+    mongoose_q8_quantize_act(act, scratch, K, stream);
+    mongoose_q4_0_matvec_dp4a_preq(w_blocks, scratch, out, N, K, stream);
+}
+
+// The reference's per-token op order (cuda_fused_infer.go:414-444 / cuda_fused_infer_q4.go:103-131)
+// issued from one C call on caller-owned buffers.
+void mongoose_partial_step_q4_fused_graph(
+    const float** norm1, const void** wq, const void** wk, const void** wv, const void** wo,
+    const float** norm2, const void** wgate, const void** wup, const void** wdown,
+    float** kCache, float** vCache,
+    float* hidden, float* normed, float* Q, float* K, float* V,
+    float* attnOut, float* proj, float* normed2,
+    float* gatePre, float* upOut, float* ffnMid,
+    void* q8Scratch,
+    const float* cosTab, const float* sinTab,
+    int dim, int kvDim, int headDim, int ffnDim, int nHeads, int nKVHeads, int halfHead,
+    int pos, int layerStart, int layerEnd,
+    cudaStream_t stream) {
+    (void)q8Scratch;   // fp32 activations throughout: no activation quantization on this path
+    const float* cosRow = cosTab + (size_t)pos * halfHead;
+    const float* sinRow = sinTab + (size_t)pos * halfHead;
+    for (int l = layerStart; l < layerEnd; l++) {
+        mongoose_rmsnorm_out(hidden, normed, norm1[l], 1, dim, stream);
+        mongoose_q4_0_matvec(normed, wq[l], Q, dim, dim, stream);
+        mongoose_q4_0_matvec(normed, wk[l], K, kvDim, dim, stream);
+        mongoose_q4_0_matvec(normed, wv[l], V, kvDim, dim, stream);
+        mongoose_rope(Q, cosRow, sinRow, 1, dim, headDim, nHeads, stream);
+        mongoose_rope(K, cosRow, sinRow, 1, kvDim, headDim, nKVHeads, stream);
+        mongoose_kv_cache_write(kCache[l], K, pos, kvDim, stream);
+        mongoose_kv_cache_write(vCache[l], V, pos, kvDim, stream);
+        mongoose_decode_attention(Q, kCache[l], vCache[l], attnOut, pos + 1, dim, kvDim, nHeads, nKVHeads, stream);
+        mongoose_q4_0_matvec(attnOut, wo[l], proj, dim, dim, stream);
+        mongoose_add_inplace(hidden, proj, dim, stream);
+        mongoose_rmsnorm_out(hidden, normed2, norm2[l], 1, dim, stream);
+        mongoose_q4_0_matvec(normed2, wgate[l], gatePre, ffnDim, dim, stream);
+        mongoose_q4_0_matvec(normed2, wup[l], upOut, ffnDim, dim, stream);
+        mongoose_silu_gate_mul(gatePre, upOut, ffnMid, ffnDim, stream);
+        mongoose_q4_0_matvec(ffnMid, wdown[l], proj, dim, ffnDim, stream);
+        mongoose_add_inplace(hidden, proj, dim, stream);
+    }
+}
+
+}  // extern "C"

@@ -1,0 +1,487 @@
+// Fused single-token decode kernels for the mg_* engine (sm_100a).
+//
+// One "phase" kernel covers every dequant-matvec of a decode step.  A warp
+// owns a tile of R weight rows at a time and streams them with 16-byte
+// loads; lanes stride over the row's 16-byte chunks, so a warp instruction
+// reads 512 contiguous bytes per row.  The activation vector is staged once
+// per CTA in shared memory (after the fused RMSNorm / embedding prologue)
+// and shared by the R rows of a tile.  Weights are dequantized in registers,
+// block scales applied once per chunk, accumulation is fp32, and the R sums
+// are reduced with warp shuffles.  The epilogue is fused: RoPE + fp16 KV
+// append for QKV, residual add for wo/down, SiLU-gate for gate/up, argmax
+// for lm_head.
+//
+// Weight loads do not depend on activations, so each warp issues the loads
+// of its first D pipeline stages BEFORE griddepcontrol.wait: under
+// programmatic dependent launch the next kernel's weights are already in
+// flight while the previous kernel finishes.
+#pragma once
+
+#include "mg_common.cuh"
+
+namespace mg {
+
+// Device-resident cursor of the decode loop (one per sequence).
+struct StepState {
+    int pos;                    // position of the token being processed
+    int token;                  // input token id (embedding mode)
+    int step;                   // tokens generated since the cursor was set
+    int out_cap;                // capacity of out_tokens
+    unsigned long long best;    // packed (ordered logit, ~index) running argmax
+    unsigned int done;          // CTAs of the lm_head kernel that have finished
+    unsigned int pad;
+};
+
+enum : int { PRO_PLAIN = 0, PRO_RMS = 1, PRO_RMS_EMBED = 2 };
+enum : int { EPI_QKV = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_LOGITS = 3 };
+
+struct PhaseArgs {
+    WeightView w[3];      // QKV: wq,wk,wv; SWIGLU: gate,up; else w[0]
+    int rows[3];
+    int K;
+    int nitems;           // tiles of R rows
+    // prologue
+    int pro;
+    const float* x_src;   // PLAIN: input vector; RMS: hidden state
+    const float* norm_w;
+    float eps;
+    WeightView embed;     // RMS_EMBED: lm_head planes, row `token` is the input embedding
+    int embed_fmt;
+    float* h_store;       // RMS_EMBED: CTA 0 stores the embedded hidden state here
+    StepState* st;
+    // epilogue
+    const float* bias[3];
+    const float* resid_in;
+    float* out;           // RESID: hidden out; SWIGLU: ffn mid; LOGITS: logits (may be NULL)
+    float* q_out;
+    __half* k_cache;      // [max_seq, kv_dim] of this layer
+    __half* v_cache;
+    const float* cos_tab;
+    const float* sin_tab;
+    int head_dim;
+    int kv_dim;
+    int* out_tokens;
+};
+
+__device__ __forceinline__ unsigned long long pack_best(float v, unsigned int idx) {
+    unsigned int u = __float_as_uint(v);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xffffffffu - idx);
+}
+
+// ---------------------------------------------------------------------
+// Prologue: stage the activation vector x[K] in shared memory.
+// ---------------------------------------------------------------------
+__device__ __forceinline__ float embed_value(const WeightView& e, int fmt, int K, int token, int i) {
+    if (fmt == FMT_Q8_0) {
+        const int8_t q = reinterpret_cast<const int8_t*>(e.qs)[(size_t)token * K + i];
+        const float d = half_bits_to_float(e.ds[(size_t)token * (K / 32) + i / 32]);
+        return d * (float)q;
+    } else if (fmt == FMT_Q4_0) {
+        const int b = i / 32, j = i % 32;
+        const uint8_t byte = e.qs[(size_t)token * (K / 2) + b * 16 + (j & 15)];
+        const int nib = j < 16 ? (byte & 0xF) : (byte >> 4);
+        const float d = half_bits_to_float(e.ds[(size_t)token * (K / 32) + b]);
+        return d * (float)(nib - 8);
+    } else {
+        return half_bits_to_float(reinterpret_cast<const unsigned short*>(e.qs)[(size_t)token * K + i]);
+    }
+}
+
+__device__ __forceinline__ void stage_x(const PhaseArgs& a, float* xs, float* red) {
+    const int K = a.K;
+    if (a.pro == PRO_PLAIN) {
+        for (int i = threadIdx.x; i < K; i += blockDim.x) xs[i] = a.x_src[i];
+        __syncthreads();
+        return;
+    }
+    float ss = 0.f;
+    if (a.pro == PRO_RMS_EMBED) {
+        const int token = a.st->token;
+        for (int i = threadIdx.x; i < K; i += blockDim.x) {
+            const float v = embed_value(a.embed, a.embed_fmt, K, token, i);
+            xs[i] = v;
+            if (blockIdx.x == 0) a.h_store[i] = v;
+            ss = fmaf(v, v, ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < K; i += blockDim.x) {
+            const float v = a.x_src[i];
+            xs[i] = v;
+            ss = fmaf(v, v, ss);
+        }
+    }
+    const float tot = block_sum(ss, red);
+    const float scale = rsqrtf(tot / (float)K + a.eps);
+    for (int i = threadIdx.x; i < K; i += blockDim.x) xs[i] = xs[i] * scale * a.norm_w[i];
+    __syncthreads();
+}
+
+// ---------------------------------------------------------------------
+// Tile addressing: which rows (matrix, row) make up item `it`.
+// ---------------------------------------------------------------------
+template <int EPI, int R>
+struct Tile {
+    const uint8_t* q[R];
+    const unsigned short* d[R];
+    int m;       // matrix index (QKV)
+    int r0;      // first row (epilogue bookkeeping)
+};
+
+template <int FMT, int EPI, int R>
+__device__ __forceinline__ void tile_rows(const PhaseArgs& a, int it, Tile<EPI, R>& t) {
+    const int rb = plane_row_bytes(FMT, a.K);
+    const int nb = a.K / 32;
+    if (EPI == EPI_QKV) {
+        static_assert(EPI != EPI_QKV || R == 2, "QKV tiles are row pairs");
+        const int half = a.head_dim / 2;
+        const int nq = a.rows[0] / 2, nk = a.rows[1] / 2;
+        int m = 0, i = it;
+        if (i >= nq) { i -= nq; m = 1; }
+        if (m == 1 && i >= nk) { i -= nk; m = 2; }
+        int r0, r1;
+        if (m < 2) {
+            const int head = i / half, j = i - head * half;
+            r0 = head * a.head_dim + j;
+            r1 = r0 + half;
+        } else {
+            r0 = 2 * i;
+            r1 = r0 + 1;
+        }
+        t.m = m;
+        t.r0 = r0;
+        t.q[0] = a.w[m].qs + (size_t)r0 * rb;
+        t.q[R - 1] = a.w[m].qs + (size_t)r1 * rb;
+        t.d[0] = a.w[m].ds + (size_t)r0 * nb;
+        t.d[R - 1] = a.w[m].ds + (size_t)r1 * nb;
+    } else if (EPI == EPI_SWIGLU) {
+        // R/2 gate rows then the matching R/2 up rows
+        constexpr int H = R / 2;
+        t.m = 0;
+        t.r0 = it * H;
+#pragma unroll
+        for (int r = 0; r < H; r++) {
+            int row = it * H + r;
+            if (row >= a.rows[0]) row = a.rows[0] - 1;
+            t.q[r] = a.w[0].qs + (size_t)row * rb;
+            t.d[r] = a.w[0].ds + (size_t)row * nb;
+            t.q[H + r] = a.w[1].qs + (size_t)row * rb;
+            t.d[H + r] = a.w[1].ds + (size_t)row * nb;
+        }
+    } else {
+        t.m = 0;
+        t.r0 = it * R;
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            int row = it * R + r;
+            if (row >= a.rows[0]) row = a.rows[0] - 1;   // clamped rows are computed and discarded
+            t.q[r] = a.w[0].qs + (size_t)row * rb;
+            t.d[r] = a.w[0].ds + (size_t)row * nb;
+        }
+    }
+}
+
+template <int R>
+struct Stage {
+    uint4 w[R];
+    unsigned short d[R];
+};
+
+template <int FMT, int EPI, int R>
+__device__ __forceinline__ void load_stage(const Tile<EPI, R>& t, int c, bool valid, Stage<R>& s) {
+    using C = Chunk<FMT>;
+    if (valid) {
+#pragma unroll
+        for (int r = 0; r < R; r++) s.w[r] = ld_stream16(t.q[r] + (size_t)c * 16);
+        if (C::kScaled) {
+#pragma unroll
+            for (int r = 0; r < R; r++) s.d[r] = ld_stream_u16(t.d[r] + C::scale_index(c));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------
+// The phase kernel.  R rows per tile, D pipeline stages per warp.
+// Dynamic shared memory: K floats (x) + 40 floats (reductions).
+// ---------------------------------------------------------------------
+template <int FMT, int EPI, int R, int D>
+__global__ void __launch_bounds__(256) phase_kernel(const PhaseArgs a) {
+    using C = Chunk<FMT>;
+    extern __shared__ __align__(16) float smem[];
+    float* xs = smem;
+    float* red = smem + a.K;
+
+    const int lane = threadIdx.x & 31;
+    const int wpc = blockDim.x >> 5;
+    const int gw = blockIdx.x * wpc + (threadIdx.x >> 5);   // global warp index
+    const int nwarps = gridDim.x * wpc;
+    const int nchunks = a.K / C::kWeights;
+    const int steps = (nchunks + 31) >> 5;
+    const int my_items = gw < a.nitems ? (a.nitems - gw + nwarps - 1) / nwarps : 0;
+    const int T = my_items * steps;                          // flattened (item, step) iterations
+
+    // ---- weight prefetch: first D stages, independent of the previous kernel ----
+    Stage<R> st[D];
+    Tile<EPI, R> ld_tile;          // tile of the stage being loaded
+    int ld_k = 0, ld_step = 0;     // item ordinal / step of the next stage to load
+    if (T > 0) tile_rows<FMT, EPI, R>(a, gw, ld_tile);
+#pragma unroll
+    for (int j = 0; j < D; j++) {
+        if (j < T) {
+            const int c = ld_step * 32 + lane;
+            load_stage<FMT, EPI, R>(ld_tile, c, c < nchunks, st[j]);
+            if (++ld_step == steps) {
+                ld_step = 0;
+                ++ld_k;
+                if (ld_k < my_items) tile_rows<FMT, EPI, R>(a, gw + ld_k * nwarps, ld_tile);
+            }
+        }
+    }
+
+    pdl_launch_dependents();
+    pdl_wait();
+
+    stage_x(a, xs, red);
+
+    const int pos = (EPI == EPI_QKV) ? a.st->pos : 0;
+    unsigned long long best = 0ull;
+
+    float acc[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r] = 0.f;
+    int k = 0, step = 0;           // item ordinal / step being consumed
+    Tile<EPI, R> cur;
+    if (T > 0) tile_rows<FMT, EPI, R>(a, gw, cur);
+
+    for (int t0 = 0; t0 < T; t0 += D) {
+#pragma unroll
+        for (int j = 0; j < D; j++) {
+            if (t0 + j < T) {
+                // ---- consume stage j ----
+                const int c = step * 32 + lane;
+                if (c < nchunks) {
+                    float4 xv[C::kWeights / 4];
+                    const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)c * C::kWeights);
+#pragma unroll
+                    for (int i = 0; i < C::kWeights / 4; i++) xv[i] = xp[i];
+#pragma unroll
+                    for (int r = 0; r < R; r++) {
+                        const float p = C::dot(st[j].w[r], xv);
+                        if (C::kScaled) acc[r] = fmaf(half_bits_to_float(st[j].d[r]), p, acc[r]);
+                        else acc[r] += p;
+                    }
+                }
+                // ---- refill stage j with iteration t0 + j + D ----
+                if (t0 + j + D < T) {
+                    const int lc = ld_step * 32 + lane;
+                    load_stage<FMT, EPI, R>(ld_tile, lc, lc < nchunks, st[j]);
+                    if (++ld_step == steps) {
+                        ld_step = 0;
+                        ++ld_k;
+                        if (ld_k < my_items) tile_rows<FMT, EPI, R>(a, gw + ld_k * nwarps, ld_tile);
+                    }
+                }
+                // ---- end of tile: reduce + epilogue ----
+                if (++step == steps) {
+#pragma unroll
+                    for (int r = 0; r < R; r++) acc[r] = warp_sum(acc[r]);
+                    const int it = gw + k * nwarps;
+                    if (EPI == EPI_QKV) {
+                        if (lane == 0) {
+                            const int half = a.head_dim / 2;
+                            float v0 = acc[0], v1 = acc[R - 1];
+                            const int r0 = cur.r0;
+                            const int r1 = cur.m < 2 ? r0 + half : r0 + 1;
+                            const float* b = a.bias[cur.m];
+                            if (b) { v0 += b[r0]; v1 += b[r1]; }
+                            if (cur.m < 2) {
+                                const int j2 = r0 % a.head_dim;
+                                const float cs = a.cos_tab[(size_t)pos * half + j2];
+                                const float sn = a.sin_tab[(size_t)pos * half + j2];
+                                const float o0 = v0 * cs - v1 * sn;
+                                const float o1 = v0 * sn + v1 * cs;
+                                v0 = o0; v1 = o1;
+                            }
+                            if (cur.m == 0) {
+                                a.q_out[r0] = v0;
+                                a.q_out[r1] = v1;
+                            } else {
+                                __half* dst = (cur.m == 1 ? a.k_cache : a.v_cache) + (size_t)pos * a.kv_dim;
+                                dst[r0] = __float2half_rn(v0);
+                                dst[r1] = __float2half_rn(v1);
+                            }
+                        }
+                    } else if (EPI == EPI_RESID) {
+                        if (lane == 0) {
+#pragma unroll
+                            for (int r = 0; r < R; r++) {
+                                const int row = it * R + r;
+                                if (row < a.rows[0]) a.out[row] = a.resid_in[row] + acc[r];
+                            }
+                        }
+                    } else if (EPI == EPI_SWIGLU) {
+                        constexpr int H = R / 2;
+                        if (lane == 0) {
+#pragma unroll
+                            for (int r = 0; r < H; r++) {
+                                const int row = it * H + r;
+                                if (row < a.rows[0]) {
+                                    const float g = acc[r], u = acc[H + r];
+                                    a.out[row] = g * (1.0f / (1.0f + expf(-g))) * u;
+                                }
+                            }
+                        }
+                    } else {  // EPI_LOGITS
+                        if (lane == 0) {
+#pragma unroll
+                            for (int r = 0; r < R; r++) {
+                                const int row = it * R + r;
+                                if (row < a.rows[0]) {
+                                    if (a.out) a.out[row] = acc[r];
+                                    const unsigned long long key = pack_best(acc[r], (unsigned)row);
+                                    if (key > best) best = key;
+                                }
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int r = 0; r < R; r++) acc[r] = 0.f;
+                    step = 0;
+                    ++k;
+                    if (k < my_items) tile_rows<FMT, EPI, R>(a, gw + k * nwarps, cur);
+                }
+            }
+        }
+    }
+
+    if (EPI == EPI_LOGITS) {
+        // CTA-level argmax, one atomic per CTA, last CTA advances the cursor.
+        unsigned long long* sbest = reinterpret_cast<unsigned long long*>(red);   // 8-byte aligned: K is a multiple of 32
+        __syncthreads();
+        if (lane == 0) sbest[threadIdx.x >> 5] = best;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned long long b = sbest[0];
+            for (int w = 1; w < wpc; w++) b = sbest[w] > b ? sbest[w] : b;
+            StepState* s = a.st;
+            if (b) atomicMax(&s->best, b);
+            __threadfence();
+            const unsigned int ticket = atomicAdd(&s->done, 1u);
+            if (ticket == gridDim.x - 1) {
+                __threadfence();
+                const unsigned long long key = atomicMax(&s->best, 0ull);
+                const int tok = (int)(0xffffffffu - (unsigned int)(key & 0xffffffffull));
+                if (a.out_tokens && s->step < s->out_cap) a.out_tokens[s->step] = tok;
+                s->token = tok;
+                s->step += 1;
+                s->pos += 1;
+                s->best = 0ull;
+                s->done = 0u;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------
+// GQA decode attention over the fp16 KV cache of one layer.
+// One CTA per query head; scores for every cached position are held in
+// shared memory (max_seq floats).  Deterministic reductions.
+//   q      : fp32 [dim]          (already rotated)
+//   kc, vc : fp16 [max_seq, kv_dim]
+//   out    : fp32 [dim]
+// ---------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restrict__ q,
+                                                          const __half* __restrict__ kc,
+                                                          const __half* __restrict__ vc,
+                                                          float* __restrict__ out, const StepState* st,
+                                                          int kv_dim, int n_heads, int n_kv_heads) {
+    extern __shared__ __align__(16) float smem[];
+    float* qs = smem;                  // HD
+    float* red = smem + HD;            // 40
+    float* part = red + 40;            // 8 * HD  (cross-group partial outputs)
+    float* sc = part + 8 * HD;         // cache_len scores
+
+    pdl_launch_dependents();
+    pdl_wait();
+
+    const int head = blockIdx.x;
+    const int kvh = head / (n_heads / n_kv_heads);
+    const int len = st->pos + 1;
+    const float scale = rsqrtf((float)HD);
+    const int tid = threadIdx.x;
+
+    if (tid < HD) qs[tid] = q[head * HD + tid];
+    __syncthreads();
+
+    // scores
+    float mx = -INFINITY;
+    for (int t = tid; t < len; t += blockDim.x) {
+        const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)t * kv_dim + kvh * HD);
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < HD / 8; i++) {
+            const uint4 kk = kp[i];
+            const __half2* h = reinterpret_cast<const __half2*>(&kk);
+            const float4 qa = reinterpret_cast<const float4*>(qs)[2 * i];
+            const float4 qb = reinterpret_cast<const float4*>(qs)[2 * i + 1];
+            const float2 k0 = __half22float2(h[0]), k1 = __half22float2(h[1]);
+            const float2 k2 = __half22float2(h[2]), k3 = __half22float2(h[3]);
+            dot = fmaf(qa.x, k0.x, dot);
+            dot = fmaf(qa.y, k0.y, dot);
+            dot = fmaf(qa.z, k1.x, dot);
+            dot = fmaf(qa.w, k1.y, dot);
+            dot = fmaf(qb.x, k2.x, dot);
+            dot = fmaf(qb.y, k2.y, dot);
+            dot = fmaf(qb.z, k3.x, dot);
+            dot = fmaf(qb.w, k3.y, dot);
+        }
+        dot *= scale;
+        sc[t] = dot;
+        mx = fmaxf(mx, dot);
+    }
+    // block max
+    mx = warp_max(mx);
+    {
+        const int lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
+        if (lane == 0) red[wid] = mx;
+        __syncthreads();
+        float m = lane < nw ? red[lane] : -INFINITY;
+        m = warp_max(m);
+        mx = m;
+        __syncthreads();
+    }
+    float sum = 0.f;
+    for (int t = tid; t < len; t += blockDim.x) {
+        const float p = expf(sc[t] - mx);
+        sc[t] = p;
+        sum += p;
+    }
+    sum = block_sum(sum, red);   // includes the barrier that publishes sc[]
+    const float inv = 1.0f / sum;
+
+    // weighted sum of V: thread = (group g, dim pair dp)
+    constexpr int DP = HD / 2;                 // dim pairs
+    const int G = blockDim.x / DP;             // position groups (<= 8)
+    const int g = tid / DP, dp = tid % DP;
+    float2 o = make_float2(0.f, 0.f);
+    if (g < G) {
+        for (int t = g; t < len; t += G) {
+            const __half2 v = *reinterpret_cast<const __half2*>(vc + (size_t)t * kv_dim + kvh * HD + 2 * dp);
+            const float2 vf = __half22float2(v);
+            const float p = sc[t];
+            o.x = fmaf(p, vf.x, o.x);
+            o.y = fmaf(p, vf.y, o.y);
+        }
+        part[g * HD + 2 * dp] = o.x;
+        part[g * HD + 2 * dp + 1] = o.y;
+    }
+    __syncthreads();
+    if (tid < HD) {
+        float s = 0.f;
+        for (int gg = 0; gg < G; gg++) s += part[gg * HD + tid];
+        out[head * HD + tid] = s * inv;
+    }
+}
+
+}  // namespace mg

@@ -1,0 +1,808 @@
+// Host side of the mg_* decode engine: the counterpart of CUDAFusedInference
+// (cuda_fused_infer.go:75-459) written in C++ over the fused sm_100a kernels.
+//
+// Memory layout in HBM, per weight matrix [rows x K] (K a multiple of 32):
+//   qs plane : rows * row_bytes, rows contiguous and 16-byte aligned
+//              Q8_0 -> K int8;  Q4_0 -> K/2 bytes, 16 per block in GGUF nibble
+//              order;  F16 -> K halves
+//   ds plane : rows * K/32 fp16 block scales (Q8_0, Q4_0)
+// i.e. the 34/18-byte blocks are split into two streams at upload so that the
+// quants can be read with aligned 16-byte loads.  KV caches are fp16
+// [layers][max_seq][kv_dim]; activations fp32.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/mongoose_kernels.h"
+#include "decode_kernels.cuh"
+
+using namespace mg;
+
+namespace {
+
+struct DevMatrix {
+    uint8_t* qs = nullptr;
+    unsigned short* ds = nullptr;
+    int rows = 0, cols = 0, fmt = 0;
+    bool set = false;
+    WeightView view() const { return WeightView{qs, ds}; }
+};
+
+struct GraphKey {
+    int ls, le, mode, head;
+    bool operator<(const GraphKey& o) const {
+        if (ls != o.ls) return ls < o.ls;
+        if (le != o.le) return le < o.le;
+        if (mode != o.mode) return mode < o.mode;
+        return head < o.head;
+    }
+};
+
+struct CachedGraph {
+    cudaGraphExec_t exec = nullptr;
+    int kernels = 0;
+};
+
+}  // namespace
+
+struct mg_engine {
+    mg_config cfg{};
+    int num_sms = 148;
+    cudaStream_t stream = nullptr;
+    std::vector<DevMatrix> mats;        // indexed by weight slot
+    std::vector<float*> vecs;           // norms / biases by slot
+    float *cos_tab = nullptr, *sin_tab = nullptr;
+    __half *kc = nullptr, *vc = nullptr;   // [layers][max_seq][kv_dim]
+    float *h = nullptr, *h2 = nullptr, *q = nullptr, *attn = nullptr, *mid = nullptr, *logits = nullptr;
+    StepState* st = nullptr;
+    int* out_tokens = nullptr;
+    int out_cap = 0;
+    // pinned staging
+    int* pin_i = nullptr;               // [0..3] cursor, [4..] prompt ids
+    int pin_i_cap = 0;
+    std::map<GraphKey, CachedGraph> graphs;
+    bool built = false;
+    bool use_graph = true;
+    bool use_pdl = true;
+    long long launches = 0;
+    int capture_kernels = 0;            // kernels enqueued by the current enqueue_step
+    size_t dev_bytes = 0;
+    std::string err;
+};
+
+namespace {
+
+int fail(mg_engine* e, int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (e) e->err = buf;
+    return code;
+}
+
+#define MG_CUDA(e, call)                                                                        \
+    do {                                                                                        \
+        cudaError_t _c = (call);                                                                \
+        if (_c != cudaSuccess)                                                                  \
+            return fail((e), MG_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(_c), \
+                        __FILE__, __LINE__);                                                    \
+    } while (0)
+
+template <typename T>
+int dev_alloc(mg_engine* e, T** p, size_t count) {
+    void* v = nullptr;
+    cudaError_t c = cudaMalloc(&v, count * sizeof(T));
+    if (c != cudaSuccess) {
+        cudaGetLastError();
+        return fail(e, MG_ERR_NOMEM, "cudaMalloc(%zu bytes) failed: %s", count * sizeof(T), cudaGetErrorString(c));
+    }
+    e->dev_bytes += count * sizeof(T);
+    *p = static_cast<T*>(v);
+    return MG_OK;
+}
+
+bool slot_info(const mg_config& c, int idx, bool* is_matrix, int* rows, int* cols, int* fmt) {
+    const int nL = c.n_layers;
+    if (idx < 0 || idx >= nL * 12 + 2) return false;
+    *is_matrix = false;
+    *rows = 1;
+    *cols = c.dim;
+    *fmt = c.layer_fmt;
+    if (idx == nL * 12) return true;
+    if (idx == nL * 12 + 1) {
+        *is_matrix = true; *rows = c.vocab; *cols = c.dim; *fmt = c.head_fmt;
+        return true;
+    }
+    switch (idx % 12) {
+        case 0: case 8: break;
+        case 1: case 7: *is_matrix = true; *rows = c.dim; *cols = c.dim; break;
+        case 2: case 3: *is_matrix = true; *rows = c.kv_dim; *cols = c.dim; break;
+        case 4: *cols = c.dim; break;
+        case 5: case 6: *cols = c.kv_dim; break;
+        case 9: case 10: *is_matrix = true; *rows = c.ffn_dim; *cols = c.dim; break;
+        case 11: *is_matrix = true; *rows = c.dim; *cols = c.ffn_dim; break;
+    }
+    return true;
+}
+
+size_t raw_row_bytes(int fmt, int K) {
+    return fmt == FMT_Q8_0 ? (size_t)(K / 32) * 34 : fmt == FMT_Q4_0 ? (size_t)(K / 32) * 18 : (size_t)K * 2;
+}
+
+inline int round_half_away(float v) { return (int)(v + (v > 0 ? 0.5f : -0.5f)); }
+
+// Host quantization of one fp32 matrix straight into the two planes.
+// Q8_0: d = amax/127 per block of 32, q = round-half-away(v * 127/amax), clamp +-127.
+// Q4_0: d = amax/8, nib = round-half-away(v * 8/amax) + 8, clamp 0..15, byte j = elem j | elem j+16 << 4.
+// d is stored as fp16 (round to nearest even); the quants use the unrounded fp32 ratio.
+void quantize_planes(int fmt, const float* w, int rows, int K, uint8_t* qs, unsigned short* ds) {
+    const int nb = K / 32;
+    for (int r = 0; r < rows; r++) {
+        const float* src = w + (size_t)r * K;
+        if (fmt == FMT_F16) {
+            __half* o = reinterpret_cast<__half*>(qs) + (size_t)r * K;
+            for (int k = 0; k < K; k++) o[k] = __float2half_rn(src[k]);
+            continue;
+        }
+        for (int b = 0; b < nb; b++) {
+            const float* s = src + b * 32;
+            float amax = 0.f;
+            for (int j = 0; j < 32; j++) {
+                const float v = fabsf(s[j]);
+                if (v > amax) amax = v;
+            }
+            if (fmt == FMT_Q8_0) {
+                const __half d = __float2half_rn(amax / 127.0f);
+                ds[(size_t)r * nb + b] = __half_as_ushort(d);
+                const float inv = amax > 0 ? 127.0f / amax : 0.f;
+                int8_t* o = reinterpret_cast<int8_t*>(qs) + (size_t)r * K + b * 32;
+                for (int j = 0; j < 32; j++) {
+                    float v = s[j] * inv;
+                    if (v > 127.f) v = 127.f;
+                    if (v < -127.f) v = -127.f;
+                    o[j] = (int8_t)round_half_away(v);
+                }
+            } else {
+                const __half d = __float2half_rn(amax / 8.0f);
+                ds[(size_t)r * nb + b] = __half_as_ushort(d);
+                const float inv = amax > 0 ? 8.0f / amax : 0.f;
+                uint8_t* o = qs + (size_t)r * (K / 2) + b * 16;
+                for (int j = 0; j < 16; j++) {
+                    int q0 = round_half_away(s[j] * inv) + 8;
+                    int q1 = round_half_away(s[j + 16] * inv) + 8;
+                    q0 = q0 < 0 ? 0 : q0 > 15 ? 15 : q0;
+                    q1 = q1 < 0 ? 0 : q1 > 15 ? 15 : q1;
+                    o[j] = (uint8_t)(q0 | (q1 << 4));
+                }
+            }
+        }
+    }
+}
+
+// Split raw 34/18-byte blocks into the two planes.
+void split_raw_blocks(int fmt, const uint8_t* raw, int rows, int K, uint8_t* qs, unsigned short* ds) {
+    const int nb = K / 32;
+    if (fmt == FMT_F16) {
+        memcpy(qs, raw, (size_t)rows * K * 2);
+        return;
+    }
+    const int bb = fmt == FMT_Q8_0 ? 34 : 18;
+    const int qb = bb - 2;
+    for (size_t i = 0; i < (size_t)rows * nb; i++) {
+        const uint8_t* blk = raw + i * bb;
+        memcpy(&ds[i], blk, 2);
+        memcpy(qs + i * qb, blk + 2, qb);
+    }
+}
+
+int upload_planes(mg_engine* e, int idx, int fmt, int rows, int K, const std::vector<uint8_t>& qs,
+                  const std::vector<unsigned short>& ds) {
+    DevMatrix& m = e->mats[idx];
+    if (m.qs) { cudaFree(m.qs); e->dev_bytes -= (size_t)m.rows * plane_row_bytes(m.fmt, m.cols); m.qs = nullptr; }
+    if (m.ds) { cudaFree(m.ds); e->dev_bytes -= (size_t)m.rows * (m.cols / 32) * 2; m.ds = nullptr; }
+    int rc = dev_alloc(e, &m.qs, qs.size());
+    if (rc) return rc;
+    MG_CUDA(e, cudaMemcpy(m.qs, qs.data(), qs.size(), cudaMemcpyHostToDevice));
+    if (fmt != FMT_F16) {
+        rc = dev_alloc(e, &m.ds, ds.size());
+        if (rc) return rc;
+        MG_CUDA(e, cudaMemcpy(m.ds, ds.data(), ds.size() * 2, cudaMemcpyHostToDevice));
+    }
+    m.rows = rows; m.cols = K; m.fmt = fmt; m.set = true;
+    e->built = false;
+    return MG_OK;
+}
+
+// ------------------------------------------------------------------
+// Kernel selection and launch
+// ------------------------------------------------------------------
+typedef void (*phase_fn_t)(const PhaseArgs);
+
+template <int FMT>
+phase_fn_t phase_fn_fmt(int epi, int R) {
+    switch (epi) {
+        case EPI_QKV: return phase_kernel<FMT, EPI_QKV, 2, 4>;
+        case EPI_SWIGLU: return R == 4 ? phase_kernel<FMT, EPI_SWIGLU, 4, 2> : phase_kernel<FMT, EPI_SWIGLU, 2, 4>;
+        case EPI_LOGITS: return phase_kernel<FMT, EPI_LOGITS, 4, 2>;
+        default:
+            return R == 4 ? phase_kernel<FMT, EPI_RESID, 4, 2>
+                 : R == 2 ? phase_kernel<FMT, EPI_RESID, 2, 4>
+                          : phase_kernel<FMT, EPI_RESID, 1, 8>;
+    }
+}
+
+phase_fn_t phase_fn(int fmt, int epi, int R) {
+    return fmt == FMT_Q8_0 ? phase_fn_fmt<FMT_Q8_0>(epi, R)
+         : fmt == FMT_Q4_0 ? phase_fn_fmt<FMT_Q4_0>(epi, R)
+                           : phase_fn_fmt<FMT_F16>(epi, R);
+}
+
+const int kMaxDynSmem = 120 * 1024;
+
+int set_kernel_attrs(mg_engine* e) {
+    for (int fmt = 0; fmt < 3; fmt++)
+        for (int epi = 0; epi < 4; epi++)
+            for (int R = 1; R <= 4; R *= 2)
+                MG_CUDA(e, cudaFuncSetAttribute((const void*)phase_fn(fmt, epi, R),
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
+    MG_CUDA(e, cudaFuncSetAttribute((const void*)attn_decode_kernel<64>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
+    MG_CUDA(e, cudaFuncSetAttribute((const void*)attn_decode_kernel<128>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
+    MG_CUDA(e, cudaFuncSetAttribute((const void*)attn_decode_kernel<32>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
+    return MG_OK;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch(mg_engine* e, cudaStream_t s, void (*kern)(KArgs...), int grid, int threads, size_t smem,
+                   Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = e->use_pdl ? 1 : 0;
+    e->capture_kernels++;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+// Warps per CTA and grid for a phase of `nitems` warp tiles: spread over every SM
+// first, then up to 8 warps per CTA, then two CTAs per SM; warps loop beyond that.
+void phase_shape(const mg_engine* e, int nitems, int* grid, int* threads) {
+    const int sms = e->num_sms;
+    int wpc = (nitems + sms - 1) / sms;
+    if (wpc < 1) wpc = 1;
+    if (wpc > 8) wpc = 8;
+    int g = (nitems + wpc - 1) / wpc;
+    if (g > 2 * sms) g = 2 * sms;
+    if (g < 1) g = 1;
+    *grid = g;
+    *threads = wpc * 32;
+}
+
+int launch_phase(mg_engine* e, cudaStream_t s, int fmt, int epi, int R, PhaseArgs& a) {
+    int grid, threads;
+    phase_shape(e, a.nitems, &grid, &threads);
+    const size_t smem = ((size_t)a.K + 40) * sizeof(float);
+    if (smem > (size_t)kMaxDynSmem) return fail(e, MG_ERR_UNSUPPORTED, "input dim %d too large", a.K);
+    MG_CUDA(e, launch(e, s, phase_fn(fmt, epi, R), grid, threads, smem, a));
+    return MG_OK;
+}
+
+int pick_rows_per_tile(const mg_engine* e, int rows) {
+    const int warps = e->num_sms * 16;
+    if (rows >= warps * 8) return 4;
+    if (rows >= warps * 2) return 2;
+    return 1;
+}
+
+enum { MODE_EMBED = 0, MODE_HIDDEN = 1 };
+enum { HEAD_NONE = 0, HEAD_ARGMAX = 1, HEAD_LOGITS = 2 };
+
+// One token through layers [ls, le) (+ head).  The op order is PartialStep's
+// (cuda_fused_infer.go:414-451) with its 17 launches per layer fused into 5.
+int enqueue_step(mg_engine* e, cudaStream_t s, int ls, int le, int mode, int head) {
+    const mg_config& c = e->cfg;
+    const int L = c.n_layers;
+    e->capture_kernels = 0;
+    for (int l = ls; l < le && l < L; l++) {
+        const int b = l * 12;
+        const size_t kvoff = (size_t)l * c.max_seq * c.kv_dim;
+        {   // RMSNorm + QKV + bias + RoPE + KV append
+            PhaseArgs a{};
+            a.w[0] = e->mats[b + 1].view(); a.w[1] = e->mats[b + 2].view(); a.w[2] = e->mats[b + 3].view();
+            a.rows[0] = c.dim; a.rows[1] = c.kv_dim; a.rows[2] = c.kv_dim;
+            a.K = c.dim;
+            a.nitems = (c.dim + 2 * c.kv_dim) / 2;
+            const bool embed = (mode == MODE_EMBED && l == 0);
+            a.pro = embed ? PRO_RMS_EMBED : PRO_RMS;
+            a.x_src = e->h;
+            a.norm_w = e->vecs[b + 0];
+            a.eps = c.rms_eps;
+            a.embed = e->mats[L * 12 + 1].view();
+            a.embed_fmt = c.head_fmt;
+            a.h_store = e->h;
+            a.st = e->st;
+            a.bias[0] = e->vecs[b + 4]; a.bias[1] = e->vecs[b + 5]; a.bias[2] = e->vecs[b + 6];
+            a.q_out = e->q;
+            a.k_cache = e->kc + kvoff;
+            a.v_cache = e->vc + kvoff;
+            a.cos_tab = e->cos_tab; a.sin_tab = e->sin_tab;
+            a.head_dim = c.head_dim; a.kv_dim = c.kv_dim;
+            int rc = launch_phase(e, s, c.layer_fmt, EPI_QKV, 2, a);
+            if (rc) return rc;
+        }
+        {   // attention
+            const size_t smem = ((size_t)c.head_dim * 9 + 40 + c.max_seq) * sizeof(float);
+            if (smem > (size_t)kMaxDynSmem) return fail(e, MG_ERR_UNSUPPORTED, "max_seq %d too large", c.max_seq);
+            cudaError_t ce;
+            if (c.head_dim == 64)
+                ce = launch(e, s, attn_decode_kernel<64>, c.n_heads, 256, smem, (const float*)e->q,
+                            (const __half*)(e->kc + kvoff), (const __half*)(e->vc + kvoff), e->attn,
+                            (const StepState*)e->st, c.kv_dim, c.n_heads, c.n_kv_heads);
+            else if (c.head_dim == 128)
+                ce = launch(e, s, attn_decode_kernel<128>, c.n_heads, 256, smem, (const float*)e->q,
+                            (const __half*)(e->kc + kvoff), (const __half*)(e->vc + kvoff), e->attn,
+                            (const StepState*)e->st, c.kv_dim, c.n_heads, c.n_kv_heads);
+            else
+                ce = launch(e, s, attn_decode_kernel<32>, c.n_heads, 256, smem, (const float*)e->q,
+                            (const __half*)(e->kc + kvoff), (const __half*)(e->vc + kvoff), e->attn,
+                            (const StepState*)e->st, c.kv_dim, c.n_heads, c.n_kv_heads);
+            MG_CUDA(e, ce);
+        }
+        {   // wo + residual: h2 = h + Wo attn
+            PhaseArgs a{};
+            const int R = pick_rows_per_tile(e, c.dim);
+            a.w[0] = e->mats[b + 7].view();
+            a.rows[0] = c.dim; a.K = c.dim;
+            a.nitems = (c.dim + R - 1) / R;
+            a.pro = PRO_PLAIN; a.x_src = e->attn;
+            a.resid_in = e->h; a.out = e->h2; a.st = e->st;
+            int rc = launch_phase(e, s, c.layer_fmt, EPI_RESID, R, a);
+            if (rc) return rc;
+        }
+        {   // RMSNorm + gate/up + SiLU-gate
+            PhaseArgs a{};
+            const int R = (c.ffn_dim >= e->num_sms * 16 * 8) ? 4 : 2;
+            a.w[0] = e->mats[b + 9].view(); a.w[1] = e->mats[b + 10].view();
+            a.rows[0] = c.ffn_dim; a.rows[1] = c.ffn_dim; a.K = c.dim;
+            a.nitems = (c.ffn_dim + R / 2 - 1) / (R / 2);
+            a.pro = PRO_RMS; a.x_src = e->h2; a.norm_w = e->vecs[b + 8]; a.eps = c.rms_eps;
+            a.out = e->mid; a.st = e->st;
+            int rc = launch_phase(e, s, c.layer_fmt, EPI_SWIGLU, R, a);
+            if (rc) return rc;
+        }
+        {   // down + residual: h = h2 + Wd mid
+            PhaseArgs a{};
+            const int R = pick_rows_per_tile(e, c.dim);
+            a.w[0] = e->mats[b + 11].view();
+            a.rows[0] = c.dim; a.K = c.ffn_dim;
+            a.nitems = (c.dim + R - 1) / R;
+            a.pro = PRO_PLAIN; a.x_src = e->mid;
+            a.resid_in = e->h2; a.out = e->h; a.st = e->st;
+            int rc = launch_phase(e, s, c.layer_fmt, EPI_RESID, R, a);
+            if (rc) return rc;
+        }
+    }
+    if (le >= L && head != HEAD_NONE) {
+        PhaseArgs a{};
+        a.w[0] = e->mats[L * 12 + 1].view();
+        a.rows[0] = c.vocab; a.K = c.dim;
+        a.nitems = (c.vocab + 3) / 4;
+        a.pro = PRO_RMS; a.x_src = e->h; a.norm_w = e->vecs[L * 12]; a.eps = c.rms_eps;
+        a.out = head == HEAD_LOGITS ? e->logits : nullptr;
+        a.st = e->st;
+        a.out_tokens = e->out_tokens;
+        int rc = launch_phase(e, s, c.head_fmt, EPI_LOGITS, 4, a);
+        if (rc) return rc;
+    }
+    return MG_OK;
+}
+
+int run_step(mg_engine* e, int ls, int le, int mode, int head) {
+    if (!e->use_graph) {
+        int rc = enqueue_step(e, e->stream, ls, le, mode, head);
+        e->launches += e->capture_kernels;
+        return rc;
+    }
+    GraphKey key{ls, le, mode, head};
+    auto it = e->graphs.find(key);
+    if (it == e->graphs.end()) {
+        cudaGraph_t g = nullptr;
+        MG_CUDA(e, cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+        int rc = enqueue_step(e, e->stream, ls, le, mode, head);
+        cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+        if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+        MG_CUDA(e, ce);
+        CachedGraph cg;
+        cg.kernels = e->capture_kernels;
+        ce = cudaGraphInstantiate(&cg.exec, g, 0);
+        cudaGraphDestroy(g);
+        MG_CUDA(e, ce);
+        it = e->graphs.emplace(key, cg).first;
+    }
+    MG_CUDA(e, cudaGraphLaunch(it->second.exec, e->stream));
+    e->launches += it->second.kernels;
+    return MG_OK;
+}
+
+int ensure_built(mg_engine* e) {
+    if (e->built) return MG_OK;
+    return mg_build(e);
+}
+
+int check_engine(mg_engine* e) {
+    if (!e) return MG_ERR_ARG;
+    cudaError_t c = cudaSetDevice(e->cfg.device);
+    if (c != cudaSuccess) return fail(e, MG_ERR_CUDA, "cudaSetDevice(%d): %s", e->cfg.device, cudaGetErrorString(c));
+    return MG_OK;
+}
+
+void drop_graphs(mg_engine* e) {
+    for (auto& kv : e->graphs)
+        if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    e->graphs.clear();
+}
+
+}  // namespace
+
+// =====================================================================
+// C ABI
+// =====================================================================
+extern "C" {
+
+const char* mg_version(void) { return "mongoose-b200 decode engine, sm_100a"; }
+
+int mg_create(const mg_config* cfg, mg_engine** out) {
+    if (!cfg || !out) return MG_ERR_ARG;
+    *out = nullptr;
+    const mg_config& c = *cfg;
+    if (c.dim <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 || c.head_dim <= 0 || c.ffn_dim <= 0 ||
+        c.vocab <= 0 || c.n_layers <= 0 || c.max_seq <= 0)
+        return MG_ERR_ARG;
+    if (c.dim % 32 || c.ffn_dim % 32 || c.kv_dim != c.n_kv_heads * c.head_dim || c.dim != c.n_heads * c.head_dim ||
+        c.n_heads % c.n_kv_heads || (c.head_dim != 32 && c.head_dim != 64 && c.head_dim != 128))
+        return MG_ERR_ARG;
+    if (c.layer_fmt < 0 || c.layer_fmt > 2 || c.head_fmt < 0 || c.head_fmt > 2) return MG_ERR_ARG;
+    if (c.max_batch > 1) return MG_ERR_UNSUPPORTED;
+
+    mg_engine* e = new mg_engine();
+    e->cfg = c;
+    if (e->cfg.rms_eps == 0.f) e->cfg.rms_eps = 1e-6f;
+    if (e->cfg.max_batch < 1) e->cfg.max_batch = 1;
+    int rc = MG_OK;
+    auto bail = [&](int code) { mg_destroy(e); return code; };
+
+    cudaError_t ce = cudaSetDevice(c.device);
+    if (ce != cudaSuccess) return bail(MG_ERR_CUDA);
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, c.device) != cudaSuccess) return bail(MG_ERR_CUDA);
+    if (prop.major != 10) {
+        fprintf(stderr, "[mongoose-b200] device %d is sm_%d%d; this library is built for sm_100a only\n", c.device,
+                prop.major, prop.minor);
+        return bail(MG_ERR_UNSUPPORTED);
+    }
+    e->num_sms = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(MG_ERR_CUDA);
+
+    const int nw = c.n_layers * 12 + 2;
+    e->mats.resize(nw);
+    e->vecs.assign(nw, nullptr);
+
+    const int half = c.head_dim / 2;
+    const size_t kv_elems = (size_t)c.n_layers * c.max_seq * c.kv_dim;
+    e->out_cap = c.max_seq > 4096 ? c.max_seq : 4096;
+    if ((rc = dev_alloc(e, &e->cos_tab, (size_t)c.max_seq * half))) return bail(rc);
+    if ((rc = dev_alloc(e, &e->sin_tab, (size_t)c.max_seq * half))) return bail(rc);
+    if ((rc = dev_alloc(e, &e->kc, kv_elems))) return bail(rc);
+    if ((rc = dev_alloc(e, &e->vc, kv_elems))) return bail(rc);
+    if ((rc = dev_alloc(e, &e->h, (size_t)c.dim))) return bail(rc);
+    if ((rc = dev_alloc(e, &e->h2, (size_t)c.dim))) return bail(rc);
+    if ((rc = dev_alloc(e, &e->q, (size_t)c.dim))) return bail(rc);
+    if ((rc = dev_alloc(e, &e->attn, (size_t)c.dim))) return bail(rc);
+    if ((rc = dev_alloc(e, &e->mid, (size_t)c.ffn_dim))) return bail(rc);
+    if ((rc = dev_alloc(e, &e->logits, (size_t)c.vocab))) return bail(rc);
+    if ((rc = dev_alloc(e, &e->st, (size_t)1))) return bail(rc);
+    if ((rc = dev_alloc(e, &e->out_tokens, (size_t)e->out_cap))) return bail(rc);
+
+    // RoPE tables in float64 on the host, narrowed to fp32 (cuda_fused_infer.go:181-190).
+    {
+        std::vector<float> cs((size_t)c.max_seq * half), sn((size_t)c.max_seq * half);
+        for (int pos = 0; pos < c.max_seq; pos++)
+            for (int j = 0; j < half; j++) {
+                const double freq = 1.0 / pow(c.rope_theta, (double)(2 * j) / (double)c.head_dim);
+                const double ang = (double)pos * freq;
+                cs[(size_t)pos * half + j] = (float)cos(ang);
+                sn[(size_t)pos * half + j] = (float)sin(ang);
+            }
+        if (cudaMemcpy(e->cos_tab, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess ||
+            cudaMemcpy(e->sin_tab, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess)
+            return bail(MG_ERR_CUDA);
+    }
+    if (cudaMemset(e->kc, 0, kv_elems * 2) != cudaSuccess || cudaMemset(e->vc, 0, kv_elems * 2) != cudaSuccess ||
+        cudaMemset(e->h, 0, (size_t)c.dim * 4) != cudaSuccess || cudaMemset(e->out_tokens, 0, (size_t)e->out_cap * 4) != cudaSuccess)
+        return bail(MG_ERR_CUDA);
+    StepState s0{};
+    s0.out_cap = e->out_cap;
+    if (cudaMemcpy(e->st, &s0, sizeof s0, cudaMemcpyHostToDevice) != cudaSuccess) return bail(MG_ERR_CUDA);
+
+    e->pin_i_cap = 8 + e->out_cap;
+    if (cudaMallocHost((void**)&e->pin_i, (size_t)e->pin_i_cap * sizeof(int)) != cudaSuccess) return bail(MG_ERR_NOMEM);
+
+    if ((rc = set_kernel_attrs(e))) return bail(rc);
+    const char* env = getenv("MG_NO_GRAPH");
+    if (env && env[0] == '1') e->use_graph = false;
+    env = getenv("MG_NO_PDL");
+    if (env && env[0] == '1') e->use_pdl = false;
+    *out = e;
+    return MG_OK;
+}
+
+void mg_destroy(mg_engine* e) {
+    if (!e) return;
+    cudaSetDevice(e->cfg.device);
+    if (e->stream) cudaStreamSynchronize(e->stream);
+    drop_graphs(e);
+    for (auto& m : e->mats) {
+        if (m.qs) cudaFree(m.qs);
+        if (m.ds) cudaFree(m.ds);
+    }
+    for (float* v : e->vecs)
+        if (v) cudaFree(v);
+    cudaFree(e->cos_tab); cudaFree(e->sin_tab); cudaFree(e->kc); cudaFree(e->vc);
+    cudaFree(e->h); cudaFree(e->h2); cudaFree(e->q); cudaFree(e->attn); cudaFree(e->mid); cudaFree(e->logits);
+    cudaFree(e->st); cudaFree(e->out_tokens);
+    if (e->pin_i) cudaFreeHost(e->pin_i);
+    if (e->stream) cudaStreamDestroy(e->stream);
+    delete e;
+}
+
+int mg_num_weights(const mg_engine* e) { return e ? e->cfg.n_layers * 12 + 2 : 0; }
+
+int mg_set_weight(mg_engine* e, int idx, const float* data, size_t count) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    bool is_matrix; int rows, cols, fmt;
+    if (!data || !slot_info(e->cfg, idx, &is_matrix, &rows, &cols, &fmt))
+        return fail(e, MG_ERR_ARG, "mg_set_weight: bad slot %d", idx);
+    if (count != (size_t)rows * cols)
+        return fail(e, MG_ERR_ARG, "mg_set_weight: slot %d wants %d x %d values, got %zu", idx, rows, cols, count);
+    if (!is_matrix) {
+        if (!e->vecs[idx] && (rc = dev_alloc(e, &e->vecs[idx], (size_t)cols))) return rc;
+        MG_CUDA(e, cudaMemcpy(e->vecs[idx], data, (size_t)cols * 4, cudaMemcpyHostToDevice));
+        e->built = false;
+        return MG_OK;
+    }
+    std::vector<uint8_t> qs((size_t)rows * plane_row_bytes(fmt, cols));
+    std::vector<unsigned short> ds(fmt == FMT_F16 ? 0 : (size_t)rows * (cols / 32));
+    quantize_planes(fmt, data, rows, cols, qs.data(), ds.data());
+    return upload_planes(e, idx, fmt, rows, cols, qs, ds);
+}
+
+int mg_set_weight_raw(mg_engine* e, int idx, const void* blocks, size_t bytes, int fmt) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    bool is_matrix; int rows, cols, slot_fmt;
+    if (!blocks || !slot_info(e->cfg, idx, &is_matrix, &rows, &cols, &slot_fmt) || !is_matrix)
+        return fail(e, MG_ERR_ARG, "mg_set_weight_raw: slot %d is not a matrix slot", idx);
+    if (fmt != slot_fmt)
+        return fail(e, MG_ERR_ARG, "mg_set_weight_raw: slot %d is configured for format %d, got %d", idx, slot_fmt, fmt);
+    if (bytes != (size_t)rows * raw_row_bytes(fmt, cols))
+        return fail(e, MG_ERR_ARG, "mg_set_weight_raw: slot %d wants %zu bytes, got %zu", idx,
+                    (size_t)rows * raw_row_bytes(fmt, cols), bytes);
+    std::vector<uint8_t> qs((size_t)rows * plane_row_bytes(fmt, cols));
+    std::vector<unsigned short> ds(fmt == FMT_F16 ? 0 : (size_t)rows * (cols / 32));
+    split_raw_blocks(fmt, static_cast<const uint8_t*>(blocks), rows, cols, qs.data(), ds.data());
+    return upload_planes(e, idx, fmt, rows, cols, qs, ds);
+}
+
+int mg_build(mg_engine* e) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    const mg_config& c = e->cfg;
+    for (int idx = 0; idx < c.n_layers * 12 + 2; idx++) {
+        bool is_matrix; int rows, cols, fmt;
+        slot_info(c, idx, &is_matrix, &rows, &cols, &fmt);
+        const int w = idx < c.n_layers * 12 ? idx % 12 : -1;
+        if (w >= 4 && w <= 6) continue;   // biases are optional (cuda_fused_infer.go:255)
+        if (is_matrix ? !e->mats[idx].set : e->vecs[idx] == nullptr)
+            return fail(e, MG_ERR_STATE, "mg_build: weight slot %d has not been set", idx);
+    }
+    drop_graphs(e);
+    e->built = true;
+    return MG_OK;
+}
+
+int mg_reset_kv(mg_engine* e) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    const size_t kv_bytes = (size_t)e->cfg.n_layers * e->cfg.max_seq * e->cfg.kv_dim * 2;
+    MG_CUDA(e, cudaMemsetAsync(e->kc, 0, kv_bytes, e->stream));
+    MG_CUDA(e, cudaMemsetAsync(e->vc, 0, kv_bytes, e->stream));
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    return MG_OK;
+}
+
+int mg_set_cursor(mg_engine* e, int token, int pos) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if (pos < 0 || pos >= e->cfg.max_seq || token < 0 || token >= e->cfg.vocab)
+        return fail(e, MG_ERR_ARG, "mg_set_cursor: token %d / pos %d out of range", token, pos);
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    e->pin_i[0] = pos; e->pin_i[1] = token; e->pin_i[2] = 0;
+    MG_CUDA(e, cudaMemcpyAsync(e->st, e->pin_i, 12, cudaMemcpyHostToDevice, e->stream));
+    return MG_OK;
+}
+
+int mg_get_cursor(mg_engine* e, int* token, int* pos) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    StepState s{};
+    MG_CUDA(e, cudaMemcpyAsync(&s, e->st, sizeof s, cudaMemcpyDeviceToHost, e->stream));
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    if (token) *token = s.token;
+    if (pos) *pos = s.pos;
+    return MG_OK;
+}
+
+int mg_sync(mg_engine* e) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    return MG_OK;
+}
+
+int mg_partial_step(mg_engine* e, const float* hidden_in, int pos, int layer_start, int layer_end,
+                    float* hidden_out, float* logits_out) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if ((rc = ensure_built(e))) return rc;
+    const mg_config& c = e->cfg;
+    if (!hidden_in || pos < 0 || pos >= c.max_seq || layer_start < 0 || layer_end < layer_start)
+        return fail(e, MG_ERR_ARG, "mg_partial_step: bad arguments (pos %d, layers [%d,%d))", pos, layer_start, layer_end);
+    if (layer_end > c.n_layers) layer_end = c.n_layers;
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));   // pin_i is reused
+    e->pin_i[0] = pos; e->pin_i[1] = 0;
+    MG_CUDA(e, cudaMemcpyAsync(e->st, e->pin_i, 8, cudaMemcpyHostToDevice, e->stream));
+    MG_CUDA(e, cudaMemcpyAsync(e->h, hidden_in, (size_t)c.dim * 4, cudaMemcpyHostToDevice, e->stream));
+    const bool want_logits = layer_end >= c.n_layers && logits_out;
+    if ((rc = run_step(e, layer_start, layer_end, MODE_HIDDEN, want_logits ? HEAD_LOGITS : HEAD_NONE))) return rc;
+    if (want_logits)
+        MG_CUDA(e, cudaMemcpyAsync(logits_out, e->logits, (size_t)c.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
+    else if (hidden_out)
+        MG_CUDA(e, cudaMemcpyAsync(hidden_out, e->h, (size_t)c.dim * 4, cudaMemcpyDeviceToHost, e->stream));
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    return MG_OK;
+}
+
+int mg_export_hidden(mg_engine* e, float* hidden_out) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if (!hidden_out) return MG_ERR_ARG;
+    MG_CUDA(e, cudaMemcpyAsync(hidden_out, e->h, (size_t)e->cfg.dim * 4, cudaMemcpyDeviceToHost, e->stream));
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    return MG_OK;
+}
+
+int mg_step_token(mg_engine* e, int token, int pos, int* next_token, float* logits_out) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if ((rc = ensure_built(e))) return rc;
+    const mg_config& c = e->cfg;
+    if (token < 0 || token >= c.vocab || pos < 0 || pos >= c.max_seq)
+        return fail(e, MG_ERR_ARG, "mg_step_token: token %d / pos %d out of range", token, pos);
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    e->pin_i[0] = pos; e->pin_i[1] = token;
+    MG_CUDA(e, cudaMemcpyAsync(e->st, e->pin_i, 8, cudaMemcpyHostToDevice, e->stream));
+    if ((rc = run_step(e, 0, c.n_layers, MODE_EMBED, logits_out ? HEAD_LOGITS : HEAD_ARGMAX))) return rc;
+    if (logits_out)
+        MG_CUDA(e, cudaMemcpyAsync(logits_out, e->logits, (size_t)c.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
+    MG_CUDA(e, cudaMemcpyAsync(e->pin_i + 4, &e->st->token, 4, cudaMemcpyDeviceToHost, e->stream));
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    if (next_token) *next_token = e->pin_i[4];
+    return MG_OK;
+}
+
+int mg_enqueue_greedy(mg_engine* e, int n_steps) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if ((rc = ensure_built(e))) return rc;
+    for (int i = 0; i < n_steps; i++)
+        if ((rc = run_step(e, 0, e->cfg.n_layers, MODE_EMBED, HEAD_ARGMAX))) return rc;
+    return MG_OK;
+}
+
+int mg_generate(mg_engine* e, const int* prompt, int n_prompt, int n_new, int start_pos, int* out_tokens) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if ((rc = ensure_built(e))) return rc;
+    const mg_config& c = e->cfg;
+    if (!prompt || n_prompt < 1 || n_new < 1 || !out_tokens || start_pos < 0 ||
+        start_pos + n_prompt + n_new - 1 > c.max_seq || n_prompt + n_new > e->out_cap)
+        return fail(e, MG_ERR_ARG, "mg_generate: %d prompt + %d new tokens from position %d do not fit max_seq %d",
+                    n_prompt, n_new, start_pos, c.max_seq);
+    for (int i = 0; i < n_prompt; i++)
+        if (prompt[i] < 0 || prompt[i] >= c.vocab) return fail(e, MG_ERR_ARG, "mg_generate: prompt id out of range");
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    e->pin_i[0] = start_pos; e->pin_i[1] = prompt[0]; e->pin_i[2] = 0;
+    for (int i = 0; i < n_prompt; i++) e->pin_i[8 + i] = prompt[i];
+    MG_CUDA(e, cudaMemcpyAsync(e->st, e->pin_i, 12, cudaMemcpyHostToDevice, e->stream));
+    const int total = n_prompt + n_new - 1;
+    for (int i = 0; i < total; i++) {
+        if (i > 0 && i < n_prompt)   // prompt tokens override the fed-back argmax
+            MG_CUDA(e, cudaMemcpyAsync(&e->st->token, e->pin_i + 8 + i, 4, cudaMemcpyHostToDevice, e->stream));
+        if ((rc = run_step(e, 0, c.n_layers, MODE_EMBED, HEAD_ARGMAX))) return rc;
+    }
+    MG_CUDA(e, cudaMemcpyAsync(out_tokens, e->out_tokens + (n_prompt - 1), (size_t)n_new * 4, cudaMemcpyDeviceToHost,
+                               e->stream));
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    return MG_OK;
+}
+
+int mg_dequant_rows(mg_engine* e, int idx, int row0, int nrows, float* out) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if (!out || idx < 0 || idx >= (int)e->mats.size() || !e->mats[idx].set)
+        return fail(e, MG_ERR_ARG, "mg_dequant_rows: slot %d is not a set matrix", idx);
+    const DevMatrix& m = e->mats[idx];
+    if (row0 < 0 || nrows < 0 || row0 + nrows > m.rows) return fail(e, MG_ERR_ARG, "mg_dequant_rows: rows out of range");
+    const int K = m.cols, nb = K / 32, rb = plane_row_bytes(m.fmt, K);
+    std::vector<uint8_t> qs((size_t)nrows * rb);
+    std::vector<unsigned short> ds(m.fmt == FMT_F16 ? 0 : (size_t)nrows * nb);
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    MG_CUDA(e, cudaMemcpy(qs.data(), m.qs + (size_t)row0 * rb, qs.size(), cudaMemcpyDeviceToHost));
+    if (!ds.empty()) MG_CUDA(e, cudaMemcpy(ds.data(), m.ds + (size_t)row0 * nb, ds.size() * 2, cudaMemcpyDeviceToHost));
+    for (int r = 0; r < nrows; r++)
+        for (int k = 0; k < K; k++) {
+            float v;
+            if (m.fmt == FMT_F16) {
+                v = __half2float(__ushort_as_half(reinterpret_cast<unsigned short*>(qs.data())[(size_t)r * K + k]));
+            } else {
+                const float d = __half2float(__ushort_as_half(ds[(size_t)r * nb + k / 32]));
+                if (m.fmt == FMT_Q8_0) {
+                    v = d * (float)reinterpret_cast<int8_t*>(qs.data())[(size_t)r * K + k];
+                } else {
+                    const int b = k / 32, j = k % 32;
+                    const uint8_t byte = qs[(size_t)r * (K / 2) + b * 16 + (j & 15)];
+                    v = d * (float)((j < 16 ? (byte & 0xF) : (byte >> 4)) - 8);
+                }
+            }
+            out[(size_t)r * K + k] = v;
+        }
+    return MG_OK;
+}
+
+int mg_read_kv(mg_engine* e, int layer, int pos0, int npos, uint16_t* k_out, uint16_t* v_out) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    const mg_config& c = e->cfg;
+    if (layer < 0 || layer >= c.n_layers || pos0 < 0 || npos < 0 || pos0 + npos > c.max_seq)
+        return fail(e, MG_ERR_ARG, "mg_read_kv: out of range");
+    const size_t off = ((size_t)layer * c.max_seq + pos0) * c.kv_dim;
+    const size_t bytes = (size_t)npos * c.kv_dim * 2;
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    if (k_out) MG_CUDA(e, cudaMemcpy(k_out, e->kc + off, bytes, cudaMemcpyDeviceToHost));
+    if (v_out) MG_CUDA(e, cudaMemcpy(v_out, e->vc + off, bytes, cudaMemcpyDeviceToHost));
+    return MG_OK;
+}
+
+cudaStream_t mg_stream(mg_engine* e) { return e ? e->stream : nullptr; }
+long long mg_launch_count(const mg_engine* e) { return e ? e->launches : 0; }
+size_t mg_device_bytes(const mg_engine* e) { return e ? e->dev_bytes : 0; }
+const char* mg_last_error(const mg_engine* e) { return e ? e->err.c_str() : "null engine"; }
+
+}  // extern "C"

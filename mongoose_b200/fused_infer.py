@@ -1,0 +1,150 @@
+"""``CUDAFusedInference``: the reference's fused decode engine
+(cuda_fused_infer.go:75-459, cuda_fused_infer_q4.go:46-266) as a thin Python
+class over the ``mg_*`` C ABI.  Method names and argument meaning follow the
+Go type; all arithmetic runs in libmongoose_kernels.so on the GPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from .configs import ModelConfig
+
+
+class MongooseError(RuntimeError):
+    pass
+
+
+def _np_ptr(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+class CUDAFusedInference:
+    def __init__(self, cfg: ModelConfig, device: int = 0):
+        """NewCUDAFusedInference (cuda_fused_infer.go:144)."""
+        self.cfg = cfg
+        self._lib = _lib.load()
+        c = _lib.MgConfig(dim=cfg.dim, kv_dim=cfg.kv_dim, head_dim=cfg.head_dim, n_heads=cfg.n_heads,
+                          n_kv_heads=cfg.n_kv_heads, ffn_dim=cfg.ffn_dim, vocab=cfg.vocab,
+                          n_layers=cfg.n_layers, max_seq=cfg.max_seq, rope_theta=float(cfg.rope_theta),
+                          rms_eps=float(cfg.eps), layer_fmt=cfg.layer_fmt, head_fmt=cfg.head_fmt,
+                          device=device, max_batch=1, flags=0)
+        h = C.c_void_p()
+        rc = self._lib.mg_create(C.byref(c), C.byref(h))
+        if rc != 0 or not h.value:
+            raise MongooseError(f"mg_create failed with status {rc} (is a B200 visible as device {device}?)")
+        self._h = h
+
+    # -- lifetime ---------------------------------------------------------
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.mg_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    def _check(self, rc: int, what: str):
+        if rc != 0:
+            raise MongooseError(f"{what}: status {rc}: {self._lib.mg_last_error(self._h).decode()}")
+
+    # -- weights ----------------------------------------------------------
+    def NumWeights(self) -> int:
+        return self._lib.mg_num_weights(self._h)
+
+    def SetWeight(self, idx: int, data) -> None:
+        """fp32 tensor for slot idx = layer*12 + w; matrices are quantized on the
+        host to the slot's format (cuda_fused_infer.go:241-272)."""
+        a = np.ascontiguousarray(data, dtype=np.float32)
+        self._check(self._lib.mg_set_weight(self._h, idx, _np_ptr(a), a.size), f"SetWeight({idx})")
+
+    def SetWeightRaw(self, idx: int, blocks, fmt: int) -> None:
+        """Raw quantized blocks for a matrix slot (SetWeightQ4_0, cuda_fused_infer_q4.go:46-90)."""
+        a = np.ascontiguousarray(blocks).view(np.uint8)
+        self._check(self._lib.mg_set_weight_raw(self._h, idx, _np_ptr(a), a.size, fmt), f"SetWeightRaw({idx})")
+
+    def SetWeightQ4_0(self, idx: int, blocks) -> None:
+        from .configs import FMT_Q4_0
+        self.SetWeightRaw(idx, blocks, FMT_Q4_0)
+
+    def BuildFusedDispatch(self) -> None:
+        self._check(self._lib.mg_build(self._h), "BuildFusedDispatch")
+
+    def ResetKV(self) -> None:
+        self._check(self._lib.mg_reset_kv(self._h), "ResetKV")
+
+    # -- stepping ---------------------------------------------------------
+    def PartialStep(self, hiddenIn, pos: int, layerStart: int, layerEnd: int, hiddenOut=None,
+                    logitsOut=None) -> int:
+        """hiddenIn/hiddenOut/logitsOut are host float32 arrays (numpy, or pinned torch CPU
+        tensors); returns 0 like the reference (cuda_fused_infer.go:392-459)."""
+        rc = self._lib.mg_partial_step(self._h, _host_ptr(hiddenIn), pos, layerStart, layerEnd,
+                                       _host_ptr(hiddenOut), _host_ptr(logitsOut))
+        self._check(rc, "PartialStep")
+        return 0
+
+    def ExportHidden(self) -> np.ndarray:
+        out = np.empty(self.cfg.dim, np.float32)
+        self._check(self._lib.mg_export_hidden(self._h, _np_ptr(out)), "ExportHidden")
+        return out
+
+    def StepToken(self, token: int, pos: int, logitsOut=None) -> int:
+        """Greedy step with the tied embedding; returns the argmax token."""
+        nxt = C.c_int(-1)
+        rc = self._lib.mg_step_token(self._h, int(token), pos, C.byref(nxt), _host_ptr(logitsOut))
+        self._check(rc, "StepToken")
+        return nxt.value
+
+    def Generate(self, prompt, n_new: int, start_pos: int = 0) -> np.ndarray:
+        p = np.ascontiguousarray(prompt, dtype=np.int32)
+        out = np.empty(n_new, np.int32)
+        rc = self._lib.mg_generate(self._h, _np_ptr(p), p.size, n_new, start_pos, _np_ptr(out))
+        self._check(rc, "Generate")
+        return out
+
+    def SetCursor(self, token: int, pos: int) -> None:
+        self._check(self._lib.mg_set_cursor(self._h, int(token), pos), "SetCursor")
+
+    def GetCursor(self):
+        t, p = C.c_int(), C.c_int()
+        self._check(self._lib.mg_get_cursor(self._h, C.byref(t), C.byref(p)), "GetCursor")
+        return t.value, p.value
+
+    def EnqueueGreedy(self, n_steps: int) -> None:
+        self._check(self._lib.mg_enqueue_greedy(self._h, n_steps), "EnqueueGreedy")
+
+    def Sync(self) -> None:
+        self._check(self._lib.mg_sync(self._h), "Sync")
+
+    # -- introspection ----------------------------------------------------
+    def DequantRows(self, idx: int, row0: int, nrows: int, cols: int) -> np.ndarray:
+        out = np.empty((nrows, cols), np.float32)
+        self._check(self._lib.mg_dequant_rows(self._h, idx, row0, nrows, _np_ptr(out)), "DequantRows")
+        return out
+
+    def ReadKV(self, layer: int, pos0: int, npos: int):
+        k = np.empty((npos, self.cfg.kv_dim), np.uint16)
+        v = np.empty((npos, self.cfg.kv_dim), np.uint16)
+        self._check(self._lib.mg_read_kv(self._h, layer, pos0, npos, _np_ptr(k), _np_ptr(v)), "ReadKV")
+        return k, v
+
+    @property
+    def stream(self) -> int:
+        return self._lib.mg_stream(self._h) or 0
+
+    def LaunchCount(self) -> int:
+        return int(self._lib.mg_launch_count(self._h))
+
+    def DeviceBytes(self) -> int:
+        return int(self._lib.mg_device_bytes(self._h))
+
+
+def _host_ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, np.ndarray):
+        assert x.dtype == np.float32 and x.flags["C_CONTIGUOUS"]
+        return _np_ptr(x)
+    return C.c_void_p(x.data_ptr())   # torch CPU tensor (pinned or not)
