@@ -55,7 +55,9 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="qwen2.5-0.5b-q8_0-b1", choices=sorted(WORKLOADS))
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--cpu-steps", type=int, default=0, help="steps of the CPU baseline sample (0 = auto)")
     return ap.parse_args()
 
@@ -238,24 +240,26 @@ def run_b200_arm(args, cfg, rank, world, local_rank):
     # ---- e2e: PartialStep with pinned host buffers (hidden in, logits out) ----
     # The token sequence is the one just generated, so no host-side sampling sits in the timed loop;
     # the caller-side embedding rows (dequantized lm_head rows) are prepared beforehand.
+    e2e_s, e2e_last_tok = float("nan"), -1
     gen_tokens = eng.Generate(prompt, K)                # g0 .. g(K-1): the inputs of the K decode steps
-    seq = np.concatenate([prompt, gen_tokens])
-    head_idx = cfg.n_layers * 12 + 1
-    hid = torch.empty((len(seq), cfg.dim), dtype=torch.float32).pin_memory()
-    for i, t in enumerate(seq):
-        hid[i] = torch.from_numpy(eng.DequantRows(head_idx, int(t), 1, cfg.dim)[0])
-    logits_host = torch.empty(cfg.vocab, dtype=torch.float32).pin_memory()
-    eng.ResetKV()
-    for i in range(PROMPT_LEN):
-        eng.PartialStep(hid[i], i, 0, cfg.n_layers, None, logits_host)
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(PROMPT_LEN, PROMPT_LEN + K):
-        eng.PartialStep(hid[i], i, 0, cfg.n_layers, None, logits_host)
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    e2e_last_tok = int(torch.argmax(logits_host))
-    barrier()
+    if not args.no_e2e:
+        seq = np.concatenate([prompt, gen_tokens])
+        head_idx = cfg.n_layers * 12 + 1
+        hid = torch.empty((len(seq), cfg.dim), dtype=torch.float32).pin_memory()
+        for i, t in enumerate(seq):
+            hid[i] = torch.from_numpy(eng.DequantRows(head_idx, int(t), 1, cfg.dim)[0])
+        logits_host = torch.empty(cfg.vocab, dtype=torch.float32).pin_memory()
+        eng.ResetKV()
+        for i in range(PROMPT_LEN):
+            eng.PartialStep(hid[i], i, 0, cfg.n_layers, None, logits_host)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(PROMPT_LEN, PROMPT_LEN + K):
+            eng.PartialStep(hid[i], i, 0, cfg.n_layers, None, logits_host)
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        e2e_last_tok = int(torch.argmax(logits_host))
+        barrier()
 
     # max over ranks
     tms = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
@@ -302,7 +306,9 @@ def run_b200_arm(args, cfg, rank, world, local_rank):
 
 
 def main():
+    global PROMPT_LEN
     args = parse_args()
+    PROMPT_LEN = args.prompt_len
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -399,8 +399,8 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
     extern __shared__ __align__(16) float smem[];
     float* qs = smem;                  // HD
     float* red = smem + HD;            // 40
-    float* part = red + 40;            // 8 * HD  (cross-group partial outputs)
-    float* sc = part + 8 * HD;         // cache_len scores
+    float* part = red + 40;            // 512: one partial per thread pair component (G groups x HD dims)
+    float* sc = part + 512;            // cache_len scores
 
     pdl_launch_dependents();
     pdl_wait();
@@ -462,7 +462,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
 
     // weighted sum of V: thread = (group g, dim pair dp)
     constexpr int DP = HD / 2;                 // dim pairs
-    const int G = blockDim.x / DP;             // position groups (<= 8)
+    const int G = blockDim.x / DP;             // position groups; G * HD = 2 * blockDim = 512
     const int g = tid / DP, dp = tid % DP;
     float2 o = make_float2(0.f, 0.f);
     if (g < G) {

@@ -347,7 +347,7 @@ int enqueue_step(mg_engine* e, cudaStream_t s, int ls, int le, int mode, int hea
             if (rc) return rc;
         }
         {   // attention
-            const size_t smem = ((size_t)c.head_dim * 9 + 40 + c.max_seq) * sizeof(float);
+            const size_t smem = ((size_t)c.head_dim + 40 + 512 + c.max_seq) * sizeof(float);
             if (smem > (size_t)kMaxDynSmem) return fail(e, MG_ERR_UNSUPPORTED, "max_seq %d too large", c.max_seq);
             cudaError_t ce;
             if (c.head_dim == 64)
