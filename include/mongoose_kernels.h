@@ -145,7 +145,8 @@ enum {
     MG_ERR_STATE = -2,       /* call out of order (e.g. step before every weight is set) */
     MG_ERR_CUDA = -3,        /* a CUDA call failed; mg_last_error has the text */
     MG_ERR_NOMEM = -4,
-    MG_ERR_UNSUPPORTED = -5
+    MG_ERR_UNSUPPORTED = -5,
+    MG_ERR_TIMEOUT = -6      /* a bounded device-side wait expired; the context stays usable */
 };
 
 /* Weight storage formats. */
@@ -215,6 +216,13 @@ MG_API int mg_sync(mg_engine* e);
 MG_API int mg_dequant_rows(mg_engine* e, int idx, int row0, int nrows, float* out);
 /* Debug/parity: copy fp16 K and V rows [pos0, pos0+npos) of a layer to HOST (uint16 bit patterns). */
 MG_API int mg_read_kv(mg_engine* e, int layer, int pos0, int npos, uint16_t* k_out, uint16_t* v_out);
+/* Per-phase timeline of ONE greedy step from the current cursor (the counterpart of the reference's
+ * per-op [PROFILE] timing at pos 1, cuda_fused_infer_q4.go:147-242).  stamps receives
+ * [n_ctas][n_events] SM clock values of each CTA's first thread: per layer, ten stamps (layer start,
+ * after the QKV input stage, after QKV, before/after attention, wo input ready, after wo, gate/up input
+ * ready, after gate/up, down input ready -> after down), then two for lm_head.  Needs the persistent
+ * kernel; capacity is in stamps. */
+MG_API int mg_trace_step(mg_engine* e, long long* stamps, int capacity, int* n_ctas, int* n_events);
 /* The stream the engine enqueues on (for event timing by the caller). */
 MG_API cudaStream_t mg_stream(mg_engine* e);
 /* Kernels launched by this engine since creation (graph replays count their kernel nodes). */

@@ -71,6 +71,7 @@ SIGNATURES = {
     "mg_sync": (ci, [vp]),
     "mg_dequant_rows": (ci, [vp, ci, ci, ci, vp]),
     "mg_read_kv": (ci, [vp, ci, ci, ci, vp, vp]),
+    "mg_trace_step": (ci, [vp, vp, ci, vp, vp]),
     "mg_stream": (vp, [vp]),
     "mg_launch_count": (C.c_longlong, [vp]),
     "mg_device_bytes": (sz, [vp]),

@@ -21,7 +21,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB_NAME = "libmongoose_kernels.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
 SOURCES = ["legacy_ops.cu", "block_ops.cu", "engine.cu"]
-HEADERS = ["mg_common.cuh", "decode_kernels.cuh"]
+HEADERS = ["mg_common.cuh", "decode_kernels.cuh", "mega_kernel.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -29,7 +29,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-ffp-contract=off",
     "--expt-relaxed-constexpr",
     "-Xptxas", "-v",
-]
+] + (["-DMK_DEBUG_TRACE"] if os.environ.get("MK_DEBUG_TRACE") == "1" else [])
 
 
 def _nvcc() -> str:

@@ -12,6 +12,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -22,6 +23,7 @@
 
 #include "../../include/mongoose_kernels.h"
 #include "decode_kernels.cuh"
+#include "mega_kernel.cuh"
 
 using namespace mg;
 
@@ -68,6 +70,21 @@ struct mg_engine {
     int* pin_i = nullptr;               // [0..3] cursor, [4..] prompt ids
     int pin_i_cap = 0;
     std::map<GraphKey, CachedGraph> graphs;
+    // persistent-kernel path (mega_kernel.cuh)
+    bool use_mega = true;               // allowed by the environment
+    bool mega_ok = false;               // built and usable for this model
+    uint8_t* tape = nullptr;
+    unsigned long long* tape_off = nullptr;
+    const float** ptr_tab = nullptr;    // device: 5 arrays of n_layers pointers (norm1, norm2, bq, bk, bv)
+    Tagged* xbuf = nullptr;             // exchange buffers, one allocation
+    MegaStatus* mk_status = nullptr;
+    long long* mk_trace = nullptr;      // per-phase clock stamps of the next launch (mg_trace_step)
+    bool trace_next = false;
+    float* h_in = nullptr;              // hidden-state input of PartialStep on the persistent path
+    unsigned int epoch = 16;
+    int mk_nslot = 0, mk_xs = 0, mk_sc = 0;
+    size_t mk_smem = 0;
+    size_t tape_bytes = 0;
     bool built = false;
     bool use_graph = true;
     bool use_pdl = true;
@@ -413,7 +430,227 @@ int enqueue_step(mg_engine* e, cudaStream_t s, int ls, int le, int mode, int hea
     return MG_OK;
 }
 
+
+// ------------------------------------------------------------------
+// Persistent-kernel path: tape construction and launch
+// ------------------------------------------------------------------
+void free_mega(mg_engine* e) {
+    auto drop = [&](void* p, size_t bytes) { if (p) { cudaFree(p); e->dev_bytes -= bytes; } };
+    drop(e->tape, e->tape_bytes); e->tape = nullptr; e->tape_bytes = 0;
+    if (e->tape_off) { cudaFree(e->tape_off); e->tape_off = nullptr; }
+    if (e->ptr_tab) { cudaFree(e->ptr_tab); e->ptr_tab = nullptr; }
+    if (e->xbuf) { cudaFree(e->xbuf); e->xbuf = nullptr; }
+    if (e->mk_status) { cudaFree(e->mk_status); e->mk_status = nullptr; }
+    if (e->mk_trace) { cudaFree(e->mk_trace); e->mk_trace = nullptr; }
+    if (e->h_in) { cudaFree(e->h_in); e->h_in = nullptr; }
+    e->mega_ok = false;
+}
+
+// Matrix slots that feed phase p of layer l, in the order the phase's items name them.
+void phase_matrices(const mg_config& c, int l, int p, int out[3], int* n) {
+    const int b = l * 12;
+    switch (p) {
+        case PH_QKV: out[0] = b + 1; out[1] = b + 2; out[2] = b + 3; *n = 3; break;
+        case PH_WO: out[0] = b + 7; *n = 1; break;
+        case PH_GU: out[0] = b + 9; out[1] = b + 10; *n = 2; break;
+        case PH_DOWN: out[0] = b + 11; *n = 1; break;
+        default: out[0] = c.n_layers * 12 + 1; *n = 1; break;
+    }
+}
+
+// Rows (matrix ordinal within the phase, row) of work item `item`, in tape order.
+inline int item_rows(const mg_config& c, int p, int item, int m_out[2], int r_out[2]) {
+    if (p == PH_QKV) {
+        int m, r0, r1;
+        qkv_pair(item, c.dim, c.kv_dim, c.head_dim, &m, &r0, &r1);
+        m_out[0] = m_out[1] = m; r_out[0] = r0; r_out[1] = r1;
+        return 2;
+    }
+    if (p == PH_GU) { m_out[0] = 0; m_out[1] = 1; r_out[0] = r_out[1] = item; return 2; }
+    m_out[0] = 0; r_out[0] = item;
+    return 1;
+}
+
+// Decide whether the persistent kernel can run this model and with how many ring slots.
+bool mega_feasible(mg_engine* e, std::string* why) {
+    const mg_config& c = e->cfg;
+    const int G = e->num_sms;
+    int coop = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, c.device);
+    if (!coop) { *why = "cooperative launch unsupported"; return false; }
+    if (c.n_heads > G) { *why = "more query heads than SMs"; return false; }
+    if (c.max_seq > 16384) { *why = "max_seq too large for the score buffer"; return false; }
+    for (int p = 0; p <= PH_HEAD; p++) {
+        const PhaseShape s = phase_shape_of(p, c.dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
+        if (rows_per_entry(s.fmt, s.K) < 2) { *why = "a weight row does not fit a ring slot"; return false; }
+        if ((s.K + 1023) / 1024 > MK_NW) { *why = "input dim needs more K segments than consumer warps"; return false; }
+    }
+    int xs = c.dim > c.ffn_dim ? c.dim : c.ffn_dim;
+    if (xs < 3 * c.head_dim) xs = 3 * c.head_dim;
+    xs = (xs + 3) & ~3;
+    const int sc = (c.max_seq + 3) & ~3;
+    int dev_max = 0;
+    cudaDeviceGetAttribute(&dev_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, c.device);
+    int nslot = MK_MAX_SLOTS;
+    while (nslot >= 4 && mk_smem_bytes(nslot, xs, c.dim, sc) > (size_t)dev_max) nslot--;
+    if (nslot < 4) { *why = "activations leave no room for the weight ring in shared memory"; return false; }
+    e->mk_nslot = nslot; e->mk_xs = xs; e->mk_sc = sc;
+    e->mk_smem = mk_smem_bytes(nslot, xs, c.dim, sc);
+    return true;
+}
+
+int build_mega(mg_engine* e) {
+    free_mega(e);
+    if (!e->use_mega) return MG_OK;
+    std::string why;
+    if (!mega_feasible(e, &why)) {
+        e->err = "persistent kernel not used: " + why;
+        return MG_OK;
+    }
+    const mg_config& c = e->cfg;
+    const int G = e->num_sms, L = c.n_layers;
+    const int ncol = L * 4 + 2;
+    std::vector<unsigned long long> off((size_t)G * ncol);
+    unsigned long long total = 0;
+    auto phase_bytes = [&](int p, int cta) {
+        const PhaseShape s = phase_shape_of(p, c.dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
+        const int nrows = (item_begin(s.items, cta + 1, G) - item_begin(s.items, cta, G)) * s.rpi;
+        const int rpe = rows_per_entry(s.fmt, s.K);
+        unsigned long long b = 0;
+        for (int r = 0; r < nrows; r += rpe) b += entry_bytes(s.fmt, s.K, std::min(rpe, nrows - r));
+        return b;
+    };
+    for (int cta = 0; cta < G; cta++) {
+        for (int l = 0; l < L; l++)
+            for (int p = 0; p < 4; p++) { off[(size_t)cta * ncol + l * 4 + p] = total; total += phase_bytes(p, cta); }
+        off[(size_t)cta * ncol + L * 4] = total; total += phase_bytes(PH_HEAD, cta);
+        off[(size_t)cta * ncol + L * 4 + 1] = total;
+    }
+    std::vector<uint8_t> tape((size_t)total + MK_SLOT, 0);
+
+    // fill: one (layer, phase) at a time so that only that phase's matrices are on the host
+    std::vector<uint8_t> hq[3];
+    std::vector<unsigned short> hd[3];
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    for (int l = 0; l <= L; l++)
+        for (int p = (l < L ? 0 : PH_HEAD); p <= (l < L ? 3 : PH_HEAD); p++) {
+            int slots[3], nm = 0;
+            phase_matrices(c, l, p, slots, &nm);
+            const PhaseShape s = phase_shape_of(p, c.dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
+            const int rq = row_q_bytes(s.fmt, s.K), rd = row_d_bytes(s.fmt, s.K);
+            for (int m = 0; m < nm; m++) {
+                const DevMatrix& M = e->mats[slots[m]];
+                hq[m].resize((size_t)M.rows * rq);
+                MG_CUDA(e, cudaMemcpy(hq[m].data(), M.qs, hq[m].size(), cudaMemcpyDeviceToHost));
+                hd[m].resize(rd ? (size_t)M.rows * (s.K / 32) : 0);
+                if (rd) MG_CUDA(e, cudaMemcpy(hd[m].data(), M.ds, hd[m].size() * 2, cudaMemcpyDeviceToHost));
+            }
+            const int rpe = rows_per_entry(s.fmt, s.K);
+            const int col = l < L ? l * 4 + p : L * 4;
+            for (int cta = 0; cta < G; cta++) {
+                const int ib = item_begin(s.items, cta, G), ie = item_begin(s.items, cta + 1, G);
+                const int nrows = (ie - ib) * s.rpi;
+                uint8_t* dst = tape.data() + off[(size_t)cta * ncol + col];
+                for (int r = 0; r < nrows; r += rpe) {
+                    const int nr = std::min(rpe, nrows - r);
+                    for (int i = 0; i < nr; i++) {
+                        const int item = ib + (r + i) / s.rpi;
+                        int mm[2], rr[2];
+                        item_rows(c, p, item, mm, rr);
+                        const int k = (r + i) % s.rpi;
+                        memcpy(dst + (size_t)i * rq, hq[mm[k]].data() + (size_t)rr[k] * rq, rq);
+                        if (rd)
+                            memcpy(dst + (size_t)nr * rq + (size_t)i * rd,
+                                   reinterpret_cast<const uint8_t*>(hd[mm[k]].data()) + (size_t)rr[k] * rd, rd);
+                    }
+                    dst += entry_bytes(s.fmt, s.K, nr);
+                }
+            }
+        }
+    for (int m = 0; m < 3; m++) { hq[m] = {}; hd[m] = {}; }
+
+    int rc;
+    e->tape_bytes = tape.size();
+    if ((rc = dev_alloc(e, &e->tape, tape.size()))) { e->tape_bytes = 0; return rc; }
+    MG_CUDA(e, cudaMemcpy(e->tape, tape.data(), tape.size(), cudaMemcpyHostToDevice));
+    tape = {};
+    MG_CUDA(e, cudaMalloc((void**)&e->tape_off, off.size() * 8));
+    MG_CUDA(e, cudaMemcpy(e->tape_off, off.data(), off.size() * 8, cudaMemcpyHostToDevice));
+    std::vector<const float*> tab((size_t)5 * L);
+    for (int l = 0; l < L; l++) {
+        tab[0 * L + l] = e->vecs[l * 12 + 0];
+        tab[1 * L + l] = e->vecs[l * 12 + 8];
+        tab[2 * L + l] = e->vecs[l * 12 + 4];
+        tab[3 * L + l] = e->vecs[l * 12 + 5];
+        tab[4 * L + l] = e->vecs[l * 12 + 6];
+    }
+    MG_CUDA(e, cudaMalloc((void**)&e->ptr_tab, tab.size() * sizeof(float*)));
+    MG_CUDA(e, cudaMemcpy(e->ptr_tab, tab.data(), tab.size() * sizeof(float*), cudaMemcpyHostToDevice));
+    const size_t nx = (size_t)3 * c.dim + 2 * c.kv_dim + c.dim + c.ffn_dim + 2;   // xh xhm xq | xkv | xattn | xmid | xtok
+    MG_CUDA(e, cudaMalloc((void**)&e->xbuf, nx * sizeof(Tagged)));
+    MG_CUDA(e, cudaMemset(e->xbuf, 0, nx * sizeof(Tagged)));
+    MG_CUDA(e, cudaMalloc((void**)&e->mk_status, sizeof(MegaStatus)));
+    MG_CUDA(e, cudaMemset(e->mk_status, 0, sizeof(MegaStatus)));
+    MG_CUDA(e, cudaFuncSetAttribute((const void*)mega_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)e->mk_smem));
+    int per_sm = 0;
+    MG_CUDA(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mega_decode_kernel, MK_THREADS, e->mk_smem));
+    if (per_sm < 1) {
+        free_mega(e);
+        e->err = "persistent kernel not used: one CTA does not fit an SM";
+        return MG_OK;
+    }
+    e->mega_ok = true;
+    return MG_OK;
+}
+
+// One launch of the persistent kernel: n_steps tokens through layers [ls, le).
+int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
+    const mg_config& c = e->cfg;
+    const int L = c.n_layers;
+    MegaArgs a{};
+    a.dim = c.dim; a.kv_dim = c.kv_dim; a.head_dim = c.head_dim; a.n_heads = c.n_heads; a.n_kv_heads = c.n_kv_heads;
+    a.ffn_dim = c.ffn_dim; a.vocab = c.vocab; a.n_layers = L; a.max_seq = c.max_seq;
+    a.layer_fmt = c.layer_fmt; a.head_fmt = c.head_fmt; a.eps = c.rms_eps;
+    a.ls = ls; a.le = le; a.head = (le >= L) ? head : 0; a.embed = (mode == MODE_EMBED); a.n_steps = n_steps;
+    a.epoch = e->epoch;
+    e->epoch += (unsigned)n_steps * (unsigned)(L * MK_EPOCHS_PER_LAYER + 8);
+    a.hd_shift = c.head_dim == 32 ? 5 : c.head_dim == 64 ? 6 : 7;
+    a.nslot = e->mk_nslot; a.xs_floats = e->mk_xs; a.sc_floats = e->mk_sc;
+    a.tape = e->tape; a.tape_off = e->tape_off;
+    a.norm1 = e->ptr_tab; a.norm2 = e->ptr_tab + L; a.bq = e->ptr_tab + 2 * L; a.bk = e->ptr_tab + 3 * L;
+    a.bv = e->ptr_tab + 4 * L;
+    a.final_norm = e->vecs[L * 12];
+    a.embed_w = e->mats[L * 12 + 1].view();
+    a.cos_tab = e->cos_tab; a.sin_tab = e->sin_tab; a.kc = e->kc; a.vc = e->vc;
+    Tagged* x = e->xbuf;
+    a.xh = x; x += c.dim; a.xhm = x; x += c.dim; a.xq = x; x += c.dim; a.xkv = x; x += 2 * c.kv_dim;
+    a.xattn = x; x += c.dim; a.xmid = x; x += c.ffn_dim; a.xtok = x;
+    a.h_in = e->h; a.h_out = e->h; a.logits = e->logits; a.st = e->st; a.out_tokens = e->out_tokens;
+    a.status = e->mk_status;
+    a.trace = e->trace_next ? e->mk_trace : nullptr;
+    e->trace_next = false;
+    void* params[] = {&a};
+    MG_CUDA(e, cudaLaunchCooperativeKernel((const void*)mega_decode_kernel, dim3(e->num_sms), dim3(MK_THREADS), params,
+                                           e->mk_smem, e->stream));
+    e->launches += 1;
+    return MG_OK;
+}
+
+// After a synchronisation: did any wait inside the persistent kernel give up?
+int check_mega_status(mg_engine* e) {
+    if (!e->mega_ok) return MG_OK;
+    MegaStatus s{};
+    MG_CUDA(e, cudaMemcpy(&s, e->mk_status, sizeof s, cudaMemcpyDeviceToHost));
+    if (s.error) {
+        cudaMemset(e->mk_status, 0, sizeof s);
+        return fail(e, MG_ERR_TIMEOUT, "persistent kernel: wait %d timed out (where %d, CTA %d)", s.error, s.where, s.cta);
+    }
+    return MG_OK;
+}
+
 int run_step(mg_engine* e, int ls, int le, int mode, int head) {
+    if (e->mega_ok && le > ls) return launch_mega(e, ls, le, mode, head, 1);
     if (!e->use_graph) {
         int rc = enqueue_step(e, e->stream, ls, le, mode, head);
         e->launches += e->capture_kernels;
@@ -546,6 +783,8 @@ int mg_create(const mg_config* cfg, mg_engine** out) {
     if ((rc = set_kernel_attrs(e))) return bail(rc);
     const char* env = getenv("MG_NO_GRAPH");
     if (env && env[0] == '1') e->use_graph = false;
+    env = getenv("MG_NO_MEGA");
+    if (env && env[0] == '1') e->use_mega = false;
     env = getenv("MG_NO_PDL");
     if (env && env[0] == '1') e->use_pdl = false;
     *out = e;
@@ -557,6 +796,7 @@ void mg_destroy(mg_engine* e) {
     cudaSetDevice(e->cfg.device);
     if (e->stream) cudaStreamSynchronize(e->stream);
     drop_graphs(e);
+    free_mega(e);
     for (auto& m : e->mats) {
         if (m.qs) cudaFree(m.qs);
         if (m.ds) cudaFree(m.ds);
@@ -623,6 +863,7 @@ int mg_build(mg_engine* e) {
             return fail(e, MG_ERR_STATE, "mg_build: weight slot %d has not been set", idx);
     }
     drop_graphs(e);
+    if ((rc = build_mega(e))) return rc;
     e->built = true;
     return MG_OK;
 }
@@ -656,14 +897,14 @@ int mg_get_cursor(mg_engine* e, int* token, int* pos) {
     MG_CUDA(e, cudaStreamSynchronize(e->stream));
     if (token) *token = s.token;
     if (pos) *pos = s.pos;
-    return MG_OK;
+    return check_mega_status(e);
 }
 
 int mg_sync(mg_engine* e) {
     int rc = check_engine(e);
     if (rc) return rc;
     MG_CUDA(e, cudaStreamSynchronize(e->stream));
-    return MG_OK;
+    return check_mega_status(e);
 }
 
 int mg_partial_step(mg_engine* e, const float* hidden_in, int pos, int layer_start, int layer_end,
@@ -686,7 +927,7 @@ int mg_partial_step(mg_engine* e, const float* hidden_in, int pos, int layer_sta
     else if (hidden_out)
         MG_CUDA(e, cudaMemcpyAsync(hidden_out, e->h, (size_t)c.dim * 4, cudaMemcpyDeviceToHost, e->stream));
     MG_CUDA(e, cudaStreamSynchronize(e->stream));
-    return MG_OK;
+    return check_mega_status(e);
 }
 
 int mg_export_hidden(mg_engine* e, float* hidden_out) {
@@ -714,13 +955,15 @@ int mg_step_token(mg_engine* e, int token, int pos, int* next_token, float* logi
     MG_CUDA(e, cudaMemcpyAsync(e->pin_i + 4, &e->st->token, 4, cudaMemcpyDeviceToHost, e->stream));
     MG_CUDA(e, cudaStreamSynchronize(e->stream));
     if (next_token) *next_token = e->pin_i[4];
-    return MG_OK;
+    return check_mega_status(e);
 }
 
 int mg_enqueue_greedy(mg_engine* e, int n_steps) {
     int rc = check_engine(e);
     if (rc) return rc;
     if ((rc = ensure_built(e))) return rc;
+    if (n_steps <= 0) return MG_OK;
+    if (e->mega_ok) return launch_mega(e, 0, e->cfg.n_layers, MODE_EMBED, HEAD_ARGMAX, n_steps);
     for (int i = 0; i < n_steps; i++)
         if ((rc = run_step(e, 0, e->cfg.n_layers, MODE_EMBED, HEAD_ARGMAX))) return rc;
     return MG_OK;
@@ -742,15 +985,23 @@ int mg_generate(mg_engine* e, const int* prompt, int n_prompt, int n_new, int st
     for (int i = 0; i < n_prompt; i++) e->pin_i[8 + i] = prompt[i];
     MG_CUDA(e, cudaMemcpyAsync(e->st, e->pin_i, 12, cudaMemcpyHostToDevice, e->stream));
     const int total = n_prompt + n_new - 1;
-    for (int i = 0; i < total; i++) {
-        if (i > 0 && i < n_prompt)   // prompt tokens override the fed-back argmax
+    for (int i = 0; i < n_prompt; i++) {
+        if (i > 0)   // prompt tokens override the fed-back argmax
             MG_CUDA(e, cudaMemcpyAsync(&e->st->token, e->pin_i + 8 + i, 4, cudaMemcpyHostToDevice, e->stream));
         if ((rc = run_step(e, 0, c.n_layers, MODE_EMBED, HEAD_ARGMAX))) return rc;
+    }
+    if (total > n_prompt) {
+        if (e->mega_ok) {
+            if ((rc = launch_mega(e, 0, c.n_layers, MODE_EMBED, HEAD_ARGMAX, total - n_prompt))) return rc;
+        } else {
+            for (int i = n_prompt; i < total; i++)
+                if ((rc = run_step(e, 0, c.n_layers, MODE_EMBED, HEAD_ARGMAX))) return rc;
+        }
     }
     MG_CUDA(e, cudaMemcpyAsync(out_tokens, e->out_tokens + (n_prompt - 1), (size_t)n_new * 4, cudaMemcpyDeviceToHost,
                                e->stream));
     MG_CUDA(e, cudaStreamSynchronize(e->stream));
-    return MG_OK;
+    return check_mega_status(e);
 }
 
 int mg_dequant_rows(mg_engine* e, int idx, int row0, int nrows, float* out) {
@@ -798,6 +1049,24 @@ int mg_read_kv(mg_engine* e, int layer, int pos0, int npos, uint16_t* k_out, uin
     if (k_out) MG_CUDA(e, cudaMemcpy(k_out, e->kc + off, bytes, cudaMemcpyDeviceToHost));
     if (v_out) MG_CUDA(e, cudaMemcpy(v_out, e->vc + off, bytes, cudaMemcpyDeviceToHost));
     return MG_OK;
+}
+
+int mg_trace_step(mg_engine* e, long long* stamps, int capacity, int* n_ctas, int* n_events) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if ((rc = ensure_built(e))) return rc;
+    if (!e->mega_ok) return fail(e, MG_ERR_UNSUPPORTED, "mg_trace_step: the persistent kernel is not in use (%s)", e->err.c_str());
+    const int ev = MK_TRACE_EVENTS(e->cfg.n_layers), G = e->num_sms;
+    if (!stamps || capacity < G * ev) return fail(e, MG_ERR_ARG, "mg_trace_step: need room for %d stamps", G * ev);
+    if (!e->mk_trace) MG_CUDA(e, cudaMalloc((void**)&e->mk_trace, (size_t)G * ev * 8));
+    MG_CUDA(e, cudaMemsetAsync(e->mk_trace, 0, (size_t)G * ev * 8, e->stream));
+    e->trace_next = true;
+    if ((rc = launch_mega(e, 0, e->cfg.n_layers, MODE_EMBED, HEAD_ARGMAX, 1))) return rc;
+    MG_CUDA(e, cudaMemcpyAsync(stamps, e->mk_trace, (size_t)G * ev * 8, cudaMemcpyDeviceToHost, e->stream));
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    if (n_ctas) *n_ctas = G;
+    if (n_events) *n_events = ev;
+    return check_mega_status(e);
 }
 
 cudaStream_t mg_stream(mg_engine* e) { return e ? e->stream : nullptr; }

@@ -1,0 +1,1014 @@
+// Persistent decode kernel: every layer of a token (and, in the greedy loop,
+// many tokens) in ONE cooperative launch, one CTA per SM.
+//
+// Why: at 0.5 B parameters a layer is ~16 MB of Q8_0 weights, about 2.4 us of
+// HBM time, split over five dependent matvec phases.  A kernel boundary costs
+// more than a phase.  Here the CTAs stay resident and hand activations to each
+// other through L2:
+//
+//  * Weight tape.  At build time every CTA's share of every matrix is copied
+//    into one contiguous per-CTA byte stream in exactly the order the CTA
+//    consumes it (rows = K quants followed, per entry, by the rows' fp16 block
+//    scales).  A dedicated producer warp walks the tape with bulk asynchronous
+//    copies (cp.async.bulk, mbarrier completion) into a ring of shared-memory
+//    slots, running up to a ring ahead of the consumers - weights never depend
+//    on activations, so HBM streaming is off the dependency chain.
+//  * Tagged exchange.  A phase's output vector is written to global memory as
+//    8-byte {fp32 value, 32-bit epoch} words.  Consumers poll the words they
+//    need until the epoch is the one they expect: data and flag arrive in one
+//    atomic 8-byte store, so no fence, no counter and no reset is needed, and
+//    a stale buffer can never be mistaken for fresh data.
+//  * 15 consumer warps per CTA.  A lane keeps 32 activation values of one
+//    1024-wide K segment in registers and streams weight rows from the ring.
+//    K <= 1024: warps split rows.  K > 1024: warps split (segment, rows) and
+//    partials are combined in a fixed order through shared memory.
+//
+// Every wait (mbarrier, exchange poll) is bounded by a deadline in SM clocks (about 1 s);
+// on expiry the kernel records an error code, stops waiting everywhere and
+// runs to completion on whatever data it has, so a logic error cannot hang
+// the GPU.  The host checks the status word after each launch.
+#pragma once
+
+#include "decode_kernels.cuh"
+
+namespace mg {
+
+constexpr int MK_NW = 15;                       // consumer warps
+constexpr int MK_CONSUMERS = MK_NW * 32;        // 480
+constexpr int MK_THREADS = MK_CONSUMERS + 32;   // + producer warp = 512 threads, 128 registers each
+constexpr int MK_SLOT = 16384;                  // ring slot bytes
+constexpr int MK_MAX_SLOTS = 14;
+constexpr int MK_PART_FLOATS = 2048;
+constexpr int MK_EPOCHS_PER_LAYER = 8;
+constexpr long long MK_WAIT_CYCLES = 2000000000ll;         // per wait: about one second of SM clocks
+
+enum : int { PH_QKV = 0, PH_WO = 1, PH_GU = 2, PH_DOWN = 3, PH_HEAD = 4 };
+enum : int { MK_OK = 0, MK_ERR_POLL = 1, MK_ERR_FULL = 2, MK_ERR_EMPTY = 3 };
+
+struct MegaStatus {
+    int error;          // first error code (0 = none)
+    int where;          // phase / tag that timed out
+    int cta;
+    int pad;
+};
+
+struct Tagged {         // one exchanged activation
+    float v;
+    unsigned int tag;
+};
+
+struct MegaArgs {
+    int dim, kv_dim, head_dim, n_heads, n_kv_heads, ffn_dim, vocab, n_layers, max_seq;
+    int layer_fmt, head_fmt;
+    float eps;
+    int ls, le;             // layer range
+    int head;               // HEAD_NONE / HEAD_ARGMAX / HEAD_LOGITS (0/1/2)
+    int embed;              // 1: hidden state from the embedding row of st->token, 0: from h_in
+    int n_steps;            // tokens per launch (greedy feedback between them)
+    unsigned int epoch;     // first epoch of this launch
+    int hd_shift;           // log2(head_dim)
+    int nslot;
+    int xs_floats;          // size of the staged-activation buffer (multiple of 4)
+    int sc_floats;          // attention score buffer: max_seq rounded up to a multiple of 4
+    // weight tape
+    const uint8_t* tape;
+    const unsigned long long* tape_off;   // [grid][n_layers*4 + 2]
+    // small vectors (device arrays of device pointers, indexed by layer)
+    const float* const* norm1;
+    const float* const* norm2;
+    const float* const* bq;
+    const float* const* bk;
+    const float* const* bv;
+    const float* final_norm;
+    WeightView embed_w;
+    const float* cos_tab;
+    const float* sin_tab;
+    __half* kc;             // [layers][max_seq][kv_dim]
+    __half* vc;
+    // exchange buffers
+    Tagged *xh, *xhm, *xq, *xkv, *xattn, *xmid, *xtok;
+    // io
+    const float* h_in;
+    float* h_out;
+    float* logits;
+    StepState* st;
+    int* out_tokens;
+    MegaStatus* status;
+    long long* trace;       // optional [grid][n_layers*10 + 2] SM-clock stamps of CTA thread 0 (first step)
+};
+
+// ---------------------------------------------------------------------
+// Row partition shared by the host tape builder and the kernel.
+// ---------------------------------------------------------------------
+struct PhaseShape {
+    int items;      // work items over the whole grid
+    int rpi;        // rows per item (2 for RoPE pairs and gate/up pairs)
+    int K;          // input dim
+    int fmt;
+};
+
+__host__ __device__ inline PhaseShape phase_shape_of(int p, int dim, int kv_dim, int ffn, int vocab, int layer_fmt,
+                                                     int head_fmt) {
+    PhaseShape s{};
+    switch (p) {
+        case PH_QKV: s.items = (dim + 2 * kv_dim) / 2; s.rpi = 2; s.K = dim; s.fmt = layer_fmt; break;
+        case PH_WO: s.items = dim; s.rpi = 1; s.K = dim; s.fmt = layer_fmt; break;
+        case PH_GU: s.items = ffn; s.rpi = 2; s.K = dim; s.fmt = layer_fmt; break;
+        case PH_DOWN: s.items = dim; s.rpi = 1; s.K = ffn; s.fmt = layer_fmt; break;
+        default: s.items = vocab; s.rpi = 1; s.K = dim; s.fmt = head_fmt; break;
+    }
+    return s;
+}
+
+__host__ __device__ inline int item_begin(int items, int cta, int grid) {
+    return (int)(((long long)cta * items) / grid);
+}
+__host__ __device__ inline int row_q_bytes(int fmt, int K) { return plane_row_bytes(fmt, K); }
+__host__ __device__ inline int row_d_bytes(int fmt, int K) { return fmt == FMT_F16 ? 0 : (K / 32) * 2; }
+// rows per ring entry (even, so pairs never straddle entries); 0 = the row does not fit
+__host__ __device__ inline int rows_per_entry(int fmt, int K) {
+    const int rb = row_q_bytes(fmt, K) + row_d_bytes(fmt, K);
+    int r = MK_SLOT / rb;
+    return r & ~1;
+}
+__host__ __device__ inline int entry_bytes(int fmt, int K, int nrows) {
+    return (nrows * (row_q_bytes(fmt, K) + row_d_bytes(fmt, K)) + 15) & ~15;
+}
+
+// QKV pair -> matrix (0 q, 1 k, 2 v) and its two rows.
+__host__ __device__ inline void qkv_pair(int item, int dim, int kv_dim, int head_dim, int* m, int* r0, int* r1) {
+    const int half = head_dim / 2;
+    const int nq = dim / 2, nk = kv_dim / 2;
+    int mm = 0, i = item;
+    if (i >= nq) { i -= nq; mm = 1; }
+    if (mm == 1 && i >= nk) { i -= nk; mm = 2; }
+    if (mm < 2) {
+        const int head = i / half, j = i - head * half;
+        *r0 = head * head_dim + j;
+        *r1 = *r0 + half;
+    } else {
+        *r0 = 2 * i;
+        *r1 = 2 * i + 1;
+    }
+    *m = mm;
+}
+
+// ---------------------------------------------------------------------
+// Low-level primitives
+// ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// Deadlines are counted in SM clocks: reading the clock register costs a few cycles, whereas the
+// global nanosecond timer is a slow off-SM read that would sit on every unsuccessful first poll.
+__device__ __forceinline__ long long global_ns() { return clock64(); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(unsigned long long* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// global -> this CTA's shared memory, completion counted on an mbarrier
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(MK_CONSUMERS) : "memory"); }
+
+// Exchange words are 64-bit {value (low), tag (high)}: each is read and written as ONE 8-byte
+// relaxed gpu-scope access, so value and tag can never be observed torn.
+__device__ __forceinline__ uint4 ld_poll16(const void* p) {
+    unsigned long long a, b;
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+    return make_uint4((unsigned)a, (unsigned)(a >> 32), (unsigned)b, (unsigned)(b >> 32));
+}
+__device__ __forceinline__ uint2 ld_poll8(const void* p) {
+    unsigned long long a;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+    return make_uint2((unsigned)a, (unsigned)(a >> 32));
+}
+__device__ __forceinline__ void st_tagged(Tagged* p, float v, unsigned int tag) {
+    const unsigned long long w = (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ uint4 lds16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+
+// ---------------------------------------------------------------------
+// Per-CTA shared memory.  Layout (bytes): ring | xs | hs | part | red | rope | sc | barriers | flag.
+// Pointers are recomputed from the shared symbol where they are used, so the compiler keeps
+// them as 32-bit shared-space addresses instead of 64-bit generic pointers held in registers.
+// ---------------------------------------------------------------------
+extern __shared__ __align__(128) uint8_t mk_smem[];
+constexpr int MK_ROPE_FLOATS = 256;
+
+struct MkCtx {
+    const MegaArgs& a;
+    unsigned int entry;           // running ring-entry counter of this thread's role (diagnostics)
+    int slot;                     // ring slot of the next entry
+    unsigned int par;             // phase parity of that slot
+    __device__ __forceinline__ MkCtx(const MegaArgs& args) : a(args), entry(0), slot(0), par(0) {}
+    __device__ __forceinline__ void advance() {
+        entry++;
+        if (++slot == a.nslot) { slot = 0; par ^= 1u; }
+    }
+    __device__ __forceinline__ uint8_t* ring() const { return mk_smem; }
+    __device__ __forceinline__ float* xs() const { return reinterpret_cast<float*>(mk_smem + (size_t)a.nslot * MK_SLOT); }
+    __device__ __forceinline__ float* hs() const { return xs() + a.xs_floats; }
+    __device__ __forceinline__ float* part() const { return hs() + a.dim; }
+    __device__ __forceinline__ float* red() const { return part() + MK_PART_FLOATS; }
+    __device__ __forceinline__ float* rope() const { return red() + 64; }
+    __device__ __forceinline__ float* sc() const { return rope() + MK_ROPE_FLOATS; }
+    __device__ __forceinline__ unsigned long long* full() const {
+        return reinterpret_cast<unsigned long long*>(sc() + a.sc_floats);
+    }
+    __device__ __forceinline__ unsigned long long* empty() const { return full() + MK_MAX_SLOTS; }
+    __device__ __forceinline__ volatile int* abort_flag() const {
+        return reinterpret_cast<volatile int*>(empty() + MK_MAX_SLOTS);
+    }
+    // per phase p: [p] first work item on this CTA, [8+p] item count, [16+p] rows per ring entry,
+    // [24+p] consumer warps per K segment
+    __device__ __forceinline__ int* phase_tab() const { return const_cast<int*>(reinterpret_cast<volatile int*>(abort_flag())) + 4; }
+    __device__ __forceinline__ MegaStatus* status() const { return a.status; }
+    __device__ __forceinline__ int nslot() const { return a.nslot; }
+};
+
+__device__ __noinline__ void mk_fail_impl(volatile int* abort_flag, MegaStatus* status, int code, int where) {
+    *abort_flag = 1;
+    if (atomicCAS(&status->error, 0, code) == 0) {
+        status->where = where;
+        status->cta = blockIdx.x;
+    }
+}
+__device__ __forceinline__ void mk_fail(MkCtx& c, int code, int where) {
+    mk_fail_impl(c.abort_flag(), c.status(), code, where);
+}
+
+#define MK_TRACE_EVENTS(L) ((L) * 10 + 2 + 48 + 16)
+#ifdef MK_DEBUG_TRACE
+#define MK_DBG(cond, idx) do { asm volatile("" ::: "memory"); if ((cond) && a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * MK_TRACE_EVENTS(a.n_layers) + a.n_layers * 10 + 2 + (idx)] = clock64(); asm volatile("" ::: "memory"); } while (0)
+#else
+#define MK_DBG(cond, idx) do {} while (0)
+#endif
+__device__ __forceinline__ void mk_trace(const MegaArgs& a, int step, int ev) {
+    if (a.trace && step == 0 && threadIdx.x == 0)
+        a.trace[(size_t)blockIdx.x * MK_TRACE_EVENTS(a.n_layers) + ev] = clock64();
+}
+
+// Bounded wait on an mbarrier phase.
+__device__ __forceinline__ void mk_wait_bar(MkCtx& c, unsigned long long* bar, uint32_t parity, int code) {
+    if (*c.abort_flag()) return;
+    if (mbar_try(bar, parity)) return;
+    const long long t0 = global_ns();
+    for (unsigned int it = 1;; ++it) {
+        if (mbar_try(bar, parity)) return;
+        if ((it & 63u) == 0u) {
+            if (*c.abort_flag()) return;
+            if (*(volatile int*)&c.status()->error) { *c.abort_flag() = 1; return; }
+            if (global_ns() - t0 > MK_WAIT_CYCLES) { mk_fail(c, code, (int)c.entry); return; }
+        }
+    }
+}
+
+// Poll two adjacent tagged values (16-byte aligned pair).
+__device__ __forceinline__ void mk_poll2(MkCtx& c, const Tagged* p, unsigned int tag, float& v0, float& v1) {
+    uint4 r = ld_poll16(p);
+    if (r.y != tag || r.w != tag) {
+        if (!*c.abort_flag()) {
+            const long long t0 = global_ns();
+            for (unsigned int it = 1;; ++it) {
+                r = ld_poll16(p);
+                if (r.y == tag && r.w == tag) break;
+                if ((it & 63u) == 0u) {
+                    if (*c.abort_flag()) break;
+                    if (*(volatile int*)&c.status()->error) { *c.abort_flag() = 1; break; }
+                    if (global_ns() - t0 > MK_WAIT_CYCLES) { mk_fail(c, MK_ERR_POLL, (int)tag); break; }
+                }
+            }
+        }
+    }
+    v0 = __uint_as_float(r.x);
+    v1 = __uint_as_float(r.z);
+}
+__device__ __forceinline__ float mk_poll1(MkCtx& c, const Tagged* p, unsigned int tag) {
+    uint2 r = ld_poll8(p);
+    if (r.y != tag) {
+        if (!*c.abort_flag()) {
+            const long long t0 = global_ns();
+            for (unsigned int it = 1;; ++it) {
+                r = ld_poll8(p);
+                if (r.y == tag) break;
+                if ((it & 63u) == 0u) {
+                    if (*c.abort_flag()) break;
+                    if (*(volatile int*)&c.status()->error) { *c.abort_flag() = 1; break; }
+                    if (global_ns() - t0 > MK_WAIT_CYCLES) { mk_fail(c, MK_ERR_POLL, (int)tag); break; }
+                }
+            }
+        }
+    }
+    return __uint_as_float(r.x);
+}
+
+// Poll n tagged values into shared memory dst[0..n) (n even).  All consumer threads call.
+__device__ __forceinline__ void mk_gather(MkCtx& c, const Tagged* src, unsigned int tag, float* dst, int n) {
+    for (int i = 2 * threadIdx.x; i < n; i += 2 * MK_CONSUMERS) {
+        float a, b;
+        mk_poll2(c, src + i, tag, a, b);
+        dst[i] = a;
+        dst[i + 1] = b;
+    }
+}
+
+// Sum over the consumer threads (deterministic order); includes one consumer barrier.
+__device__ __forceinline__ float mk_block_sum(MkCtx& c, float v) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (lane == 0) c.red()[w] = v;
+    consumer_sync();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < MK_NW; i++) t += c.red()[i];
+    return t;
+}
+
+// ---------------------------------------------------------------------
+// Activation registers: 32 values of one 1024-wide K segment per lane, held in
+// eight named float4 (no arrays: they must stay in registers).
+//   Q8_0: chunks {lane, lane+32} of the segment, 16 values each -> a..d, e..h
+//   Q4_0: chunk lane, 32 values -> a..h
+//   F16 : chunks {lane + 32 i, i < 4}, 8 values each -> (a,b) (c,d) (e,f) (g,h)
+// ---------------------------------------------------------------------
+struct X8 {
+    float4 a, b, c, d, e, f, g, h;
+};
+
+__device__ __forceinline__ float4 ldx(const float* xs, int idx, bool ok, float scale) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ok) {
+        v = *reinterpret_cast<const float4*>(xs + idx);
+        v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+    }
+    return v;
+}
+
+template <int FMT>
+__device__ __forceinline__ X8 load_xregs(const float* xs, int K, int seg, int lane, float scale) {
+    X8 x;
+    if (FMT == FMT_Q8_0) {
+        const int c0 = seg * 64 + lane, c1 = c0 + 32, n = K / 16;
+        x.a = ldx(xs, c0 * 16 + 0, c0 < n, scale); x.b = ldx(xs, c0 * 16 + 4, c0 < n, scale);
+        x.c = ldx(xs, c0 * 16 + 8, c0 < n, scale); x.d = ldx(xs, c0 * 16 + 12, c0 < n, scale);
+        x.e = ldx(xs, c1 * 16 + 0, c1 < n, scale); x.f = ldx(xs, c1 * 16 + 4, c1 < n, scale);
+        x.g = ldx(xs, c1 * 16 + 8, c1 < n, scale); x.h = ldx(xs, c1 * 16 + 12, c1 < n, scale);
+    } else if (FMT == FMT_Q4_0) {
+        const int c0 = seg * 32 + lane, n = K / 32;
+        const bool ok = c0 < n;
+        x.a = ldx(xs, c0 * 32 + 0, ok, scale);  x.b = ldx(xs, c0 * 32 + 4, ok, scale);
+        x.c = ldx(xs, c0 * 32 + 8, ok, scale);  x.d = ldx(xs, c0 * 32 + 12, ok, scale);
+        x.e = ldx(xs, c0 * 32 + 16, ok, scale); x.f = ldx(xs, c0 * 32 + 20, ok, scale);
+        x.g = ldx(xs, c0 * 32 + 24, ok, scale); x.h = ldx(xs, c0 * 32 + 28, ok, scale);
+    } else {
+        const int c0 = seg * 128 + lane, n = K / 8;
+        x.a = ldx(xs, c0 * 8, c0 < n, scale);          x.b = ldx(xs, c0 * 8 + 4, c0 < n, scale);
+        x.c = ldx(xs, (c0 + 32) * 8, c0 + 32 < n, scale); x.d = ldx(xs, (c0 + 32) * 8 + 4, c0 + 32 < n, scale);
+        x.e = ldx(xs, (c0 + 64) * 8, c0 + 64 < n, scale); x.f = ldx(xs, (c0 + 64) * 8 + 4, c0 + 64 < n, scale);
+        x.g = ldx(xs, (c0 + 96) * 8, c0 + 96 < n, scale); x.h = ldx(xs, (c0 + 96) * 8 + 4, c0 + 96 < n, scale);
+    }
+    return x;
+}
+
+__device__ __forceinline__ float dot8_f16(uint4 w, float4 xa, float4 xb) {
+    const __half2* h = reinterpret_cast<const __half2*>(&w);
+    const float2 a0 = __half22float2(h[0]), a1 = __half22float2(h[1]);
+    const float2 a2 = __half22float2(h[2]), a3 = __half22float2(h[3]);
+    float a = a0.x * xa.x;
+    a = fmaf(a0.y, xa.y, a); a = fmaf(a1.x, xa.z, a); a = fmaf(a1.y, xa.w, a);
+    a = fmaf(a2.x, xb.x, a); a = fmaf(a2.y, xb.y, a); a = fmaf(a3.x, xb.z, a); a = fmaf(a3.y, xb.w, a);
+    return a;
+}
+
+__device__ __forceinline__ float dot8_u4(uint32_t w, float4 xl, float4 xh, float acc) {
+    // bytes of w: low nibbles pair with xl (elements j), high nibbles with xh (elements j + 16)
+    const uint32_t lo = w & 0x0f0f0f0fu, hi = (w >> 4) & 0x0f0f0f0fu;
+    acc = fmaf(u4_to_f32_magic(lo, 0), xl.x, acc); acc = fmaf(u4_to_f32_magic(lo, 1), xl.y, acc);
+    acc = fmaf(u4_to_f32_magic(lo, 2), xl.z, acc); acc = fmaf(u4_to_f32_magic(lo, 3), xl.w, acc);
+    acc = fmaf(u4_to_f32_magic(hi, 0), xh.x, acc); acc = fmaf(u4_to_f32_magic(hi, 1), xh.y, acc);
+    acc = fmaf(u4_to_f32_magic(hi, 2), xh.z, acc); acc = fmaf(u4_to_f32_magic(hi, 3), xh.w, acc);
+    return acc;
+}
+
+// Partial dot of one weight row (in the ring) with the lane's activation registers.
+template <int FMT>
+__device__ __forceinline__ float row_dot(const uint8_t* rq, const unsigned short* rd, int K, int seg, int lane,
+                                         const X8 x) {
+    float acc = 0.f;
+    if (FMT == FMT_Q8_0) {
+        const int c0 = seg * 64 + lane, c1 = c0 + 32, n = K / 16;
+        // four independent 4-FMA chains per chunk keep the FP pipe busy
+        if (c0 < n) {
+            const uint4 w = lds16(rq + c0 * 16);
+            const float p0 = dot4_s8(w.x, x.a, 0.f), p1 = dot4_s8(w.y, x.b, 0.f);
+            const float p2 = dot4_s8(w.z, x.c, 0.f), p3 = dot4_s8(w.w, x.d, 0.f);
+            acc = half_bits_to_float(rd[c0 >> 1]) * ((p0 + p1) + (p2 + p3));
+        }
+        if (c1 < n) {
+            const uint4 w = lds16(rq + c1 * 16);
+            const float p0 = dot4_s8(w.x, x.e, 0.f), p1 = dot4_s8(w.y, x.f, 0.f);
+            const float p2 = dot4_s8(w.z, x.g, 0.f), p3 = dot4_s8(w.w, x.h, 0.f);
+            acc = fmaf(half_bits_to_float(rd[c1 >> 1]), (p0 + p1) + (p2 + p3), acc);
+        }
+    } else if (FMT == FMT_Q4_0) {
+        const int c0 = seg * 32 + lane, n = K / 32;
+        if (c0 < n) {
+            const uint4 w = lds16(rq + c0 * 16);
+            // word i holds bytes 4i..4i+3: low nibbles = elements 4i..4i+3, high = 16+4i..
+            const float p0 = dot8_u4(w.x, x.a, x.e, 0.f), p1 = dot8_u4(w.y, x.b, x.f, 0.f);
+            const float p2 = dot8_u4(w.z, x.c, x.g, 0.f), p3 = dot8_u4(w.w, x.d, x.h, 0.f);
+            acc = half_bits_to_float(rd[c0]) * ((p0 + p1) + (p2 + p3));
+        }
+    } else {
+        const int c0 = seg * 128 + lane, n = K / 8;
+        if (c0 < n) acc = dot8_f16(lds16(rq + c0 * 16), x.a, x.b);
+        if (c0 + 32 < n) acc += dot8_f16(lds16(rq + (c0 + 32) * 16), x.c, x.d);
+        if (c0 + 64 < n) acc += dot8_f16(lds16(rq + (c0 + 64) * 16), x.e, x.f);
+        if (c0 + 96 < n) acc += dot8_f16(lds16(rq + (c0 + 96) * 16), x.g, x.h);
+    }
+    return acc;
+}
+
+// ---------------------------------------------------------------------
+// Producer warp: stream this CTA's tape through the ring.
+// ---------------------------------------------------------------------
+__device__ __forceinline__ void mk_produce_phase(MkCtx& c, const MegaArgs& a, const uint8_t* src, int fmt, int K,
+                                                 int nrows, int rpe) {
+    for (int r = 0; r < nrows; r += rpe) {
+        const int nr = min(rpe, nrows - r);
+        const uint32_t bytes = (uint32_t)entry_bytes(fmt, K, nr);
+        const int slot = c.slot;
+        const uint32_t par = c.par;
+        mk_wait_bar(c, &c.empty()[slot], par ^ 1u, MK_ERR_EMPTY);
+        mbar_expect_tx(&c.full()[slot], bytes);
+        bulk_g2s(c.ring() + (size_t)slot * MK_SLOT, src, bytes, &c.full()[slot]);
+        src += bytes;
+        c.advance();
+    }
+}
+
+__device__ __forceinline__ void mk_producer(MkCtx& c, const MegaArgs& a) {
+    if ((threadIdx.x & 31) != 0) return;
+    const unsigned long long* off = a.tape_off + (size_t)blockIdx.x * (a.n_layers * 4 + 2);
+    for (int step = 0; step < a.n_steps; step++) {
+        for (int l = a.ls; l < a.le; l++)
+            for (int p = 0; p < 4; p++) {
+                const PhaseShape s = phase_shape_of(p, a.dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
+                const int nrows = c.phase_tab()[8 + p] * s.rpi;
+                mk_produce_phase(c, a, a.tape + off[l * 4 + p], s.fmt, s.K, nrows, c.phase_tab()[16 + p]);
+            }
+        if (a.le >= a.n_layers && a.head) {
+            const PhaseShape s = phase_shape_of(PH_HEAD, a.dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
+            const int nrows = c.phase_tab()[8 + PH_HEAD];
+            mk_produce_phase(c, a, a.tape + off[a.n_layers * 4], s.fmt, s.K, nrows, c.phase_tab()[16 + PH_HEAD]);
+        }
+    }
+    // every issued copy has been waited for by the consumers unless the kernel is aborting:
+    // then give the copies in flight a bounded time to land before the CTA retires.
+    if (*c.abort_flag()) {
+        // the last nslot entries: slot s was last filled with parity par (slots before the cursor) or
+        // par ^ 1 (slots at and after it)
+        for (int sidx = 0; sidx < c.nslot(); sidx++) {
+            if (c.entry < (unsigned)c.nslot() && sidx >= (int)c.entry) continue;
+            const uint32_t par = sidx < c.slot ? c.par : (c.par ^ 1u);
+            const long long t0 = global_ns();
+            while (!mbar_try(&c.full()[sidx], par) && global_ns() - t0 < 40000000ll) {}
+        }
+    }
+}
+
+// ---------------------------------------------------------------------
+// Consumer side of one matvec phase.
+//   EPI_QKV   : pairs -> bias, RoPE -> tagged q / fp16-rounded tagged k,v
+//   EPI_RESID : out[r] = hs[r] + dot -> tagged
+//   EPI_SWIGLU: pairs (gate, up) -> silu(g) * u -> tagged
+//   EPI_LOGITS: logits[r] (plain store if requested) + running argmax
+// xs holds the (un-normalised) input vector, `scale` the RMSNorm factor
+// (1 for plain inputs; norm weights are already folded into xs).
+// ---------------------------------------------------------------------
+// Sum two per-lane values over the warp with 6 shuffles; every lane of the lower half-warp ends
+// with total(v0) in v0 and lane 0 additionally gets total(v1) in v1.
+__device__ __forceinline__ void warp_sum2(float& v0, float& v1, int lane) {
+    const bool hi = (lane & 16) != 0;
+    float keep = hi ? v1 : v0;
+    const float send = hi ? v0 : v1;
+    keep += __shfl_xor_sync(MG_FULL_MASK, send, 16);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) keep += __shfl_xor_sync(MG_FULL_MASK, keep, o);
+    const float other = __shfl_sync(MG_FULL_MASK, keep, 16);
+    v0 = keep;
+    v1 = other;
+}
+
+// ---------------------------------------------------------------------
+// One matvec phase on the consumer warps.  ONE code path serves every phase
+// (QKV, wo, gate/up, down, lm_head) so that the instructions stay resident in
+// the instruction caches across the ~120 phases of a token; only the epilogue
+// switches on the phase.  Rows are always processed two at a time:
+//   QKV      : the two rows of a RoPE pair  -> bias, rotate -> tagged q / fp16-rounded tagged k,v
+//   gate/up  : gate row j and up row j      -> silu(g) * u -> tagged
+//   wo, down : two consecutive output rows  -> hs[r] + dot -> tagged
+//   lm_head  : two consecutive vocab rows   -> logits (optional) + running argmax
+// xs holds the input vector (norm weights already folded in), `scale` is the RMSNorm factor.
+// ---------------------------------------------------------------------
+__device__ __forceinline__ void mk_epilogue(const MegaArgs& a, MkCtx& c, int p, int layer, unsigned int tag,
+                                            int row, bool has2, float v0, float v1, unsigned long long& best) {
+    const int ib = c.phase_tab()[p];
+    if (p == PH_QKV) {
+        // same mapping as qkv_pair(), with the divisions by head_dim/2 done as shifts
+        const int item = ib + (row >> 1);
+        const int half = a.head_dim >> 1, hs1 = a.hd_shift - 1;
+        const int nq = a.dim >> 1, nk = a.kv_dim >> 1;
+        int m = 0, i = item;
+        if (i >= nq) { i -= nq; m = 1; }
+        if (m == 1 && i >= nk) { i -= nk; m = 2; }
+        int r0, r1;
+        if (m < 2) {
+            const int head = i >> hs1, j = i - (head << hs1);
+            r0 = (head << a.hd_shift) + j;
+            r1 = r0 + half;
+        } else {
+            r0 = 2 * i;
+            r1 = r0 + 1;
+        }
+        const float* bias = m == 0 ? a.bq[layer] : m == 1 ? a.bk[layer] : a.bv[layer];
+        if (bias) { v0 += bias[r0]; v1 += bias[r1]; }
+        if (m < 2) {
+            const int j = r0 & (a.head_dim - 1);
+            const float cs = c.rope()[j], sn = c.rope()[half + j];
+            const float t0 = v0 * cs - v1 * sn, t1 = v0 * sn + v1 * cs;
+            v0 = t0; v1 = t1;
+        }
+        if (m == 0) {
+            st_tagged(a.xq + r0, v0, tag);
+            st_tagged(a.xq + r1, v1, tag);
+        } else {
+            // K (after RoPE) and V are stored in the cache as fp16: exchange the rounded values
+            Tagged* dst = a.xkv + (m == 1 ? 0 : a.kv_dim);
+            st_tagged(dst + r0, __half2float(__float2half_rn(v0)), tag);
+            st_tagged(dst + r1, __half2float(__float2half_rn(v1)), tag);
+        }
+    } else if (p == PH_GU) {
+        st_tagged(a.xmid + ib + (row >> 1), v0 * (1.0f / (1.0f + expf(-v0))) * v1, tag);
+    } else if (p == PH_HEAD) {
+        const int r0 = ib + row;
+        if (a.head == 2) { a.logits[r0] = v0; if (has2) a.logits[r0 + 1] = v1; }
+        unsigned long long key = pack_best(v0, (unsigned)r0);
+        if (key > best) best = key;
+        if (has2) { key = pack_best(v1, (unsigned)(r0 + 1)); if (key > best) best = key; }
+    } else {
+        Tagged* out = p == PH_WO ? a.xhm : a.xh;
+        const int r0 = ib + row;
+        st_tagged(out + r0, c.hs()[r0] + v0, tag);
+        if (has2) st_tagged(out + r0 + 1, c.hs()[r0 + 1] + v1, tag);
+    }
+}
+
+template <int FMT>
+__device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int layer, unsigned int tag, float scale,
+                                         unsigned long long& best) {
+    MK_DBG(p == PH_WO && layer == 5, 0);
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int K = p == PH_DOWN ? a.ffn_dim : a.dim;
+    const int nrows = c.phase_tab()[8 + p] * ((p == PH_QKV || p == PH_GU) ? 2 : 1);
+    const int rpe = c.phase_tab()[16 + p];
+    const int rqb = row_q_bytes(FMT, K);
+    const int nb = K >> 5;
+    const int S = (K + 1023) >> 10;                  // K segments
+    const int WS = c.phase_tab()[24 + p];            // warps per segment = MK_NW / S
+    const int seg = w / WS, sub = w - seg * WS;      // warps with seg >= S idle
+    const bool active = seg < S;
+    MK_DBG(p == PH_WO && layer == 5, 1);
+    const X8 xr = load_xregs<FMT>(c.xs(), K, active ? seg : 0, lane, scale);
+    MK_DBG(p == PH_WO && layer == 5, 2);
+
+    // With S > 1 the per-row partials of all segments meet in shared memory and are combined in
+    // segment order by one thread per row pair; `part` holds CAP rows, so long phases flush in batches.
+    const bool direct = (S == 1);
+    constexpr int CAP = MK_PART_FLOATS / MK_NW;
+    int pend0 = 0;                                   // first row whose partials are still pending
+
+    for (int r = 0; r < nrows; r += rpe) {
+        const int nr = min(rpe, nrows - r);
+        const int slot = c.slot;
+        mk_wait_bar(c, &c.full()[slot], c.par, MK_ERR_FULL);
+        MK_DBG(p == PH_WO && layer == 5, 3);
+        const uint8_t* base = c.ring() + (size_t)slot * MK_SLOT;
+        const unsigned short* dbase = reinterpret_cast<const unsigned short*>(base + (size_t)nr * rqb);
+        if (active) {
+            const int npair = (nr + 1) >> 1;
+            for (int li = sub; li < npair; li += WS) {
+                const int row = 2 * li;
+                const bool has2 = row + 1 < nr;
+                float v0 = row_dot<FMT>(base + (size_t)row * rqb, dbase + (size_t)row * nb, K, seg, lane, xr);
+                float v1 = 0.f;
+                if (has2) v1 = row_dot<FMT>(base + (size_t)(row + 1) * rqb, dbase + (size_t)(row + 1) * nb, K, seg, lane, xr);
+                MK_DBG(p == PH_WO && layer == 5, 4);
+                warp_sum2(v0, v1, lane);
+                MK_DBG(p == PH_WO && layer == 5, 5);
+                if (lane == 0) {
+                    if (direct) {
+                        mk_epilogue(a, c, p, layer, tag, r + row, has2, v0, v1, best);
+                    } else {
+                        c.part()[(r + row - pend0) * MK_NW + seg] = v0;
+                        if (has2) c.part()[(r + row + 1 - pend0) * MK_NW + seg] = v1;
+                    }
+                }
+            }
+        }
+        MK_DBG(p == PH_WO && layer == 5, 6);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&c.empty()[slot]);
+        c.advance();
+        MK_DBG(p == PH_WO && layer == 5, 7);
+        if (!direct) {
+            const int done_rows = r + nr;
+            const bool last = r + rpe >= nrows;
+            if (last || (done_rows - pend0) + rpe > CAP) {
+                consumer_sync();
+                for (int row = pend0 + 2 * (int)threadIdx.x; row < done_rows; row += 2 * MK_CONSUMERS) {
+                    const bool has2 = row + 1 < done_rows;
+                    float v0 = 0.f, v1 = 0.f;
+                    for (int sg = 0; sg < S; sg++) {
+                        v0 += c.part()[(row - pend0) * MK_NW + sg];
+                        if (has2) v1 += c.part()[(row + 1 - pend0) * MK_NW + sg];
+                    }
+                    mk_epilogue(a, c, p, layer, tag, row, has2, v0, v1, best);
+                }
+                consumer_sync();
+                pend0 = done_rows;
+            }
+        }
+    }
+}
+
+// Hidden-state staging fused with RMSNorm.  Each thread fetches a pair of elements of the
+// hidden state (from an exchange buffer, the embedding row, or a plain vector), keeps the raw
+// values in hs (the residual), writes value * norm weight to xs and returns the RMSNorm factor
+// 1/sqrt(mean(h^2) + eps), which callers fold into the activation registers.  One barrier.
+enum : int { SRC_POLL = 0, SRC_EMBED = 1, SRC_PLAIN = 2 };
+__device__ __forceinline__ float mk_stage_norm(const MegaArgs& a, MkCtx& c, int src_kind, const Tagged* xsrc,
+                                               unsigned int tag, int token, const float* norm_w) {
+    float ss = 0.f;
+    for (int i = 2 * threadIdx.x; i < a.dim; i += 2 * MK_CONSUMERS) {
+        const float2 nw = *reinterpret_cast<const float2*>(norm_w + i);   // issued before the poll
+        float v0, v1;
+        if (src_kind == SRC_POLL) {
+            mk_poll2(c, xsrc + i, tag, v0, v1);
+        } else if (src_kind == SRC_EMBED) {
+            v0 = embed_value(a.embed_w, a.head_fmt, a.dim, token, i);
+            v1 = embed_value(a.embed_w, a.head_fmt, a.dim, token, i + 1);
+        } else {
+            v0 = a.h_in[i];
+            v1 = a.h_in[i + 1];
+        }
+        c.hs()[i] = v0;
+        c.hs()[i + 1] = v1;
+        ss = fmaf(v0, v0, ss);
+        ss = fmaf(v1, v1, ss);
+        c.xs()[i] = v0 * nw.x;
+        c.xs()[i + 1] = v1 * nw.y;
+    }
+    const float tot = mk_block_sum(c, ss);     // barrier: xs and hs are published
+    return rsqrtf(tot / (float)a.dim + a.eps);
+}
+
+// ---------------------------------------------------------------------
+// Attention for one query head on this CTA (fp16 KV cache).
+// Cached K/V rows do not depend on this token, so each thread loads the rows it
+// will need into registers BEFORE it waits for q: thread t holds the K row of
+// position t, thread (group g, dim pair dp) holds V[g + j*Gp][2dp..2dp+1] for
+// j < MK_VPF.  Longer contexts take the remainder from L2 in unrolled batches.
+// ---------------------------------------------------------------------
+constexpr int MK_VPF = 16;
+
+__device__ __forceinline__ float dot8_kq(uint4 kk, const float* q) {
+    const __half2* h = reinterpret_cast<const __half2*>(&kk);
+    const float4 qa = reinterpret_cast<const float4*>(q)[0];
+    const float4 qb = reinterpret_cast<const float4*>(q)[1];
+    const float2 k0 = __half22float2(h[0]), k1 = __half22float2(h[1]);
+    const float2 k2 = __half22float2(h[2]), k3 = __half22float2(h[3]);
+    float d0 = qa.x * k0.x, d1 = qa.y * k0.y;
+    d0 = fmaf(qa.z, k1.x, d0); d1 = fmaf(qa.w, k1.y, d1);
+    d0 = fmaf(qb.x, k2.x, d0); d1 = fmaf(qb.y, k2.y, d1);
+    d0 = fmaf(qb.z, k3.x, d0); d1 = fmaf(qb.w, k3.y, d1);
+    return d0 + d1;
+}
+
+template <int HD>
+__device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int layer, int pos, unsigned int tag_in,
+                                             unsigned int tag_out) {
+    constexpr int KV = HD / 8;                 // 16-byte pieces of one K row
+    constexpr int DP = HD / 2;                 // dim pairs
+    constexpr int Gp = MK_CONSUMERS / DP;      // whole position groups: 15 for hd 64, 7 for hd 128, 30 for hd 32
+    const int head = blockIdx.x;
+    const int kvh = head / (a.n_heads / a.n_kv_heads);
+    const int tid = threadIdx.x;
+    const size_t lbase = (size_t)layer * a.max_seq * a.kv_dim;
+    __half* kc = a.kc + lbase + kvh * HD;
+    __half* vc = a.vc + lbase + kvh * HD;
+    float* qs = c.xs();                 // HD
+    float* kn = c.xs() + HD;            // new K row
+    float* vn = c.xs() + 2 * HD;        // new V row
+    const int g = tid / DP, dp = tid - g * DP;
+
+    // ---- prefetch cached rows (positions < pos) ----
+    uint4 kreg[KV];
+#pragma unroll
+    for (int i = 0; i < KV; i++) kreg[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (tid < pos) {
+        const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)tid * a.kv_dim);
+#pragma unroll
+        for (int i = 0; i < KV; i++) kreg[i] = __ldcg(kp + i);
+    }
+    __half2 vreg[MK_VPF];
+#pragma unroll
+    for (int j = 0; j < MK_VPF; j++) {
+        const int t = g + j * Gp;
+        vreg[j] = __floats2half2_rn(0.f, 0.f);
+        if (g < Gp && t < pos) vreg[j] = __ldcg(reinterpret_cast<const __half2*>(vc + (size_t)t * a.kv_dim) + dp);
+    }
+
+    // ---- gather q, new k, new v (HD values each); append the new row to the cache ----
+    for (int i = 2 * tid; i < 3 * HD; i += 2 * MK_CONSUMERS) {
+        const int which = i / HD, d = i - which * HD;
+        const Tagged* src = which == 0 ? a.xq + head * HD + d
+                          : which == 1 ? a.xkv + kvh * HD + d
+                                       : a.xkv + a.kv_dim + kvh * HD + d;
+        float v0, v1;
+        mk_poll2(c, src, tag_in, v0, v1);
+        c.xs()[i] = v0;
+        c.xs()[i + 1] = v1;
+        // every CTA of the KV group appends the (identical) new row; each CTA later reads back
+        // only addresses it has written itself
+        if (which == 1) *reinterpret_cast<__half2*>(kc + (size_t)pos * a.kv_dim + d) = __floats2half2_rn(v0, v1);
+        if (which == 2) *reinterpret_cast<__half2*>(vc + (size_t)pos * a.kv_dim + d) = __floats2half2_rn(v0, v1);
+    }
+    consumer_sync();
+
+    // ---- scores ----
+    const int len = pos + 1;
+    const float scale = rsqrtf((float)HD);
+    float mx = -INFINITY;
+    if (tid < pos) {
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < KV; i++) dot += dot8_kq(kreg[i], qs + 8 * i);
+        dot *= scale;
+        c.sc()[tid] = dot;
+        mx = dot;
+    }
+    for (int t = tid + MK_CONSUMERS; t < pos; t += MK_CONSUMERS) {     // contexts beyond one row per thread
+        const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)t * a.kv_dim);
+        uint4 kk[KV];
+#pragma unroll
+        for (int i = 0; i < KV; i++) kk[i] = __ldcg(kp + i);
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < KV; i++) dot += dot8_kq(kk[i], qs + 8 * i);
+        dot *= scale;
+        c.sc()[t] = dot;
+        mx = fmaxf(mx, dot);
+    }
+    if (tid == 0) {                                                     // the new position, from shared memory
+        float dot = 0.f;
+        for (int d = 0; d < HD; d++) dot = fmaf(qs[d], kn[d], dot);
+        dot *= scale;
+        c.sc()[pos] = dot;
+        mx = fmaxf(mx, dot);
+    }
+    mx = warp_max(mx);
+    const int lane = tid & 31, w = tid >> 5;
+    if (lane == 0) c.red()[32 + w] = mx;
+    consumer_sync();
+    mx = c.red()[32];
+#pragma unroll
+    for (int i = 1; i < MK_NW; i++) mx = fmaxf(mx, c.red()[32 + i]);
+    float sum = 0.f;
+    for (int t = tid; t < len; t += MK_CONSUMERS) {
+        const float pv = expf(c.sc()[t] - mx);
+        c.sc()[t] = pv;
+        sum += pv;
+    }
+    sum = mk_block_sum(c, sum);      // barrier publishes sc[]
+
+    // ---- weighted V ----
+    if (g < Gp) {
+        float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < MK_VPF; j++) {
+            const int t = g + j * Gp;
+            if (t < pos) {
+                const float2 vf = __half22float2(vreg[j]);
+                const float pv = c.sc()[t];
+                acc.x = fmaf(pv, vf.x, acc.x);
+                acc.y = fmaf(pv, vf.y, acc.y);
+            }
+        }
+        for (int t0 = g + MK_VPF * Gp; t0 < pos; t0 += 4 * Gp) {        // remainder, four loads in flight
+            __half2 vv[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int t = t0 + j * Gp;
+                vv[j] = __floats2half2_rn(0.f, 0.f);
+                if (t < pos) vv[j] = __ldcg(reinterpret_cast<const __half2*>(vc + (size_t)t * a.kv_dim) + dp);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int t = t0 + j * Gp;
+                if (t < pos) {
+                    const float2 vf = __half22float2(vv[j]);
+                    const float pv = c.sc()[t];
+                    acc.x = fmaf(pv, vf.x, acc.x);
+                    acc.y = fmaf(pv, vf.y, acc.y);
+                }
+            }
+        }
+        if (g == pos % Gp) {                                             // the new position belongs to one group
+            const float pv = c.sc()[pos];
+            acc.x = fmaf(pv, vn[2 * dp], acc.x);
+            acc.y = fmaf(pv, vn[2 * dp + 1], acc.y);
+        }
+        c.part()[g * HD + 2 * dp] = acc.x;
+        c.part()[g * HD + 2 * dp + 1] = acc.y;
+    }
+    consumer_sync();
+    if (tid < HD) {
+        float s = 0.f;
+#pragma unroll 1
+        for (int gg = 0; gg < Gp; gg++) s += c.part()[gg * HD + tid];
+        st_tagged(a.xattn + head * HD + tid, s / sum, tag_out);
+    }
+    consumer_sync();     // part / xs are reused by the next phase
+}
+
+// ---------------------------------------------------------------------
+// Consumer warps: the decode loop, one flat loop over phases.
+// Phase index ph = layer * 4 + p for the layer phases; ph = L * 4 is lm_head.
+// Trace events per layer (mg_trace_step): 2p = input of phase p ready, 2p+1 = phase p done,
+// 8 = layer start, 9 = attention done (attention CTAs).
+// ---------------------------------------------------------------------
+__device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
+    const int tid = threadIdx.x;
+    const int L = a.n_layers;
+    const int half = a.head_dim / 2;
+    const int pos0 = a.st->pos;
+    int token = a.st->token;
+    const bool do_head = a.le >= L && a.head;
+    const int ph_begin = a.ls * 4;
+    const int ph_end = a.le * 4 + (do_head ? 1 : 0);
+
+    for (int step = 0; step < a.n_steps; step++) {
+        const unsigned int ep = a.epoch + (unsigned)step * (unsigned)(L * MK_EPOCHS_PER_LAYER + 8);
+        const int pos = min(pos0 + step, a.max_seq - 1);
+        // ---- token of this step (greedy feedback from the previous step) ----
+        if (a.embed) {
+            if (step > 0) token = (int)__float_as_uint(mk_poll1(c, a.xtok, ep - 8u + 1u));
+            token = min(max(token, 0), a.vocab - 1);
+        }
+        // RoPE row of this position: staged once per step, published by the first stage barrier
+        if (tid < 2 * half)
+            c.rope()[tid] = tid < half ? a.cos_tab[(size_t)pos * half + tid] : a.sin_tab[(size_t)pos * half + tid - half];
+        unsigned long long best = 0ull;
+
+        for (int ph = ph_begin; ph < ph_end; ph++) {
+            const bool is_head = ph >= L * 4;
+            const int l = is_head ? L : (ph >> 2);
+            const int p = is_head ? PH_HEAD : (ph & 3);
+            // tags of layer l: +1 q/kv, +2 attn, +3 h after wo, +4 ffn mid, +5 h after down
+            const unsigned int base = ep + (unsigned)l * MK_EPOCHS_PER_LAYER;
+            const unsigned int tag_prev_h = base - MK_EPOCHS_PER_LAYER + 5;
+            if (p == PH_QKV) mk_trace(a, step, l * 10 + 8);
+
+            // ---- input staging ----
+            float scale = 1.0f;
+            if (p == PH_QKV || p == PH_GU || p == PH_HEAD) {
+                int kind = SRC_POLL;
+                const Tagged* src = a.xh;
+                unsigned int tag = tag_prev_h;
+                const float* nw = is_head ? a.final_norm : a.norm1[l];
+                if (p == PH_GU) { src = a.xhm; tag = base + 3; nw = a.norm2[l]; }
+                else if (p == PH_QKV && l == a.ls) kind = a.embed ? SRC_EMBED : SRC_PLAIN;
+                scale = mk_stage_norm(a, c, kind, src, tag, token, nw);
+            } else {
+                if (p == PH_WO && (int)blockIdx.x < a.n_heads) {
+                    if (a.head_dim == 64) mk_attention<64>(a, c, l, pos, base + 1, base + 2);
+                    else if (a.head_dim == 128) mk_attention<128>(a, c, l, pos, base + 1, base + 2);
+                    else mk_attention<32>(a, c, l, pos, base + 1, base + 2);
+                    mk_trace(a, step, l * 10 + 9);
+                }
+                const bool wo = p == PH_WO;
+                mk_gather(c, wo ? a.xattn : a.xmid, wo ? base + 2 : base + 4, c.xs(), wo ? a.dim : a.ffn_dim);
+                consumer_sync();
+            }
+            if (is_head && blockIdx.x == 0 && a.h_out && step == a.n_steps - 1)
+                for (int i = tid; i < a.dim; i += MK_CONSUMERS) a.h_out[i] = c.hs()[i];
+            mk_trace(a, step, l * 10 + 2 * (is_head ? 0 : p));
+
+            // ---- matvec + fused epilogue ----
+            const unsigned int tag_out = base + (p == PH_QKV ? 1u : p == PH_WO ? 3u : p == PH_GU ? 4u : 5u);
+            const int fmt = is_head ? a.head_fmt : a.layer_fmt;
+            if (fmt == FMT_Q8_0) mk_phase<FMT_Q8_0>(a, c, p, l, tag_out, scale, best);
+            else if (fmt == FMT_Q4_0) mk_phase<FMT_Q4_0>(a, c, p, l, tag_out, scale, best);
+            else mk_phase<FMT_F16>(a, c, p, l, tag_out, scale, best);
+            MK_DBG(p == PH_WO && l == 5, 8);
+            consumer_sync();             // xs / hs / part are reused by the next phase
+            MK_DBG(p == PH_WO && l == 5, 9);
+            mk_trace(a, step, l * 10 + 2 * (is_head ? 0 : p) + 1);
+        }
+
+        if (!do_head) {
+            // partial layer range: CTA 0 hands the hidden state back
+            if (blockIdx.x == 0 && a.h_out && step == a.n_steps - 1 && a.le > a.ls) {
+                const unsigned int tag_final_h = ep + (unsigned)(a.le - 1) * MK_EPOCHS_PER_LAYER + 5;
+                mk_gather(c, a.xh, tag_final_h, c.hs(), a.dim);
+                consumer_sync();
+                for (int i = tid; i < a.dim; i += MK_CONSUMERS) a.h_out[i] = c.hs()[i];
+            }
+        } else {
+            // CTA argmax -> one atomic per CTA -> the last CTA publishes the token
+            unsigned long long* sb = reinterpret_cast<unsigned long long*>(c.part());
+            unsigned long long wb = best;         // candidates may sit in any lane (cross-segment path)
+#pragma unroll
+            for (int sh = 16; sh > 0; sh >>= 1) {
+                const unsigned long long other = __shfl_xor_sync(MG_FULL_MASK, wb, sh);
+                wb = other > wb ? other : wb;
+            }
+            if ((tid & 31) == 0) sb[tid >> 5] = wb;
+            consumer_sync();
+            if (tid == 0) {
+                unsigned long long b = sb[0];
+                for (int i = 1; i < MK_NW; i++) b = sb[i] > b ? sb[i] : b;
+                StepState* s = a.st;
+                if (b) atomicMax(&s->best, b);
+                __threadfence();
+                const unsigned int ticket = atomicAdd(&s->done, 1u);
+                if (ticket == gridDim.x - 1) {
+                    __threadfence();
+                    const unsigned long long key = atomicMax(&s->best, 0ull);
+                    const int tok = (int)(0xffffffffu - (unsigned int)(key & 0xffffffffull));
+                    if (a.out_tokens && s->step < s->out_cap) a.out_tokens[s->step] = tok;
+                    s->token = tok;
+                    s->step += 1;
+                    s->pos += 1;
+                    s->best = 0ull;
+                    s->done = 0u;
+                    __threadfence();
+                    st_tagged(a.xtok, __uint_as_float((unsigned)tok), ep + (unsigned)(L * MK_EPOCHS_PER_LAYER) + 1u);
+                }
+            }
+            consumer_sync();
+        }
+    }
+}
+
+__host__ __device__ inline size_t mk_smem_bytes(int nslot, int xs_floats, int dim, int sc_floats) {
+    return (size_t)nslot * MK_SLOT + ((size_t)xs_floats + dim + MK_PART_FLOATS + 64 + MK_ROPE_FLOATS + sc_floats) * 4 +
+           2 * MK_MAX_SLOTS * 8 + 16 + 144;
+}
+
+__global__ void __launch_bounds__(MK_THREADS, 1) mega_decode_kernel(const MegaArgs a) {
+    MkCtx c(a);
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < a.nslot; i++) {
+            mbar_init(&c.full()[i], 1);
+            mbar_init(&c.empty()[i], MK_NW);
+        }
+        *c.abort_flag() = 0;
+        for (int p = 0; p <= PH_HEAD; p++) {
+            const PhaseShape sh = phase_shape_of(p, a.dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
+            const int ib = item_begin(sh.items, blockIdx.x, gridDim.x);
+            c.phase_tab()[p] = ib;
+            c.phase_tab()[8 + p] = item_begin(sh.items, blockIdx.x + 1, gridDim.x) - ib;
+            c.phase_tab()[16 + p] = rows_per_entry(sh.fmt, sh.K);
+            c.phase_tab()[24 + p] = MK_NW / ((sh.K + 1023) / 1024);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x >= MK_CONSUMERS) mk_producer(c, a);
+    else mk_consumer(c, a);
+}
+
+}  // namespace mg

@@ -130,6 +130,14 @@ class CUDAFusedInference:
         self._check(self._lib.mg_read_kv(self._h, layer, pos0, npos, _np_ptr(k), _np_ptr(v)), "ReadKV")
         return k, v
 
+    def TraceStep(self) -> np.ndarray:
+        """SM-clock stamps [n_ctas, n_events] of one greedy step (see mg_trace_step)."""
+        cap = 256 * (self.cfg.n_layers * 10 + 2 + 64)
+        buf = np.zeros(cap, np.int64)
+        n_ctas, n_ev = C.c_int(), C.c_int()
+        self._check(self._lib.mg_trace_step(self._h, _np_ptr(buf), cap, C.byref(n_ctas), C.byref(n_ev)), "TraceStep")
+        return buf[: n_ctas.value * n_ev.value].reshape(n_ctas.value, n_ev.value)
+
     @property
     def stream(self) -> int:
         return self._lib.mg_stream(self._h) or 0
