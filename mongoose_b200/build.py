@@ -29,7 +29,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-ffp-contract=off",
     "--expt-relaxed-constexpr",
     "-Xptxas", "-v",
-] + (["-DMK_DEBUG_TRACE"] if os.environ.get("MK_DEBUG_TRACE") == "1" else [])
+]
 
 
 def _nvcc() -> str:

@@ -257,12 +257,7 @@ __device__ __forceinline__ void mk_fail(MkCtx& c, int code, int where) {
     mk_fail_impl(c.abort_flag(), c.status(), code, where);
 }
 
-#define MK_TRACE_EVENTS(L) ((L) * 10 + 2 + 48 + 16)
-#ifdef MK_DEBUG_TRACE
-#define MK_DBG(cond, idx) do { asm volatile("" ::: "memory"); if ((cond) && a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * MK_TRACE_EVENTS(a.n_layers) + a.n_layers * 10 + 2 + (idx)] = clock64(); asm volatile("" ::: "memory"); } while (0)
-#else
-#define MK_DBG(cond, idx) do {} while (0)
-#endif
+#define MK_TRACE_EVENTS(L) ((L) * 10 + 2)
 __device__ __forceinline__ void mk_trace(const MegaArgs& a, int step, int ev) {
     if (a.trace && step == 0 && threadIdx.x == 0)
         a.trace[(size_t)blockIdx.x * MK_TRACE_EVENTS(a.n_layers) + ev] = clock64();
@@ -322,6 +317,51 @@ __device__ __forceinline__ float mk_poll1(MkCtx& c, const Tagged* p, unsigned in
     return __uint_as_float(r.x);
 }
 
+// ---------------------------------------------------------------------
+// Fixed-point activations.  For int8 / 4-bit weights the dot products run on
+// the integer pipe (dp4a) without giving up fp32-class accuracy: every group
+// of 16 consecutive activations is scaled by its own s = max|x| / (2^23 - 1)
+// and rounded to a 24-bit integer t = a2*65536 + a1*256 + a0 (a2 signed byte,
+// a1 and a0 unsigned bytes).  sum q_i x_i over the group is then
+// s * (65536 * dp(q, a2) + 256 * dp(q, a1) + dp(q, a0)) with exact integer
+// dot products; the representation error is at most 2^-24 of the group's
+// largest element per term.  Shared-memory layout for a vector of K values
+// (at xs): byte planes P0 | P1 | P2 (K bytes each, element order), then one
+// float2 {s, s * sum(t)} per group of 16.
+// ---------------------------------------------------------------------
+__device__ __forceinline__ uint8_t* xq_plane(MkCtx& c, int K, int k) {
+    return reinterpret_cast<uint8_t*>(c.xs()) + (size_t)k * K;
+}
+__device__ __forceinline__ float2* xq_scales(MkCtx& c, int K) {
+    return reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(c.xs()) + (size_t)3 * K);
+}
+
+// All 32 lanes call; lanes 8j..8j+7 hold the 16 values of one group (u0,u1 each).
+__device__ __forceinline__ void xq_store_pair(MkCtx& c, int K, int i, bool ok, float u0, float u1) {
+    float m = fmaxf(fabsf(u0), fabsf(u1));
+    m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 2));
+    m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 4));
+    const float inv = m > 0.f ? 8388607.0f / m : 0.f;
+    // the group maximum may round to 2^23, which would not fit the signed top byte: clamp
+    const int t0 = max(-8388607, min(8388607, __float2int_rn(u0 * inv)));
+    const int t1 = max(-8388607, min(8388607, __float2int_rn(u1 * inv)));
+    int ts = t0 + t1;
+    ts += __shfl_xor_sync(MG_FULL_MASK, ts, 1);
+    ts += __shfl_xor_sync(MG_FULL_MASK, ts, 2);
+    ts += __shfl_xor_sync(MG_FULL_MASK, ts, 4);
+    if (ok) {
+        const unsigned int a = (unsigned)t0, b = (unsigned)t1;
+        *reinterpret_cast<unsigned short*>(xq_plane(c, K, 0) + i) = (unsigned short)((a & 0xffu) | ((b & 0xffu) << 8));
+        *reinterpret_cast<unsigned short*>(xq_plane(c, K, 1) + i) = (unsigned short)(((a >> 8) & 0xffu) | (b & 0xff00u));
+        *reinterpret_cast<unsigned short*>(xq_plane(c, K, 2) + i) = (unsigned short)(((a >> 16) & 0xffu) | ((b >> 8) & 0xff00u));
+        if ((threadIdx.x & 7) == 0) {
+            const float sc = m * (1.0f / 8388607.0f);
+            xq_scales(c, K)[i >> 4] = make_float2(sc, sc * (float)ts);
+        }
+    }
+}
+
 // Poll n tagged values into shared memory dst[0..n) (n even).  All consumer threads call.
 __device__ __forceinline__ void mk_gather(MkCtx& c, const Tagged* src, unsigned int tag, float* dst, int n) {
     for (int i = 2 * threadIdx.x; i < n; i += 2 * MK_CONSUMERS) {
@@ -329,6 +369,45 @@ __device__ __forceinline__ void mk_gather(MkCtx& c, const Tagged* src, unsigned 
         mk_poll2(c, src + i, tag, a, b);
         dst[i] = a;
         dst[i + 1] = b;
+    }
+}
+// Re-poll one pair until both tags match (bounded); r holds the first attempt.
+__device__ __forceinline__ void mk_poll2_finish(MkCtx& c, const Tagged* p, unsigned int tag, uint4& r) {
+    if (r.y == tag && r.w == tag) return;
+    if (*c.abort_flag()) return;
+    const long long t0 = global_ns();
+    for (unsigned int it = 1;; ++it) {
+        r = ld_poll16(p);
+        if (r.y == tag && r.w == tag) return;
+        if ((it & 63u) == 0u) {
+            if (*c.abort_flag()) return;
+            if (*(volatile int*)&c.status()->error) { *c.abort_flag() = 1; return; }
+            if (global_ns() - t0 > MK_WAIT_CYCLES) { mk_fail(c, MK_ERR_POLL, (int)tag); return; }
+        }
+    }
+}
+
+// Same, but the values land in xs as fixed-point planes (n a multiple of 32).  A thread's loads
+// for up to four strides are issued together so that their L2 latencies overlap; only then are the
+// tags checked (and stale words polled again).
+__device__ __forceinline__ void mk_gather_q(MkCtx& c, const Tagged* src, unsigned int tag, int n) {
+    constexpr int STRIDE = 2 * MK_CONSUMERS;
+    for (int i0 = 0; i0 < n; i0 += 4 * STRIDE) {
+        const int ia = i0 + 2 * (int)threadIdx.x, ib = ia + STRIDE, ic = ib + STRIDE, id = ic + STRIDE;
+        const uint4 z = make_uint4(0u, tag, 0u, tag);
+        uint4 ra = z, rb = z, rc = z, rd = z;
+        if (ia < n) ra = ld_poll16(src + ia);
+        if (ib < n) rb = ld_poll16(src + ib);
+        if (ic < n) rc = ld_poll16(src + ic);
+        if (id < n) rd = ld_poll16(src + id);
+        if (ia < n) mk_poll2_finish(c, src + ia, tag, ra);
+        if (ib < n) mk_poll2_finish(c, src + ib, tag, rb);
+        if (ic < n) mk_poll2_finish(c, src + ic, tag, rc);
+        if (id < n) mk_poll2_finish(c, src + id, tag, rd);
+        xq_store_pair(c, n, ia, ia < n, __uint_as_float(ra.x), __uint_as_float(ra.z));
+        if (i0 + STRIDE < n) xq_store_pair(c, n, ib, ib < n, __uint_as_float(rb.x), __uint_as_float(rb.z));
+        if (i0 + 2 * STRIDE < n) xq_store_pair(c, n, ic, ic < n, __uint_as_float(rc.x), __uint_as_float(rc.z));
+        if (i0 + 3 * STRIDE < n) xq_store_pair(c, n, id, id < n, __uint_as_float(rd.x), __uint_as_float(rd.z));
     }
 }
 
@@ -447,6 +526,114 @@ __device__ __forceinline__ float row_dot(const uint8_t* rq, const unsigned short
         if (c0 + 96 < n) acc += dot8_f16(lds16(rq + (c0 + 96) * 16), x.g, x.h);
     }
     return acc;
+}
+
+// ---------------------------------------------------------------------
+// Integer path registers: the lane's two groups of 16 activations as packed
+// bytes (4 per register, three planes) plus their scales.
+//   Q8_0: groups = chunks {lane, lane + 32} of the 1024-wide segment
+//   Q4_0: groups = the two halves (elements 0..15 / 16..31) of block `lane`
+// ---------------------------------------------------------------------
+struct XQ {
+    uint4 p0a, p1a, p2a;      // group A planes
+    uint4 p0b, p1b, p2b;      // group B planes
+    float sa, sxa, sb, sxb;   // scale and scale*sum(t), already multiplied by the RMSNorm factor
+    bool oka, okb;
+};
+
+template <int FMT>
+__device__ __forceinline__ XQ load_xq(MkCtx& c, int K, int seg, int lane, float scale) {
+    XQ x;
+    const int ngroups = K >> 4;
+    const int ga = FMT == FMT_Q8_0 ? seg * 64 + lane : (seg * 32 + lane) * 2;
+    const int gb = FMT == FMT_Q8_0 ? ga + 32 : ga + 1;
+    x.oka = ga < ngroups;
+    x.okb = gb < ngroups;
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    x.p0a = x.p1a = x.p2a = x.p0b = x.p1b = x.p2b = z;
+    x.sa = x.sxa = x.sb = x.sxb = 0.f;
+    if (x.oka) {
+        x.p0a = lds16(xq_plane(c, K, 0) + ga * 16);
+        x.p1a = lds16(xq_plane(c, K, 1) + ga * 16);
+        x.p2a = lds16(xq_plane(c, K, 2) + ga * 16);
+        const float2 s = xq_scales(c, K)[ga];
+        x.sa = s.x * scale; x.sxa = s.y * scale;
+    }
+    if (x.okb) {
+        x.p0b = lds16(xq_plane(c, K, 0) + gb * 16);
+        x.p1b = lds16(xq_plane(c, K, 1) + gb * 16);
+        x.p2b = lds16(xq_plane(c, K, 2) + gb * 16);
+        const float2 s = xq_scales(c, K)[gb];
+        x.sb = s.x * scale; x.sxb = s.y * scale;
+    }
+    return x;
+}
+
+// signed weights x {unsigned, unsigned, signed} activation bytes
+__device__ __forceinline__ int dp4a_su(uint32_t w, uint32_t a, int acc) {
+    int r;
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(a), "r"(acc));
+    return r;
+}
+__device__ __forceinline__ int dp4a_ss(uint32_t w, uint32_t a, int acc) {
+    int r;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(a), "r"(acc));
+    return r;
+}
+__device__ __forceinline__ int dp4a_uu(uint32_t w, uint32_t a, int acc) {
+    int r;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(a), "r"(acc));
+    return r;
+}
+__device__ __forceinline__ int dp4a_us(uint32_t w, uint32_t a, int acc) {
+    int r;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(a), "r"(acc));
+    return r;
+}
+
+// 16 signed int8 weights (one uint4) against one activation group: exact integer sum, as float.
+__device__ __forceinline__ float group_dot_s8(uint4 w, uint4 p0, uint4 p1, uint4 p2) {
+    int i0 = dp4a_su(w.x, p0.x, 0), i1 = dp4a_su(w.x, p1.x, 0), i2 = dp4a_ss(w.x, p2.x, 0);
+    i0 = dp4a_su(w.y, p0.y, i0); i1 = dp4a_su(w.y, p1.y, i1); i2 = dp4a_ss(w.y, p2.y, i2);
+    i0 = dp4a_su(w.z, p0.z, i0); i1 = dp4a_su(w.z, p1.z, i1); i2 = dp4a_ss(w.z, p2.z, i2);
+    i0 = dp4a_su(w.w, p0.w, i0); i1 = dp4a_su(w.w, p1.w, i1); i2 = dp4a_ss(w.w, p2.w, i2);
+    return fmaf((float)i2, 65536.0f, fmaf((float)i1, 256.0f, (float)i0));
+}
+// 16 unsigned nibbles (as bytes in four words) against one activation group.
+__device__ __forceinline__ float group_dot_u4(uint32_t n0, uint32_t n1, uint32_t n2, uint32_t n3, uint4 p0, uint4 p1,
+                                              uint4 p2) {
+    int i0 = dp4a_uu(n0, p0.x, 0), i1 = dp4a_uu(n0, p1.x, 0), i2 = dp4a_us(n0, p2.x, 0);
+    i0 = dp4a_uu(n1, p0.y, i0); i1 = dp4a_uu(n1, p1.y, i1); i2 = dp4a_us(n1, p2.y, i2);
+    i0 = dp4a_uu(n2, p0.z, i0); i1 = dp4a_uu(n2, p1.z, i1); i2 = dp4a_us(n2, p2.z, i2);
+    i0 = dp4a_uu(n3, p0.w, i0); i1 = dp4a_uu(n3, p1.w, i1); i2 = dp4a_us(n3, p2.w, i2);
+    return fmaf((float)i2, 65536.0f, fmaf((float)i1, 256.0f, (float)i0));
+}
+
+// Branch-free: groups a lane does not own have zero planes and zero scales, and their weight
+// loads are redirected to chunk 0 of the row, so both groups and both rows of a pair form one
+// straight-line block whose twelve dp4a chains the scheduler can interleave.
+template <int FMT>
+__device__ __forceinline__ float row_dot_q(const uint8_t* rq, const unsigned short* rd, int seg, int lane, const XQ x) {
+    if (FMT == FMT_Q8_0) {
+        const int c0 = x.oka ? seg * 64 + lane : 0;
+        const int c1 = x.okb ? seg * 64 + lane + 32 : 0;
+        const uint4 w0 = lds16(rq + c0 * 16), w1 = lds16(rq + c1 * 16);
+        const float d0 = half_bits_to_float(rd[c0 >> 1]), d1 = half_bits_to_float(rd[c1 >> 1]);
+        const float f0 = group_dot_s8(w0, x.p0a, x.p1a, x.p2a);
+        const float f1 = group_dot_s8(w1, x.p0b, x.p1b, x.p2b);
+        return fmaf(d0 * x.sa, f0, (d1 * x.sb) * f1);
+    } else {
+        const int b = x.oka ? seg * 32 + lane : 0;
+        // word i holds bytes 4i..4i+3: low nibbles = elements 4i..4i+3 (group A), high = 16+4i.. (group B)
+        const uint4 w = lds16(rq + b * 16);
+        const float d = half_bits_to_float(rd[b]);
+        const float fa = group_dot_u4(w.x & 0x0f0f0f0fu, w.y & 0x0f0f0f0fu, w.z & 0x0f0f0f0fu, w.w & 0x0f0f0f0fu,
+                                      x.p0a, x.p1a, x.p2a);
+        const float fb = group_dot_u4((w.x >> 4) & 0x0f0f0f0fu, (w.y >> 4) & 0x0f0f0f0fu, (w.z >> 4) & 0x0f0f0f0fu,
+                                      (w.w >> 4) & 0x0f0f0f0fu, x.p0b, x.p1b, x.p2b);
+        // sum (nib - 8) x = sum nib x - 8 sum x
+        return d * (fmaf(x.sa, fa, x.sb * fb) - 8.0f * (x.sxa + x.sxb));
+    }
 }
 
 // ---------------------------------------------------------------------
@@ -587,7 +774,6 @@ __device__ __forceinline__ void mk_epilogue(const MegaArgs& a, MkCtx& c, int p, 
 template <int FMT>
 __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int layer, unsigned int tag, float scale,
                                          unsigned long long& best) {
-    MK_DBG(p == PH_WO && layer == 5, 0);
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int K = p == PH_DOWN ? a.ffn_dim : a.dim;
     const int nrows = c.phase_tab()[8 + p] * ((p == PH_QKV || p == PH_GU) ? 2 : 1);
@@ -598,9 +784,10 @@ __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int
     const int WS = c.phase_tab()[24 + p];            // warps per segment = MK_NW / S
     const int seg = w / WS, sub = w - seg * WS;      // warps with seg >= S idle
     const bool active = seg < S;
-    MK_DBG(p == PH_WO && layer == 5, 1);
-    const X8 xr = load_xregs<FMT>(c.xs(), K, active ? seg : 0, lane, scale);
-    MK_DBG(p == PH_WO && layer == 5, 2);
+    X8 xr{};
+    XQ xq{};
+    if (FMT == FMT_F16) xr = load_xregs<FMT>(c.xs(), K, active ? seg : 0, lane, scale);
+    else xq = load_xq<FMT>(c, K, active ? seg : 0, lane, scale);
 
     // With S > 1 the per-row partials of all segments meet in shared memory and are combined in
     // segment order by one thread per row pair; `part` holds CAP rows, so long phases flush in batches.
@@ -611,21 +798,30 @@ __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int
     for (int r = 0; r < nrows; r += rpe) {
         const int nr = min(rpe, nrows - r);
         const int slot = c.slot;
-        mk_wait_bar(c, &c.full()[slot], c.par, MK_ERR_FULL);
-        MK_DBG(p == PH_WO && layer == 5, 3);
         const uint8_t* base = c.ring() + (size_t)slot * MK_SLOT;
         const unsigned short* dbase = reinterpret_cast<const unsigned short*>(base + (size_t)nr * rqb);
-        if (active) {
-            const int npair = (nr + 1) >> 1;
-            for (int li = sub; li < npair; li += WS) {
+        // Row pairs are dealt to the warps of a segment round-robin over the WHOLE phase (not per
+        // entry), so every warp gets work; a warp without a pair in this entry does not touch the
+        // slot and only reports it free.
+        const int npair = (nr + 1) >> 1;
+        const int first = (r >> 1);                          // phase-wide index of this entry's first pair
+        int li = sub - first % WS;
+        if (li < 0) li += WS;
+        if (active && li < npair) {
+            mk_wait_bar(c, &c.full()[slot], c.par, MK_ERR_FULL);
+            for (; li < npair; li += WS) {
                 const int row = 2 * li;
                 const bool has2 = row + 1 < nr;
-                float v0 = row_dot<FMT>(base + (size_t)row * rqb, dbase + (size_t)row * nb, K, seg, lane, xr);
-                float v1 = 0.f;
-                if (has2) v1 = row_dot<FMT>(base + (size_t)(row + 1) * rqb, dbase + (size_t)(row + 1) * nb, K, seg, lane, xr);
-                MK_DBG(p == PH_WO && layer == 5, 4);
+                float v0, v1 = 0.f;
+                if (FMT == FMT_F16) {
+                    v0 = row_dot<FMT>(base + (size_t)row * rqb, dbase + (size_t)row * nb, K, seg, lane, xr);
+                    if (has2) v1 = row_dot<FMT>(base + (size_t)(row + 1) * rqb, dbase + (size_t)(row + 1) * nb, K, seg, lane, xr);
+                } else {
+                    const int row1 = has2 ? row + 1 : row;     // a missing partner re-reads the first row
+                    v0 = row_dot_q<FMT>(base + (size_t)row * rqb, dbase + (size_t)row * nb, seg, lane, xq);
+                    v1 = row_dot_q<FMT>(base + (size_t)row1 * rqb, dbase + (size_t)row1 * nb, seg, lane, xq);
+                }
                 warp_sum2(v0, v1, lane);
-                MK_DBG(p == PH_WO && layer == 5, 5);
                 if (lane == 0) {
                     if (direct) {
                         mk_epilogue(a, c, p, layer, tag, r + row, has2, v0, v1, best);
@@ -636,11 +832,9 @@ __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int
                 }
             }
         }
-        MK_DBG(p == PH_WO && layer == 5, 6);
         __syncwarp();
         if (lane == 0) mbar_arrive(&c.empty()[slot]);
         c.advance();
-        MK_DBG(p == PH_WO && layer == 5, 7);
         if (!direct) {
             const int done_rows = r + nr;
             const bool last = r + rpe >= nrows;
@@ -668,26 +862,35 @@ __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int
 // 1/sqrt(mean(h^2) + eps), which callers fold into the activation registers.  One barrier.
 enum : int { SRC_POLL = 0, SRC_EMBED = 1, SRC_PLAIN = 2 };
 __device__ __forceinline__ float mk_stage_norm(const MegaArgs& a, MkCtx& c, int src_kind, const Tagged* xsrc,
-                                               unsigned int tag, int token, const float* norm_w) {
+                                               unsigned int tag, int token, const float* norm_w, bool quant) {
     float ss = 0.f;
-    for (int i = 2 * threadIdx.x; i < a.dim; i += 2 * MK_CONSUMERS) {
-        const float2 nw = *reinterpret_cast<const float2*>(norm_w + i);   // issued before the poll
-        float v0, v1;
-        if (src_kind == SRC_POLL) {
-            mk_poll2(c, xsrc + i, tag, v0, v1);
-        } else if (src_kind == SRC_EMBED) {
-            v0 = embed_value(a.embed_w, a.head_fmt, a.dim, token, i);
-            v1 = embed_value(a.embed_w, a.head_fmt, a.dim, token, i + 1);
-        } else {
-            v0 = a.h_in[i];
-            v1 = a.h_in[i + 1];
+    for (int i0 = 0; i0 < a.dim; i0 += 2 * MK_CONSUMERS) {
+        const int i = i0 + 2 * (int)threadIdx.x;
+        const bool ok = i < a.dim;
+        float v0 = 0.f, v1 = 0.f;
+        float2 nw = make_float2(0.f, 0.f);
+        if (ok) {
+            nw = *reinterpret_cast<const float2*>(norm_w + i);   // issued before the poll
+            if (src_kind == SRC_POLL) {
+                mk_poll2(c, xsrc + i, tag, v0, v1);
+            } else if (src_kind == SRC_EMBED) {
+                v0 = embed_value(a.embed_w, a.head_fmt, a.dim, token, i);
+                v1 = embed_value(a.embed_w, a.head_fmt, a.dim, token, i + 1);
+            } else {
+                v0 = a.h_in[i];
+                v1 = a.h_in[i + 1];
+            }
+            c.hs()[i] = v0;
+            c.hs()[i + 1] = v1;
+            ss = fmaf(v0, v0, ss);
+            ss = fmaf(v1, v1, ss);
         }
-        c.hs()[i] = v0;
-        c.hs()[i + 1] = v1;
-        ss = fmaf(v0, v0, ss);
-        ss = fmaf(v1, v1, ss);
-        c.xs()[i] = v0 * nw.x;
-        c.xs()[i + 1] = v1 * nw.y;
+        if (quant) {
+            xq_store_pair(c, a.dim, i, ok, v0 * nw.x, v1 * nw.y);
+        } else if (ok) {
+            c.xs()[i] = v0 * nw.x;
+            c.xs()[i + 1] = v1 * nw.y;
+        }
     }
     const float tot = mk_block_sum(c, ss);     // barrier: xs and hs are published
     return rsqrtf(tot / (float)a.dim + a.eps);
@@ -909,7 +1112,7 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
                 const float* nw = is_head ? a.final_norm : a.norm1[l];
                 if (p == PH_GU) { src = a.xhm; tag = base + 3; nw = a.norm2[l]; }
                 else if (p == PH_QKV && l == a.ls) kind = a.embed ? SRC_EMBED : SRC_PLAIN;
-                scale = mk_stage_norm(a, c, kind, src, tag, token, nw);
+                scale = mk_stage_norm(a, c, kind, src, tag, token, nw, (is_head ? a.head_fmt : a.layer_fmt) != FMT_F16);
             } else {
                 if (p == PH_WO && (int)blockIdx.x < a.n_heads) {
                     if (a.head_dim == 64) mk_attention<64>(a, c, l, pos, base + 1, base + 2);
@@ -918,7 +1121,8 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
                     mk_trace(a, step, l * 10 + 9);
                 }
                 const bool wo = p == PH_WO;
-                mk_gather(c, wo ? a.xattn : a.xmid, wo ? base + 2 : base + 4, c.xs(), wo ? a.dim : a.ffn_dim);
+                if (a.layer_fmt != FMT_F16) mk_gather_q(c, wo ? a.xattn : a.xmid, wo ? base + 2 : base + 4, wo ? a.dim : a.ffn_dim);
+                else mk_gather(c, wo ? a.xattn : a.xmid, wo ? base + 2 : base + 4, c.xs(), wo ? a.dim : a.ffn_dim);
                 consumer_sync();
             }
             if (is_head && blockIdx.x == 0 && a.h_out && step == a.n_steps - 1)
@@ -931,9 +1135,7 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
             if (fmt == FMT_Q8_0) mk_phase<FMT_Q8_0>(a, c, p, l, tag_out, scale, best);
             else if (fmt == FMT_Q4_0) mk_phase<FMT_Q4_0>(a, c, p, l, tag_out, scale, best);
             else mk_phase<FMT_F16>(a, c, p, l, tag_out, scale, best);
-            MK_DBG(p == PH_WO && l == 5, 8);
             consumer_sync();             // xs / hs / part are reused by the next phase
-            MK_DBG(p == PH_WO && l == 5, 9);
             mk_trace(a, step, l * 10 + 2 * (is_head ? 0 : p) + 1);
         }
 
