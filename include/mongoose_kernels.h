@@ -103,6 +103,16 @@ MG_API void mongoose_q4_0_matvec_dp4a_preq(const void* w_blocks, const void* q8,
 /* B pre-quantized activations; out is [B, N].  Declared at kernels.go:66. */
 MG_API void mongoose_q4_0_matvec_dp4a_batch(const void* w_blocks, const void* q8, float* out, int N, int K, int B,
                                      cudaStream_t stream);
+/* Q4_0 integer-dot matvec for callers that cannot allocate device memory (allocator calls forbidden
+ * in the section they run in, or no budget left to carve a scratch buffer from): the activation
+ * blocks live in a fixed 40 KiB array inside the library instead of a caller buffer, so K is limited
+ * to 32768.  No counterpart in the reference.  The first call on each device resolves the array's
+ * device address (make it before any stream capture); calls share the array, so calls that overlap
+ * on the GPU race.  Returns MG_OK / MG_ERR_ARG / MG_ERR_CUDA. */
+MG_API int mongoose_q4_0_matvec_dp4a_static(const float* act, const void* w_blocks, float* out, int N, int K,
+                                            cudaStream_t stream);
+/* Text of the last error mongoose_q4_0_matvec_dp4a_static returned on the calling thread ("" if none). */
+MG_API const char* mongoose_static_scratch_error(void);
 /* Replaces mongoose.cu:355-368 (fn_copy / fn_zero / fn_sync, kernels.go:24-26). */
 MG_API void mongoose_copy(void* dst, const void* src, size_t bytes, cudaStream_t stream);
 MG_API void mongoose_zero(void* ptr, size_t bytes, cudaStream_t stream);

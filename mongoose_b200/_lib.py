@@ -47,6 +47,8 @@ SIGNATURES = {
     "mongoose_q4_0_matvec_dp4a": (None, [vp, vp, vp, ci, ci, vp, vp]),
     "mongoose_q4_0_matvec_dp4a_preq": (None, [vp, vp, vp, ci, ci, vp]),
     "mongoose_q4_0_matvec_dp4a_batch": (None, [vp, vp, vp, ci, ci, ci, vp]),
+    "mongoose_q4_0_matvec_dp4a_static": (ci, [vp, vp, vp, ci, ci, vp]),
+    "mongoose_static_scratch_error": (C.c_char_p, []),
     "mongoose_copy": (None, [vp, vp, sz, vp]),
     "mongoose_zero": (None, [vp, sz, vp]),
     "mongoose_sync": (None, [vp]),

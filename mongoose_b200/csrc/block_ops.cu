@@ -10,6 +10,10 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdio>
+
+#include <mutex>
+
 #include "../../include/mongoose_kernels.h"
 #include "mg_common.cuh"
 
@@ -120,6 +124,22 @@ __global__ void __launch_bounds__(256) q4_0_dp4a_kernel(const uint8_t* __restric
 
 inline int cdiv(int a, int b) { return (a + b - 1) / b; }
 
+// ---- scratch that lives in the library image, for callers that must not allocate ----
+// 40 bytes per 32 activations; 32768 input features at most.
+constexpr int kStaticMaxK = 32768;
+constexpr size_t kStaticScratchBytes = (size_t)(kStaticMaxK / 32) * sizeof(ActBlock);
+static __device__ __align__(256) unsigned char g_static_act_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {};      // device address of g_static_act_scratch on each device
+thread_local char g_static_err[256] = "";
+
+int static_fail(int code, const char* fmt, int a, int b) {
+    snprintf(g_static_err, sizeof g_static_err, fmt, a, b);
+    return code;
+}
+
 }  // namespace
 
 extern "C" {
@@ -163,6 +183,54 @@ void mongoose_q4_0_matvec_dp4a(const float* act, const void* w_blocks, float* ou
     mongoose_q8_quantize_act(act, scratch, K, stream);
     mongoose_q4_0_matvec_dp4a_preq(w_blocks, scratch, out, N, K, stream);
 }
+
+// Q4_0 integer-dot matvec that allocates nothing.
+//
+// Who needs it: code that may not call cudaMalloc at the moment it wants a matvec - a capture-time
+// or latency-critical section that forbids allocator calls, a plugin host that owns the memory
+// budget and hands out no more, or a caller running after the pool it was given is exhausted.  The
+// activation blocks (40 bytes per 32 inputs) that mongoose_q4_0_matvec_dp4a wants in a caller
+// buffer live instead in a fixed array inside the library image (40 KiB, room for K <= 32768),
+// present on every GPU that loads the library until the process exits.
+//
+// The array's name is only a host-side handle; the device address is looked up once per device with
+// cudaGetSymbolAddress while that device is current.  That lookup happens on the FIRST call on a
+// device, so make the first call outside any stream capture.  Every call overwrites the whole
+// region it uses before reading it, so nothing needs clearing between calls, but all calls share
+// the one array: two calls that overlap on the GPU (different streams, different threads) race.
+// Returns MG_OK, MG_ERR_ARG (NULL pointer, K not a multiple of 32, or K > 32768) or MG_ERR_CUDA;
+// mongoose_static_scratch_error() has the text.
+int mongoose_q4_0_matvec_dp4a_static(const float* act, const void* w_blocks, float* out, int N, int K,
+                                     cudaStream_t stream) {
+    g_static_err[0] = 0;
+    if (!act || !w_blocks || !out) return static_fail(MG_ERR_ARG, "NULL pointer argument (N=%d K=%d)", N, K);
+    if (N <= 0 || K < 32 || K % 32) return static_fail(MG_ERR_ARG, "N=%d must be positive and K=%d a multiple of 32", N, K);
+    if (K > kStaticMaxK)
+        return static_fail(MG_ERR_ARG, "K=%d exceeds the built-in scratch limit of %d input features", K, kStaticMaxK);
+    int dev = -1;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+        return static_fail(MG_ERR_CUDA, "cudaGetDevice failed or device ordinal %d is out of range (%d)", dev, (int)ce);
+    void* scratch;
+    {
+        std::lock_guard<std::mutex> lk(g_static_mu);
+        if (!g_static_ptr[dev]) {
+            void* p = nullptr;
+            ce = cudaGetSymbolAddress(&p, g_static_act_scratch);
+            if (ce != cudaSuccess || !p)
+                return static_fail(MG_ERR_CUDA, "cudaGetSymbolAddress failed on device %d (error %d)", dev, (int)ce);
+            g_static_ptr[dev] = p;
+        }
+        scratch = g_static_ptr[dev];
+    }
+    quantize_act_kernel<<<cdiv(K / 32, 8), 256, 0, stream>>>(act, (ActBlock*)scratch, K / 32);
+    q4_0_dp4a_kernel<<<cdiv(N, 8), 256, 0, stream>>>((const uint8_t*)w_blocks, (const ActBlock*)scratch, out, N, K, 1);
+    ce = cudaPeekAtLastError();
+    if (ce != cudaSuccess) return static_fail(MG_ERR_CUDA, "kernel launch failed on device %d (error %d)", dev, (int)ce);
+    return MG_OK;
+}
+
+const char* mongoose_static_scratch_error(void) { return g_static_err; }
 
 // The reference's per-token op order (cuda_fused_infer.go:414-444 / cuda_fused_infer_q4.go:103-131)
 // issued from one C call on caller-owned buffers.

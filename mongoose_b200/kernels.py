@@ -118,6 +118,16 @@ def KQ4_0MatvecDP4ABatch(w_blocks, q8, out, N, K, B, stream=None):
     _lib.load().mongoose_q4_0_matvec_dp4a_batch(_ptr(w_blocks), _ptr(q8), _ptr(out), N, K, B, _stream(stream))
 
 
+def KQ4_0MatvecDP4AStatic(act, w_blocks, out, N, K, stream=None) -> int:
+    """Integer-dot Q4_0 matvec whose activation scratch is a fixed array inside the library: for
+    callers that are not allowed to allocate.  Returns the C status (0 = ok)."""
+    return _lib.load().mongoose_q4_0_matvec_dp4a_static(_ptr(act), _ptr(w_blocks), _ptr(out), N, K, _stream(stream))
+
+
+def StaticScratchError() -> str:
+    return _lib.load().mongoose_static_scratch_error().decode()
+
+
 def KCopy(dst, src, nbytes, stream=None):
     _lib.load().mongoose_copy(_ptr(dst), _ptr(src), nbytes, _stream(stream))
 
