@@ -75,7 +75,8 @@ struct mg_engine {
     bool mega_ok = false;               // built and usable for this model
     uint8_t* tape = nullptr;
     unsigned long long* tape_off = nullptr;
-    const float** ptr_tab = nullptr;    // device: 5 arrays of n_layers pointers (norm1, norm2, bq, bk, bv)
+    float* mk_norms = nullptr;          // [layers][2][dim] copy of the norm vectors
+    float* mk_bias = nullptr;           // [layers][dim + 2 kv_dim] copy of the QKV biases, NULL if none is set
     Tagged* xbuf = nullptr;             // exchange buffers, one allocation
     MegaStatus* mk_status = nullptr;
     long long* mk_trace = nullptr;      // per-phase clock stamps of the next launch (mg_trace_step)
@@ -438,7 +439,8 @@ void free_mega(mg_engine* e) {
     auto drop = [&](void* p, size_t bytes) { if (p) { cudaFree(p); e->dev_bytes -= bytes; } };
     drop(e->tape, e->tape_bytes); e->tape = nullptr; e->tape_bytes = 0;
     if (e->tape_off) { cudaFree(e->tape_off); e->tape_off = nullptr; }
-    if (e->ptr_tab) { cudaFree(e->ptr_tab); e->ptr_tab = nullptr; }
+    if (e->mk_norms) { cudaFree(e->mk_norms); e->mk_norms = nullptr; }
+    if (e->mk_bias) { cudaFree(e->mk_bias); e->mk_bias = nullptr; }
     if (e->xbuf) { cudaFree(e->xbuf); e->xbuf = nullptr; }
     if (e->mk_status) { cudaFree(e->mk_status); e->mk_status = nullptr; }
     if (e->mk_trace) { cudaFree(e->mk_trace); e->mk_trace = nullptr; }
@@ -576,16 +578,25 @@ int build_mega(mg_engine* e) {
     tape = {};
     MG_CUDA(e, cudaMalloc((void**)&e->tape_off, off.size() * 8));
     MG_CUDA(e, cudaMemcpy(e->tape_off, off.data(), off.size() * 8, cudaMemcpyHostToDevice));
-    std::vector<const float*> tab((size_t)5 * L);
+    MG_CUDA(e, cudaMalloc((void**)&e->mk_norms, (size_t)L * 2 * c.dim * 4));
+    bool any_bias = false;
     for (int l = 0; l < L; l++) {
-        tab[0 * L + l] = e->vecs[l * 12 + 0];
-        tab[1 * L + l] = e->vecs[l * 12 + 8];
-        tab[2 * L + l] = e->vecs[l * 12 + 4];
-        tab[3 * L + l] = e->vecs[l * 12 + 5];
-        tab[4 * L + l] = e->vecs[l * 12 + 6];
+        MG_CUDA(e, cudaMemcpy(e->mk_norms + (size_t)l * 2 * c.dim, e->vecs[l * 12 + 0], (size_t)c.dim * 4, cudaMemcpyDeviceToDevice));
+        MG_CUDA(e, cudaMemcpy(e->mk_norms + (size_t)l * 2 * c.dim + c.dim, e->vecs[l * 12 + 8], (size_t)c.dim * 4, cudaMemcpyDeviceToDevice));
+        any_bias = any_bias || e->vecs[l * 12 + 4] || e->vecs[l * 12 + 5] || e->vecs[l * 12 + 6];
     }
-    MG_CUDA(e, cudaMalloc((void**)&e->ptr_tab, tab.size() * sizeof(float*)));
-    MG_CUDA(e, cudaMemcpy(e->ptr_tab, tab.data(), tab.size() * sizeof(float*), cudaMemcpyHostToDevice));
+    if (any_bias) {
+        const size_t bw = (size_t)c.dim + 2 * c.kv_dim;
+        MG_CUDA(e, cudaMalloc((void**)&e->mk_bias, (size_t)L * bw * 4));
+        MG_CUDA(e, cudaMemset(e->mk_bias, 0, (size_t)L * bw * 4));     // an unset bias adds zero
+        for (int l = 0; l < L; l++) {
+            const size_t offs[3] = {0, (size_t)c.dim, (size_t)c.dim + c.kv_dim};
+            const size_t lens[3] = {(size_t)c.dim, (size_t)c.kv_dim, (size_t)c.kv_dim};
+            for (int k = 0; k < 3; k++)
+                if (e->vecs[l * 12 + 4 + k])
+                    MG_CUDA(e, cudaMemcpy(e->mk_bias + l * bw + offs[k], e->vecs[l * 12 + 4 + k], lens[k] * 4, cudaMemcpyDeviceToDevice));
+        }
+    }
     const size_t nx = (size_t)3 * c.dim + 2 * c.kv_dim + c.dim + c.ffn_dim + 2;   // xh xhm xq | xkv | xattn | xmid | xtok
     MG_CUDA(e, cudaMalloc((void**)&e->xbuf, nx * sizeof(Tagged)));
     MG_CUDA(e, cudaMemset(e->xbuf, 0, nx * sizeof(Tagged)));
@@ -618,8 +629,7 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
     a.hd_shift = c.head_dim == 32 ? 5 : c.head_dim == 64 ? 6 : 7;
     a.nslot = e->mk_nslot; a.xs_floats = e->mk_xs; a.sc_floats = e->mk_sc;
     a.tape = e->tape; a.tape_off = e->tape_off;
-    a.norm1 = e->ptr_tab; a.norm2 = e->ptr_tab + L; a.bq = e->ptr_tab + 2 * L; a.bk = e->ptr_tab + 3 * L;
-    a.bv = e->ptr_tab + 4 * L;
+    a.norms = e->mk_norms; a.qkv_bias = e->mk_bias;
     a.final_norm = e->vecs[L * 12];
     a.embed_w = e->mats[L * 12 + 1].view();
     a.cos_tab = e->cos_tab; a.sin_tab = e->sin_tab; a.kc = e->kc; a.vc = e->vc;

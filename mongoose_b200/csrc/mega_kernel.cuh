@@ -73,12 +73,10 @@ struct MegaArgs {
     // weight tape
     const uint8_t* tape;
     const unsigned long long* tape_off;   // [grid][n_layers*4 + 2]
-    // small vectors (device arrays of device pointers, indexed by layer)
-    const float* const* norm1;
-    const float* const* norm2;
-    const float* const* bq;
-    const float* const* bk;
-    const float* const* bv;
+    // small vectors, flat so that no pointer has to be fetched on the dependency chain:
+    // norms[layer][2][dim] (attention norm, ffn norm); qkv_bias[layer][dim + 2*kv_dim] or NULL
+    const float* norms;
+    const float* qkv_bias;
     const float* final_norm;
     WeightView embed_w;
     const float* cos_tab;
@@ -738,8 +736,12 @@ __device__ __forceinline__ void mk_epilogue(const MegaArgs& a, MkCtx& c, int p, 
             r0 = 2 * i;
             r1 = r0 + 1;
         }
-        const float* bias = m == 0 ? a.bq[layer] : m == 1 ? a.bk[layer] : a.bv[layer];
-        if (bias) { v0 += bias[r0]; v1 += bias[r1]; }
+        if (a.qkv_bias) {
+            const float* bias = a.qkv_bias + (size_t)layer * (a.dim + 2 * a.kv_dim) +
+                                (m == 0 ? 0 : m == 1 ? a.dim : a.dim + a.kv_dim);
+            v0 += bias[r0];
+            v1 += bias[r1];
+        }
         if (m < 2) {
             const int j = r0 & (a.head_dim - 1);
             const float cs = c.rope()[j], sn = c.rope()[half + j];
@@ -794,6 +796,7 @@ __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int
     const bool direct = (S == 1);
     constexpr int CAP = MK_PART_FLOATS / MK_NW;
     int pend0 = 0;                                   // first row whose partials are still pending
+    int carry = sub;                                 // this warp's next pair, relative to the entry's first pair
 
     for (int r = 0; r < nrows; r += rpe) {
         const int nr = min(rpe, nrows - r);
@@ -804,9 +807,8 @@ __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int
         // entry), so every warp gets work; a warp without a pair in this entry does not touch the
         // slot and only reports it free.
         const int npair = (nr + 1) >> 1;
-        const int first = (r >> 1);                          // phase-wide index of this entry's first pair
-        int li = sub - first % WS;
-        if (li < 0) li += WS;
+        int li = carry;
+        carry -= npair;
         if (active && li < npair) {
             mk_wait_bar(c, &c.full()[slot], c.par, MK_ERR_FULL);
             for (; li < npair; li += WS) {
@@ -831,6 +833,7 @@ __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int
                     }
                 }
             }
+            carry = li - npair;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&c.empty()[slot]);
@@ -1109,8 +1112,8 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
                 int kind = SRC_POLL;
                 const Tagged* src = a.xh;
                 unsigned int tag = tag_prev_h;
-                const float* nw = is_head ? a.final_norm : a.norm1[l];
-                if (p == PH_GU) { src = a.xhm; tag = base + 3; nw = a.norm2[l]; }
+                const float* nw = is_head ? a.final_norm : a.norms + (size_t)l * 2 * a.dim;
+                if (p == PH_GU) { src = a.xhm; tag = base + 3; nw += a.dim; }
                 else if (p == PH_QKV && l == a.ls) kind = a.embed ? SRC_EMBED : SRC_PLAIN;
                 scale = mk_stage_norm(a, c, kind, src, tag, token, nw, (is_head ? a.head_fmt : a.layer_fmt) != FMT_F16);
             } else {
