@@ -84,6 +84,7 @@ struct mg_engine {
     float* h_in = nullptr;              // hidden-state input of PartialStep on the persistent path
     unsigned int epoch = 16;
     int mk_nslot = 0, mk_xs = 0, mk_sc = 0;
+    PhaseGeom mk_geom[5] = {};
     size_t mk_smem = 0;
     size_t tape_bytes = 0;
     bool built = false;
@@ -484,8 +485,11 @@ bool mega_feasible(mg_engine* e, std::string* why) {
     if (c.max_seq > 16384) { *why = "max_seq too large for the score buffer"; return false; }
     for (int p = 0; p <= PH_HEAD; p++) {
         const PhaseShape s = phase_shape_of(p, c.dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
-        if (rows_per_entry(s.fmt, s.K) < 2) { *why = "a weight row does not fit a ring slot"; return false; }
-        if ((s.K + 1023) / 1024 > MK_NW) { *why = "input dim needs more K segments than consumer warps"; return false; }
+        int max_rows = 0;
+        for (int cta = 0; cta < G; cta++)
+            max_rows = std::max(max_rows, (item_begin(s.items, cta + 1, G) - item_begin(s.items, cta, G)) * s.rpi);
+        e->mk_geom[p] = choose_geom(s.fmt, s.K, max_rows, s.rpi == 2, MK_NW, MK_SLOT);
+        if (e->mk_geom[p].ni == 0) { *why = "a weight tile does not fit a ring slot"; return false; }
     }
     int xs = c.dim > c.ffn_dim ? c.dim : c.ffn_dim;
     if (xs < 3 * c.head_dim) xs = 3 * c.head_dim;
@@ -514,13 +518,14 @@ int build_mega(mg_engine* e) {
     const int ncol = L * 4 + 2;
     std::vector<unsigned long long> off((size_t)G * ncol);
     unsigned long long total = 0;
-    auto phase_bytes = [&](int p, int cta) {
+    auto phase_tiles = [&](int p, int cta) {
         const PhaseShape s = phase_shape_of(p, c.dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
         const int nrows = (item_begin(s.items, cta + 1, G) - item_begin(s.items, cta, G)) * s.rpi;
-        const int rpe = rows_per_entry(s.fmt, s.K);
-        unsigned long long b = 0;
-        for (int r = 0; r < nrows; r += rpe) b += entry_bytes(s.fmt, s.K, std::min(rpe, nrows - r));
-        return b;
+        const int rpt = 32 >> e->mk_geom[p].lpr_shift;
+        return (nrows + rpt - 1) / rpt;
+    };
+    auto phase_bytes = [&](int p, int cta) {
+        return (unsigned long long)phase_tiles(p, cta) * e->mk_geom[p].tile_bytes;
     };
     for (int cta = 0; cta < G; cta++) {
         for (int l = 0; l < L; l++)
@@ -547,25 +552,35 @@ int build_mega(mg_engine* e) {
                 hd[m].resize(rd ? (size_t)M.rows * (s.K / 32) : 0);
                 if (rd) MG_CUDA(e, cudaMemcpy(hd[m].data(), M.ds, hd[m].size() * 2, cudaMemcpyDeviceToHost));
             }
-            const int rpe = rows_per_entry(s.fmt, s.K);
+            const PhaseGeom g = e->mk_geom[p];
+            const int lpr = 1 << g.lpr_shift, rpt = 32 >> g.lpr_shift;
             const int col = l < L ? l * 4 + p : L * 4;
             for (int cta = 0; cta < G; cta++) {
                 const int ib = item_begin(s.items, cta, G), ie = item_begin(s.items, cta + 1, G);
                 const int nrows = (ie - ib) * s.rpi;
+                const int ntiles = (nrows + rpt - 1) / rpt;
                 uint8_t* dst = tape.data() + off[(size_t)cta * ncol + col];
-                for (int r = 0; r < nrows; r += rpe) {
-                    const int nr = std::min(rpe, nrows - r);
-                    for (int i = 0; i < nr; i++) {
-                        const int item = ib + (r + i) / s.rpi;
-                        int mm[2], rr[2];
-                        item_rows(c, p, item, mm, rr);
-                        const int k = (r + i) % s.rpi;
-                        memcpy(dst + (size_t)i * rq, hq[mm[k]].data() + (size_t)rr[k] * rq, rq);
-                        if (rd)
-                            memcpy(dst + (size_t)nr * rq + (size_t)i * rd,
-                                   reinterpret_cast<const uint8_t*>(hd[mm[k]].data()) + (size_t)rr[k] * rd, rd);
-                    }
-                    dst += entry_bytes(s.fmt, s.K, nr);
+                // source row of every tape row of this CTA
+                std::vector<const uint8_t*> srcq(nrows);
+                std::vector<const unsigned short*> srcd(nrows);
+                for (int r = 0; r < nrows; r++) {
+                    int mm[2], rr[2];
+                    item_rows(c, p, ib + r / s.rpi, mm, rr);
+                    const int k = r % s.rpi;
+                    srcq[r] = hq[mm[k]].data() + (size_t)rr[k] * rq;
+                    srcd[r] = rd ? hd[mm[k]].data() + (size_t)rr[k] * (s.K / 32) : nullptr;
+                }
+                for (int t = 0; t < ntiles; t++) {
+                    uint8_t* tile = dst + (size_t)t * g.tile_bytes;            // zero-initialised
+                    unsigned short* tds = reinterpret_cast<unsigned short*>(tile + (size_t)g.ni * 512);
+                    for (int i = 0; i < g.ni; i++)
+                        for (int lane = 0; lane < 32; lane++) {
+                            const int row = t * rpt + (lane >> g.lpr_shift);
+                            const int ch = (lane & (lpr - 1)) + i * lpr;
+                            if (row >= nrows || ch >= g.nchunks) continue;
+                            memcpy(tile + (size_t)(i * 32 + lane) * 16, srcq[row] + (size_t)ch * 16, 16);
+                            if (rd) tds[i * 32 + lane] = srcd[row][s.fmt == FMT_Q8_0 ? (ch >> 1) : ch];
+                        }
                 }
             }
         }
@@ -627,8 +642,9 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
     a.epoch = e->epoch;
     e->epoch += (unsigned)n_steps * (unsigned)(L * MK_EPOCHS_PER_LAYER + 8);
     a.hd_shift = c.head_dim == 32 ? 5 : c.head_dim == 64 ? 6 : 7;
+    for (int p = 0; p < 5; p++) a.geom[p] = e->mk_geom[p];
     a.nslot = e->mk_nslot; a.xs_floats = e->mk_xs; a.sc_floats = e->mk_sc;
-    a.tape = e->tape; a.tape_off = e->tape_off;
+    a.tape = e->tape; a.tape_off = e->tape_off; a.tape_bytes = e->tape_bytes;
     a.norms = e->mk_norms; a.qkv_bias = e->mk_bias;
     a.final_norm = e->vecs[L * 12];
     a.embed_w = e->mats[L * 12 + 1].view();

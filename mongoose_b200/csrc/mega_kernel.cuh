@@ -8,20 +8,25 @@
 //
 //  * Weight tape.  At build time every CTA's share of every matrix is copied
 //    into one contiguous per-CTA byte stream in exactly the order the CTA
-//    consumes it (rows = K quants followed, per entry, by the rows' fp16 block
-//    scales).  A dedicated producer warp walks the tape with bulk asynchronous
-//    copies (cp.async.bulk, mbarrier completion) into a ring of shared-memory
-//    slots, running up to a ring ahead of the consumers - weights never depend
-//    on activations, so HBM streaming is off the dependency chain.
+//    consumes it: tiles of 32 >> s rows in which 1 << s adjacent lanes share a
+//    row, stored as [iteration][lane] 16-byte chunks followed by the fp16 block
+//    scales in the same order, so a warp reads 512 contiguous, conflict-free
+//    bytes per iteration.  A dedicated producer warp walks the tape with bulk
+//    asynchronous copies (cp.async.bulk, mbarrier completion) into a ring of
+//    shared-memory slots, running up to a ring ahead of the consumers - weights
+//    never depend on activations, so HBM streaming is off the dependency chain.
 //  * Tagged exchange.  A phase's output vector is written to global memory as
 //    8-byte {fp32 value, 32-bit epoch} words.  Consumers poll the words they
 //    need until the epoch is the one they expect: data and flag arrive in one
-//    atomic 8-byte store, so no fence, no counter and no reset is needed, and
+//    atomic 8-byte access, so no fence, no counter and no reset is needed, and
 //    a stale buffer can never be mistaken for fresh data.
-//  * 15 consumer warps per CTA.  A lane keeps 32 activation values of one
-//    1024-wide K segment in registers and streams weight rows from the ring.
-//    K <= 1024: warps split rows.  K > 1024: warps split (segment, rows) and
-//    partials are combined in a fixed order through shared memory.
+//  * 15 consumer warps per CTA.  The input vector is staged in shared memory
+//    (for int8/4-bit weights as 24-bit fixed point in three byte planes, so
+//    the dot products are integer dp4a); every lane accumulates its share of
+//    one row, lanes of a row combine with log2(lanes per row) shuffles, and all
+//    rows of a tile run their fused epilogue in parallel lanes.  The lanes-per-
+//    row split is chosen per phase on the host so that even a phase with eight
+//    rows per CTA spreads over several warps.
 //
 // Every wait (mbarrier, exchange poll) is bounded by a deadline in SM clocks (about 1 s);
 // on expiry the kernel records an error code, stops waiting everywhere and
@@ -43,7 +48,7 @@ constexpr int MK_EPOCHS_PER_LAYER = 8;
 constexpr long long MK_WAIT_CYCLES = 2000000000ll;         // per wait: about one second of SM clocks
 
 enum : int { PH_QKV = 0, PH_WO = 1, PH_GU = 2, PH_DOWN = 3, PH_HEAD = 4 };
-enum : int { MK_OK = 0, MK_ERR_POLL = 1, MK_ERR_FULL = 2, MK_ERR_EMPTY = 3 };
+enum : int { MK_OK = 0, MK_ERR_POLL = 1, MK_ERR_FULL = 2, MK_ERR_EMPTY = 3, MK_ERR_RANGE = 4 };
 
 struct MegaStatus {
     int error;          // first error code (0 = none)
@@ -55,6 +60,18 @@ struct MegaStatus {
 struct Tagged {         // one exchanged activation
     float v;
     unsigned int tag;
+};
+
+// How a phase's rows are laid over lanes (the same on every CTA).  A warp works on a TILE of
+// 32 >> lpr_shift rows; a row is shared by 1 << lpr_shift adjacent lanes, lane `part` of a row taking
+// the 16-byte chunks part, part + lpr, part + 2 lpr, ...  The tape stores a tile exactly in the order
+// the lanes read it: ni iterations x 32 lanes x 16 bytes, then ni x 32 fp16 block scales.
+struct PhaseGeom {
+    int lpr_shift;      // log2(lanes per row)
+    int ni;             // chunks per lane = ceil(chunks per row / lanes per row)
+    int tile_bytes;
+    int tpe;            // tiles per ring entry
+    int nchunks;        // 16-byte chunks per weight row
 };
 
 struct MegaArgs {
@@ -69,10 +86,12 @@ struct MegaArgs {
     int hd_shift;           // log2(head_dim)
     int nslot;
     int xs_floats;          // size of the staged-activation buffer (multiple of 4)
+    PhaseGeom geom[5];
     int sc_floats;          // attention score buffer: max_seq rounded up to a multiple of 4
     // weight tape
     const uint8_t* tape;
     const unsigned long long* tape_off;   // [grid][n_layers*4 + 2]
+    unsigned long long tape_bytes;
     // small vectors, flat so that no pointer has to be fetched on the dependency chain:
     // norms[layer][2][dim] (attention norm, ffn norm); qkv_bias[layer][dim + 2*kv_dim] or NULL
     const float* norms;
@@ -123,14 +142,31 @@ __host__ __device__ inline int item_begin(int items, int cta, int grid) {
 }
 __host__ __device__ inline int row_q_bytes(int fmt, int K) { return plane_row_bytes(fmt, K); }
 __host__ __device__ inline int row_d_bytes(int fmt, int K) { return fmt == FMT_F16 ? 0 : (K / 32) * 2; }
-// rows per ring entry (even, so pairs never straddle entries); 0 = the row does not fit
-__host__ __device__ inline int rows_per_entry(int fmt, int K) {
-    const int rb = row_q_bytes(fmt, K) + row_d_bytes(fmt, K);
-    int r = MK_SLOT / rb;
-    return r & ~1;
+__host__ __device__ inline int chunks_per_row(int fmt, int K) {
+    return fmt == FMT_Q8_0 ? K / 16 : fmt == FMT_Q4_0 ? K / 32 : K / 8;
 }
-__host__ __device__ inline int entry_bytes(int fmt, int K, int nrows) {
-    return (nrows * (row_q_bytes(fmt, K) + row_d_bytes(fmt, K)) + 15) & ~15;
+__host__ __device__ inline int tile_bytes_of(int fmt, int ni) { return ni * 32 * (fmt == FMT_F16 ? 16 : 18); }
+// Lanes per row for a phase whose busiest CTA has max_rows rows: the choice that minimises the
+// chunks a warp walks through (tiles per warp x chunks per lane) among those whose tile fits a ring
+// slot; row pairs must stay inside a tile, so pair phases use at most 16 lanes per row.
+__host__ inline PhaseGeom choose_geom(int fmt, int K, int max_rows, bool pairs, int n_warps, int slot_bytes) {
+    PhaseGeom best{};
+    long long best_cost = -1;
+    const int nch = chunks_per_row(fmt, K);
+    for (int sh = 0; sh <= (pairs ? 4 : 5); sh++) {
+        const int lpr = 1 << sh, rpt = 32 >> sh;
+        const int ni = (nch + lpr - 1) / lpr;
+        const int tb = tile_bytes_of(fmt, ni);
+        if (tb > slot_bytes) continue;
+        const int tiles = (max_rows + rpt - 1) / rpt;
+        const long long cost = (long long)((tiles + n_warps - 1) / n_warps) * (ni + 6);   // + per-tile overhead
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best.lpr_shift = sh; best.ni = ni; best.tile_bytes = tb; best.tpe = slot_bytes / tb; best.nchunks = nch;
+        }
+    }
+    if (best_cost < 0) best.ni = 0;     // no feasible layout
+    return best;
 }
 
 // QKV pair -> matrix (0 q, 1 k, 2 v) and its two rows.
@@ -335,19 +371,24 @@ __device__ __forceinline__ float2* xq_scales(MkCtx& c, int K) {
 }
 
 // All 32 lanes call; lanes 8j..8j+7 hold the 16 values of one group (u0,u1 each).
-__device__ __forceinline__ void xq_store_pair(MkCtx& c, int K, int i, bool ok, float u0, float u1) {
+// `want_sum`: the group's sum(t) is only needed by 4-bit weights (their -8 offset).
+__device__ __forceinline__ void xq_store_pair(MkCtx& c, int K, int i, bool ok, float u0, float u1, bool want_sum) {
     float m = fmaxf(fabsf(u0), fabsf(u1));
     m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 1));
     m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 2));
     m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 4));
-    const float inv = m > 0.f ? 8388607.0f / m : 0.f;
+    // an approximate reciprocal is enough: t is clamped, and the value represented is t * (m / 8388607)
+    const float inv = m > 0.f ? 8388607.0f * __frcp_rn(m) : 0.f;
     // the group maximum may round to 2^23, which would not fit the signed top byte: clamp
     const int t0 = max(-8388607, min(8388607, __float2int_rn(u0 * inv)));
     const int t1 = max(-8388607, min(8388607, __float2int_rn(u1 * inv)));
-    int ts = t0 + t1;
-    ts += __shfl_xor_sync(MG_FULL_MASK, ts, 1);
-    ts += __shfl_xor_sync(MG_FULL_MASK, ts, 2);
-    ts += __shfl_xor_sync(MG_FULL_MASK, ts, 4);
+    int ts = 0;
+    if (want_sum) {
+        ts = t0 + t1;
+        ts += __shfl_xor_sync(MG_FULL_MASK, ts, 1);
+        ts += __shfl_xor_sync(MG_FULL_MASK, ts, 2);
+        ts += __shfl_xor_sync(MG_FULL_MASK, ts, 4);
+    }
     if (ok) {
         const unsigned int a = (unsigned)t0, b = (unsigned)t1;
         *reinterpret_cast<unsigned short*>(xq_plane(c, K, 0) + i) = (unsigned short)((a & 0xffu) | ((b & 0xffu) << 8));
@@ -388,7 +429,7 @@ __device__ __forceinline__ void mk_poll2_finish(MkCtx& c, const Tagged* p, unsig
 // Same, but the values land in xs as fixed-point planes (n a multiple of 32).  A thread's loads
 // for up to four strides are issued together so that their L2 latencies overlap; only then are the
 // tags checked (and stale words polled again).
-__device__ __forceinline__ void mk_gather_q(MkCtx& c, const Tagged* src, unsigned int tag, int n) {
+__device__ __forceinline__ void mk_gather_q(MkCtx& c, const Tagged* src, unsigned int tag, int n, bool want_sum) {
     constexpr int STRIDE = 2 * MK_CONSUMERS;
     for (int i0 = 0; i0 < n; i0 += 4 * STRIDE) {
         const int ia = i0 + 2 * (int)threadIdx.x, ib = ia + STRIDE, ic = ib + STRIDE, id = ic + STRIDE;
@@ -402,10 +443,10 @@ __device__ __forceinline__ void mk_gather_q(MkCtx& c, const Tagged* src, unsigne
         if (ib < n) mk_poll2_finish(c, src + ib, tag, rb);
         if (ic < n) mk_poll2_finish(c, src + ic, tag, rc);
         if (id < n) mk_poll2_finish(c, src + id, tag, rd);
-        xq_store_pair(c, n, ia, ia < n, __uint_as_float(ra.x), __uint_as_float(ra.z));
-        if (i0 + STRIDE < n) xq_store_pair(c, n, ib, ib < n, __uint_as_float(rb.x), __uint_as_float(rb.z));
-        if (i0 + 2 * STRIDE < n) xq_store_pair(c, n, ic, ic < n, __uint_as_float(rc.x), __uint_as_float(rc.z));
-        if (i0 + 3 * STRIDE < n) xq_store_pair(c, n, id, id < n, __uint_as_float(rd.x), __uint_as_float(rd.z));
+        xq_store_pair(c, n, ia, ia < n, __uint_as_float(ra.x), __uint_as_float(ra.z), want_sum);
+        if (i0 + STRIDE < n) xq_store_pair(c, n, ib, ib < n, __uint_as_float(rb.x), __uint_as_float(rb.z), want_sum);
+        if (i0 + 2 * STRIDE < n) xq_store_pair(c, n, ic, ic < n, __uint_as_float(rc.x), __uint_as_float(rc.z), want_sum);
+        if (i0 + 3 * STRIDE < n) xq_store_pair(c, n, id, id < n, __uint_as_float(rd.x), __uint_as_float(rd.z), want_sum);
     }
 }
 
@@ -421,52 +462,6 @@ __device__ __forceinline__ float mk_block_sum(MkCtx& c, float v) {
     return t;
 }
 
-// ---------------------------------------------------------------------
-// Activation registers: 32 values of one 1024-wide K segment per lane, held in
-// eight named float4 (no arrays: they must stay in registers).
-//   Q8_0: chunks {lane, lane+32} of the segment, 16 values each -> a..d, e..h
-//   Q4_0: chunk lane, 32 values -> a..h
-//   F16 : chunks {lane + 32 i, i < 4}, 8 values each -> (a,b) (c,d) (e,f) (g,h)
-// ---------------------------------------------------------------------
-struct X8 {
-    float4 a, b, c, d, e, f, g, h;
-};
-
-__device__ __forceinline__ float4 ldx(const float* xs, int idx, bool ok, float scale) {
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (ok) {
-        v = *reinterpret_cast<const float4*>(xs + idx);
-        v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
-    }
-    return v;
-}
-
-template <int FMT>
-__device__ __forceinline__ X8 load_xregs(const float* xs, int K, int seg, int lane, float scale) {
-    X8 x;
-    if (FMT == FMT_Q8_0) {
-        const int c0 = seg * 64 + lane, c1 = c0 + 32, n = K / 16;
-        x.a = ldx(xs, c0 * 16 + 0, c0 < n, scale); x.b = ldx(xs, c0 * 16 + 4, c0 < n, scale);
-        x.c = ldx(xs, c0 * 16 + 8, c0 < n, scale); x.d = ldx(xs, c0 * 16 + 12, c0 < n, scale);
-        x.e = ldx(xs, c1 * 16 + 0, c1 < n, scale); x.f = ldx(xs, c1 * 16 + 4, c1 < n, scale);
-        x.g = ldx(xs, c1 * 16 + 8, c1 < n, scale); x.h = ldx(xs, c1 * 16 + 12, c1 < n, scale);
-    } else if (FMT == FMT_Q4_0) {
-        const int c0 = seg * 32 + lane, n = K / 32;
-        const bool ok = c0 < n;
-        x.a = ldx(xs, c0 * 32 + 0, ok, scale);  x.b = ldx(xs, c0 * 32 + 4, ok, scale);
-        x.c = ldx(xs, c0 * 32 + 8, ok, scale);  x.d = ldx(xs, c0 * 32 + 12, ok, scale);
-        x.e = ldx(xs, c0 * 32 + 16, ok, scale); x.f = ldx(xs, c0 * 32 + 20, ok, scale);
-        x.g = ldx(xs, c0 * 32 + 24, ok, scale); x.h = ldx(xs, c0 * 32 + 28, ok, scale);
-    } else {
-        const int c0 = seg * 128 + lane, n = K / 8;
-        x.a = ldx(xs, c0 * 8, c0 < n, scale);          x.b = ldx(xs, c0 * 8 + 4, c0 < n, scale);
-        x.c = ldx(xs, (c0 + 32) * 8, c0 + 32 < n, scale); x.d = ldx(xs, (c0 + 32) * 8 + 4, c0 + 32 < n, scale);
-        x.e = ldx(xs, (c0 + 64) * 8, c0 + 64 < n, scale); x.f = ldx(xs, (c0 + 64) * 8 + 4, c0 + 64 < n, scale);
-        x.g = ldx(xs, (c0 + 96) * 8, c0 + 96 < n, scale); x.h = ldx(xs, (c0 + 96) * 8 + 4, c0 + 96 < n, scale);
-    }
-    return x;
-}
-
 __device__ __forceinline__ float dot8_f16(uint4 w, float4 xa, float4 xb) {
     const __half2* h = reinterpret_cast<const __half2*>(&w);
     const float2 a0 = __half22float2(h[0]), a1 = __half22float2(h[1]);
@@ -475,96 +470,6 @@ __device__ __forceinline__ float dot8_f16(uint4 w, float4 xa, float4 xb) {
     a = fmaf(a0.y, xa.y, a); a = fmaf(a1.x, xa.z, a); a = fmaf(a1.y, xa.w, a);
     a = fmaf(a2.x, xb.x, a); a = fmaf(a2.y, xb.y, a); a = fmaf(a3.x, xb.z, a); a = fmaf(a3.y, xb.w, a);
     return a;
-}
-
-__device__ __forceinline__ float dot8_u4(uint32_t w, float4 xl, float4 xh, float acc) {
-    // bytes of w: low nibbles pair with xl (elements j), high nibbles with xh (elements j + 16)
-    const uint32_t lo = w & 0x0f0f0f0fu, hi = (w >> 4) & 0x0f0f0f0fu;
-    acc = fmaf(u4_to_f32_magic(lo, 0), xl.x, acc); acc = fmaf(u4_to_f32_magic(lo, 1), xl.y, acc);
-    acc = fmaf(u4_to_f32_magic(lo, 2), xl.z, acc); acc = fmaf(u4_to_f32_magic(lo, 3), xl.w, acc);
-    acc = fmaf(u4_to_f32_magic(hi, 0), xh.x, acc); acc = fmaf(u4_to_f32_magic(hi, 1), xh.y, acc);
-    acc = fmaf(u4_to_f32_magic(hi, 2), xh.z, acc); acc = fmaf(u4_to_f32_magic(hi, 3), xh.w, acc);
-    return acc;
-}
-
-// Partial dot of one weight row (in the ring) with the lane's activation registers.
-template <int FMT>
-__device__ __forceinline__ float row_dot(const uint8_t* rq, const unsigned short* rd, int K, int seg, int lane,
-                                         const X8 x) {
-    float acc = 0.f;
-    if (FMT == FMT_Q8_0) {
-        const int c0 = seg * 64 + lane, c1 = c0 + 32, n = K / 16;
-        // four independent 4-FMA chains per chunk keep the FP pipe busy
-        if (c0 < n) {
-            const uint4 w = lds16(rq + c0 * 16);
-            const float p0 = dot4_s8(w.x, x.a, 0.f), p1 = dot4_s8(w.y, x.b, 0.f);
-            const float p2 = dot4_s8(w.z, x.c, 0.f), p3 = dot4_s8(w.w, x.d, 0.f);
-            acc = half_bits_to_float(rd[c0 >> 1]) * ((p0 + p1) + (p2 + p3));
-        }
-        if (c1 < n) {
-            const uint4 w = lds16(rq + c1 * 16);
-            const float p0 = dot4_s8(w.x, x.e, 0.f), p1 = dot4_s8(w.y, x.f, 0.f);
-            const float p2 = dot4_s8(w.z, x.g, 0.f), p3 = dot4_s8(w.w, x.h, 0.f);
-            acc = fmaf(half_bits_to_float(rd[c1 >> 1]), (p0 + p1) + (p2 + p3), acc);
-        }
-    } else if (FMT == FMT_Q4_0) {
-        const int c0 = seg * 32 + lane, n = K / 32;
-        if (c0 < n) {
-            const uint4 w = lds16(rq + c0 * 16);
-            // word i holds bytes 4i..4i+3: low nibbles = elements 4i..4i+3, high = 16+4i..
-            const float p0 = dot8_u4(w.x, x.a, x.e, 0.f), p1 = dot8_u4(w.y, x.b, x.f, 0.f);
-            const float p2 = dot8_u4(w.z, x.c, x.g, 0.f), p3 = dot8_u4(w.w, x.d, x.h, 0.f);
-            acc = half_bits_to_float(rd[c0]) * ((p0 + p1) + (p2 + p3));
-        }
-    } else {
-        const int c0 = seg * 128 + lane, n = K / 8;
-        if (c0 < n) acc = dot8_f16(lds16(rq + c0 * 16), x.a, x.b);
-        if (c0 + 32 < n) acc += dot8_f16(lds16(rq + (c0 + 32) * 16), x.c, x.d);
-        if (c0 + 64 < n) acc += dot8_f16(lds16(rq + (c0 + 64) * 16), x.e, x.f);
-        if (c0 + 96 < n) acc += dot8_f16(lds16(rq + (c0 + 96) * 16), x.g, x.h);
-    }
-    return acc;
-}
-
-// ---------------------------------------------------------------------
-// Integer path registers: the lane's two groups of 16 activations as packed
-// bytes (4 per register, three planes) plus their scales.
-//   Q8_0: groups = chunks {lane, lane + 32} of the 1024-wide segment
-//   Q4_0: groups = the two halves (elements 0..15 / 16..31) of block `lane`
-// ---------------------------------------------------------------------
-struct XQ {
-    uint4 p0a, p1a, p2a;      // group A planes
-    uint4 p0b, p1b, p2b;      // group B planes
-    float sa, sxa, sb, sxb;   // scale and scale*sum(t), already multiplied by the RMSNorm factor
-    bool oka, okb;
-};
-
-template <int FMT>
-__device__ __forceinline__ XQ load_xq(MkCtx& c, int K, int seg, int lane, float scale) {
-    XQ x;
-    const int ngroups = K >> 4;
-    const int ga = FMT == FMT_Q8_0 ? seg * 64 + lane : (seg * 32 + lane) * 2;
-    const int gb = FMT == FMT_Q8_0 ? ga + 32 : ga + 1;
-    x.oka = ga < ngroups;
-    x.okb = gb < ngroups;
-    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-    x.p0a = x.p1a = x.p2a = x.p0b = x.p1b = x.p2b = z;
-    x.sa = x.sxa = x.sb = x.sxb = 0.f;
-    if (x.oka) {
-        x.p0a = lds16(xq_plane(c, K, 0) + ga * 16);
-        x.p1a = lds16(xq_plane(c, K, 1) + ga * 16);
-        x.p2a = lds16(xq_plane(c, K, 2) + ga * 16);
-        const float2 s = xq_scales(c, K)[ga];
-        x.sa = s.x * scale; x.sxa = s.y * scale;
-    }
-    if (x.okb) {
-        x.p0b = lds16(xq_plane(c, K, 0) + gb * 16);
-        x.p1b = lds16(xq_plane(c, K, 1) + gb * 16);
-        x.p2b = lds16(xq_plane(c, K, 2) + gb * 16);
-        const float2 s = xq_scales(c, K)[gb];
-        x.sb = s.x * scale; x.sxb = s.y * scale;
-    }
-    return x;
 }
 
 // signed weights x {unsigned, unsigned, signed} activation bytes
@@ -607,44 +512,23 @@ __device__ __forceinline__ float group_dot_u4(uint32_t n0, uint32_t n1, uint32_t
     return fmaf((float)i2, 65536.0f, fmaf((float)i1, 256.0f, (float)i0));
 }
 
-// Branch-free: groups a lane does not own have zero planes and zero scales, and their weight
-// loads are redirected to chunk 0 of the row, so both groups and both rows of a pair form one
-// straight-line block whose twelve dp4a chains the scheduler can interleave.
-template <int FMT>
-__device__ __forceinline__ float row_dot_q(const uint8_t* rq, const unsigned short* rd, int seg, int lane, const XQ x) {
-    if (FMT == FMT_Q8_0) {
-        const int c0 = x.oka ? seg * 64 + lane : 0;
-        const int c1 = x.okb ? seg * 64 + lane + 32 : 0;
-        const uint4 w0 = lds16(rq + c0 * 16), w1 = lds16(rq + c1 * 16);
-        const float d0 = half_bits_to_float(rd[c0 >> 1]), d1 = half_bits_to_float(rd[c1 >> 1]);
-        const float f0 = group_dot_s8(w0, x.p0a, x.p1a, x.p2a);
-        const float f1 = group_dot_s8(w1, x.p0b, x.p1b, x.p2b);
-        return fmaf(d0 * x.sa, f0, (d1 * x.sb) * f1);
-    } else {
-        const int b = x.oka ? seg * 32 + lane : 0;
-        // word i holds bytes 4i..4i+3: low nibbles = elements 4i..4i+3 (group A), high = 16+4i.. (group B)
-        const uint4 w = lds16(rq + b * 16);
-        const float d = half_bits_to_float(rd[b]);
-        const float fa = group_dot_u4(w.x & 0x0f0f0f0fu, w.y & 0x0f0f0f0fu, w.z & 0x0f0f0f0fu, w.w & 0x0f0f0f0fu,
-                                      x.p0a, x.p1a, x.p2a);
-        const float fb = group_dot_u4((w.x >> 4) & 0x0f0f0f0fu, (w.y >> 4) & 0x0f0f0f0fu, (w.z >> 4) & 0x0f0f0f0fu,
-                                      (w.w >> 4) & 0x0f0f0f0fu, x.p0b, x.p1b, x.p2b);
-        // sum (nib - 8) x = sum nib x - 8 sum x
-        return d * (fmaf(x.sa, fa, x.sb * fb) - 8.0f * (x.sxa + x.sxb));
-    }
-}
-
 // ---------------------------------------------------------------------
 // Producer warp: stream this CTA's tape through the ring.
 // ---------------------------------------------------------------------
-__device__ __forceinline__ void mk_produce_phase(MkCtx& c, const MegaArgs& a, const uint8_t* src, int fmt, int K,
-                                                 int nrows, int rpe) {
-    for (int r = 0; r < nrows; r += rpe) {
-        const int nr = min(rpe, nrows - r);
-        const uint32_t bytes = (uint32_t)entry_bytes(fmt, K, nr);
+__device__ __forceinline__ void mk_produce_phase(MkCtx& c, const MegaArgs& a, const uint8_t* src, int p, int nrows) {
+    const PhaseGeom g = a.geom[p];
+    const int rpt = 32 >> g.lpr_shift;
+    const int ntiles = (nrows + rpt - 1) >> (5 - g.lpr_shift);
+    for (int t = 0; t < ntiles; t += g.tpe) {
+        const uint32_t bytes = (uint32_t)(min(g.tpe, ntiles - t) * g.tile_bytes);
         const int slot = c.slot;
         const uint32_t par = c.par;
         mk_wait_bar(c, &c.empty()[slot], par ^ 1u, MK_ERR_EMPTY);
+        if ((unsigned long long)(src - a.tape) + bytes > a.tape_bytes || bytes == 0 || bytes > MK_SLOT || (bytes & 15u) ||
+            ((unsigned long long)(src - a.tape) & 15ull)) {
+            mk_fail(c, MK_ERR_RANGE, 300000 + p);
+            return;
+        }
         mbar_expect_tx(&c.full()[slot], bytes);
         bulk_g2s(c.ring() + (size_t)slot * MK_SLOT, src, bytes, &c.full()[slot]);
         src += bytes;
@@ -660,12 +544,11 @@ __device__ __forceinline__ void mk_producer(MkCtx& c, const MegaArgs& a) {
             for (int p = 0; p < 4; p++) {
                 const PhaseShape s = phase_shape_of(p, a.dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
                 const int nrows = c.phase_tab()[8 + p] * s.rpi;
-                mk_produce_phase(c, a, a.tape + off[l * 4 + p], s.fmt, s.K, nrows, c.phase_tab()[16 + p]);
+                mk_produce_phase(c, a, a.tape + off[l * 4 + p], p, nrows);
             }
         if (a.le >= a.n_layers && a.head) {
             const PhaseShape s = phase_shape_of(PH_HEAD, a.dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
-            const int nrows = c.phase_tab()[8 + PH_HEAD];
-            mk_produce_phase(c, a, a.tape + off[a.n_layers * 4], s.fmt, s.K, nrows, c.phase_tab()[16 + PH_HEAD]);
+            mk_produce_phase(c, a, a.tape + off[a.n_layers * 4], PH_HEAD, c.phase_tab()[8 + PH_HEAD]);
         }
     }
     // every issued copy has been waited for by the consumers unless the kernel is aborting:
@@ -691,20 +574,6 @@ __device__ __forceinline__ void mk_producer(MkCtx& c, const MegaArgs& a) {
 // xs holds the (un-normalised) input vector, `scale` the RMSNorm factor
 // (1 for plain inputs; norm weights are already folded into xs).
 // ---------------------------------------------------------------------
-// Sum two per-lane values over the warp with 6 shuffles; every lane of the lower half-warp ends
-// with total(v0) in v0 and lane 0 additionally gets total(v1) in v1.
-__device__ __forceinline__ void warp_sum2(float& v0, float& v1, int lane) {
-    const bool hi = (lane & 16) != 0;
-    float keep = hi ? v1 : v0;
-    const float send = hi ? v0 : v1;
-    keep += __shfl_xor_sync(MG_FULL_MASK, send, 16);
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) keep += __shfl_xor_sync(MG_FULL_MASK, keep, o);
-    const float other = __shfl_sync(MG_FULL_MASK, keep, 16);
-    v0 = keep;
-    v1 = other;
-}
-
 // ---------------------------------------------------------------------
 // One matvec phase on the consumer warps.  ONE code path serves every phase
 // (QKV, wo, gate/up, down, lm_head) so that the instructions stay resident in
@@ -719,6 +588,11 @@ __device__ __forceinline__ void warp_sum2(float& v0, float& v1, int lane) {
 __device__ __forceinline__ void mk_epilogue(const MegaArgs& a, MkCtx& c, int p, int layer, unsigned int tag,
                                             int row, bool has2, float v0, float v1, unsigned long long& best) {
     const int ib = c.phase_tab()[p];
+    {   // self-check: every index an epilogue writes through must lie inside its vector
+        const int lim = p == PH_QKV ? (a.dim + 2 * a.kv_dim) / 2 : p == PH_GU ? a.ffn_dim : p == PH_HEAD ? a.vocab : a.dim;
+        const int idx = (p == PH_QKV || p == PH_GU) ? ib + (row >> 1) : ib + row + (has2 ? 1 : 0);
+        if (row < 0 || idx >= lim) { mk_fail(c, MK_ERR_RANGE, 1000 * p + 100000 + row); return; }
+    }
     if (p == PH_QKV) {
         // same mapping as qkv_pair(), with the divisions by head_dim/2 done as shifts
         const int item = ib + (row >> 1);
@@ -773,89 +647,111 @@ __device__ __forceinline__ void mk_epilogue(const MegaArgs& a, MkCtx& c, int p, 
     }
 }
 
+// Dot product of this lane's share of a tile row with the staged activations.
+// tile: [ni][32] x 16-byte weight chunks, then [ni][32] fp16 block scales (lane order).
+// Lane `part` of a row takes chunks part, part + lpr, ...; chunks beyond the row are zero in the
+// tape (weights and scale), their activation index is clamped so that the loads stay in range.
+template <int FMT>
+__device__ __forceinline__ float tile_dot(MkCtx& c, const uint8_t* tile, int ni, int lane, int part, int lpr_shift,
+                                          int K) {
+    float acc = 0.f;
+    if (FMT == FMT_F16) {
+        const int last = (K >> 3) - 1;
+        const float* xs = c.xs();
+#pragma unroll 4
+        for (int i = 0; i < ni; i++) {
+            const uint4 w = lds16(tile + (size_t)(i * 32 + lane) * 16);
+            const int ch = min(part + (i << lpr_shift), last);
+            const float4 xa = *reinterpret_cast<const float4*>(xs + ch * 8);
+            const float4 xb = *reinterpret_cast<const float4*>(xs + ch * 8 + 4);
+            acc += dot8_f16(w, xa, xb);
+        }
+        return acc;
+    }
+    const unsigned short* ds = reinterpret_cast<const unsigned short*>(tile + (size_t)ni * 512);
+    const uint8_t* p0 = xq_plane(c, K, 0);
+    const uint8_t* p1 = xq_plane(c, K, 1);
+    const uint8_t* p2 = xq_plane(c, K, 2);
+    const float2* sc = xq_scales(c, K);
+    if (FMT == FMT_Q8_0) {
+        const int last = (K >> 4) - 1;
+#pragma unroll 4
+        for (int i = 0; i < ni; i++) {
+            const uint4 w = lds16(tile + (size_t)(i * 32 + lane) * 16);
+            const float d = half_bits_to_float(ds[i * 32 + lane]);
+            const int g = min(part + (i << lpr_shift), last);          // chunk = activation group
+            const float f = group_dot_s8(w, lds16(p0 + g * 16), lds16(p1 + g * 16), lds16(p2 + g * 16));
+            acc = fmaf(d * sc[g].x, f, acc);
+        }
+    } else {
+        const int last = (K >> 5) - 1;
+#pragma unroll 4
+        for (int i = 0; i < ni; i++) {
+            const uint4 w = lds16(tile + (size_t)(i * 32 + lane) * 16);
+            const float d = half_bits_to_float(ds[i * 32 + lane]);
+            const int b = min(part + (i << lpr_shift), last);          // chunk = block = groups 2b, 2b+1
+            const int ga = 2 * b, gb = 2 * b + 1;
+            // word i holds bytes 4i..4i+3: low nibbles = elements 4i..4i+3 (group A), high = 16+4i.. (group B)
+            const float fa = group_dot_u4(w.x & 0x0f0f0f0fu, w.y & 0x0f0f0f0fu, w.z & 0x0f0f0f0fu, w.w & 0x0f0f0f0fu,
+                                          lds16(p0 + ga * 16), lds16(p1 + ga * 16), lds16(p2 + ga * 16));
+            const float fb = group_dot_u4((w.x >> 4) & 0x0f0f0f0fu, (w.y >> 4) & 0x0f0f0f0fu,
+                                          (w.z >> 4) & 0x0f0f0f0fu, (w.w >> 4) & 0x0f0f0f0fu,
+                                          lds16(p0 + gb * 16), lds16(p1 + gb * 16), lds16(p2 + gb * 16));
+            const float2 sa = sc[ga], sb = sc[gb];
+            // sum (nib - 8) x = sum nib x - 8 sum x
+            acc = fmaf(d, fmaf(sa.x, fa, sb.x * fb) - 8.0f * (sa.y + sb.y), acc);
+        }
+    }
+    return acc;
+}
+
 template <int FMT>
 __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int layer, unsigned int tag, float scale,
                                          unsigned long long& best) {
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const PhaseGeom g = a.geom[p];
     const int K = p == PH_DOWN ? a.ffn_dim : a.dim;
-    const int nrows = c.phase_tab()[8 + p] * ((p == PH_QKV || p == PH_GU) ? 2 : 1);
-    const int rpe = c.phase_tab()[16 + p];
-    const int rqb = row_q_bytes(FMT, K);
-    const int nb = K >> 5;
-    const int S = (K + 1023) >> 10;                  // K segments
-    const int WS = c.phase_tab()[24 + p];            // warps per segment = MK_NW / S
-    const int seg = w / WS, sub = w - seg * WS;      // warps with seg >= S idle
-    const bool active = seg < S;
-    X8 xr{};
-    XQ xq{};
-    if (FMT == FMT_F16) xr = load_xregs<FMT>(c.xs(), K, active ? seg : 0, lane, scale);
-    else xq = load_xq<FMT>(c, K, active ? seg : 0, lane, scale);
+    const bool pairs = (p == PH_QKV || p == PH_GU);
+    const int nrows = c.phase_tab()[8 + p] * (pairs ? 2 : 1);
+    const int lpr = 1 << g.lpr_shift;
+    const int part = lane & (lpr - 1), rloc = lane >> g.lpr_shift;
+    const int ntiles = (nrows + (32 >> g.lpr_shift) - 1) >> (5 - g.lpr_shift);
+    int carry = w;                                   // this warp's next tile, relative to the entry's first tile
 
-    // With S > 1 the per-row partials of all segments meet in shared memory and are combined in
-    // segment order by one thread per row pair; `part` holds CAP rows, so long phases flush in batches.
-    const bool direct = (S == 1);
-    constexpr int CAP = MK_PART_FLOATS / MK_NW;
-    int pend0 = 0;                                   // first row whose partials are still pending
-    int carry = sub;                                 // this warp's next pair, relative to the entry's first pair
-
-    for (int r = 0; r < nrows; r += rpe) {
-        const int nr = min(rpe, nrows - r);
+    for (int t = 0; t < ntiles; t += g.tpe) {
+        const int nt = min(g.tpe, ntiles - t);
         const int slot = c.slot;
-        const uint8_t* base = c.ring() + (size_t)slot * MK_SLOT;
-        const unsigned short* dbase = reinterpret_cast<const unsigned short*>(base + (size_t)nr * rqb);
-        // Row pairs are dealt to the warps of a segment round-robin over the WHOLE phase (not per
-        // entry), so every warp gets work; a warp without a pair in this entry does not touch the
-        // slot and only reports it free.
-        const int npair = (nr + 1) >> 1;
-        int li = carry;
-        carry -= npair;
-        if (active && li < npair) {
-            mk_wait_bar(c, &c.full()[slot], c.par, MK_ERR_FULL);
-            for (; li < npair; li += WS) {
-                const int row = 2 * li;
-                const bool has2 = row + 1 < nr;
-                float v0, v1 = 0.f;
-                if (FMT == FMT_F16) {
-                    v0 = row_dot<FMT>(base + (size_t)row * rqb, dbase + (size_t)row * nb, K, seg, lane, xr);
-                    if (has2) v1 = row_dot<FMT>(base + (size_t)(row + 1) * rqb, dbase + (size_t)(row + 1) * nb, K, seg, lane, xr);
+        int tl = carry;
+        carry -= nt;
+        // Every warp observes every entry's arrival, also of entries it owns no tile of: a warp that
+        // skipped ahead could otherwise meet a slot whose barrier is a whole ring revolution behind,
+        // take the stale phase for its own (parity waits cannot tell them apart) and release the slot
+        // early.  Waiting on a completed phase costs a few cycles.
+        mk_wait_bar(c, &c.full()[slot], c.par, MK_ERR_FULL);
+        if (tl < nt) {
+            // tiles are dealt to the warps round-robin over the whole phase
+            const uint8_t* base = c.ring() + (size_t)slot * MK_SLOT;
+            if (slot < 0 || slot >= a.nslot || nt * g.tile_bytes > MK_SLOT || g.ni <= 0) {
+                mk_fail(c, MK_ERR_RANGE, 200000 + p);
+                tl = nt + ((tl - nt) % MK_NW + MK_NW) % MK_NW;      // skip this entry's tiles
+            }
+            for (; tl < nt; tl += MK_NW) {
+                float v = tile_dot<FMT>(c, base + (size_t)tl * g.tile_bytes, g.ni, lane, part, g.lpr_shift, K);
+                for (int o = lpr >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(MG_FULL_MASK, v, o);
+                v *= scale;
+                const int row = ((t + tl) << (5 - g.lpr_shift)) + rloc;       // row within this CTA's phase rows
+                if (pairs) {
+                    const float v1 = __shfl_down_sync(MG_FULL_MASK, v, lpr);  // the partner row sits lpr lanes up
+                    if (part == 0 && (rloc & 1) == 0 && row < nrows) mk_epilogue(a, c, p, layer, tag, row, true, v, v1, best);
                 } else {
-                    const int row1 = has2 ? row + 1 : row;     // a missing partner re-reads the first row
-                    v0 = row_dot_q<FMT>(base + (size_t)row * rqb, dbase + (size_t)row * nb, seg, lane, xq);
-                    v1 = row_dot_q<FMT>(base + (size_t)row1 * rqb, dbase + (size_t)row1 * nb, seg, lane, xq);
-                }
-                warp_sum2(v0, v1, lane);
-                if (lane == 0) {
-                    if (direct) {
-                        mk_epilogue(a, c, p, layer, tag, r + row, has2, v0, v1, best);
-                    } else {
-                        c.part()[(r + row - pend0) * MK_NW + seg] = v0;
-                        if (has2) c.part()[(r + row + 1 - pend0) * MK_NW + seg] = v1;
-                    }
+                    if (part == 0 && row < nrows) mk_epilogue(a, c, p, layer, tag, row, false, v, 0.f, best);
                 }
             }
-            carry = li - npair;
+            carry = tl - nt;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&c.empty()[slot]);
         c.advance();
-        if (!direct) {
-            const int done_rows = r + nr;
-            const bool last = r + rpe >= nrows;
-            if (last || (done_rows - pend0) + rpe > CAP) {
-                consumer_sync();
-                for (int row = pend0 + 2 * (int)threadIdx.x; row < done_rows; row += 2 * MK_CONSUMERS) {
-                    const bool has2 = row + 1 < done_rows;
-                    float v0 = 0.f, v1 = 0.f;
-                    for (int sg = 0; sg < S; sg++) {
-                        v0 += c.part()[(row - pend0) * MK_NW + sg];
-                        if (has2) v1 += c.part()[(row + 1 - pend0) * MK_NW + sg];
-                    }
-                    mk_epilogue(a, c, p, layer, tag, row, has2, v0, v1, best);
-                }
-                consumer_sync();
-                pend0 = done_rows;
-            }
-        }
     }
 }
 
@@ -865,7 +761,7 @@ __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int
 // 1/sqrt(mean(h^2) + eps), which callers fold into the activation registers.  One barrier.
 enum : int { SRC_POLL = 0, SRC_EMBED = 1, SRC_PLAIN = 2 };
 __device__ __forceinline__ float mk_stage_norm(const MegaArgs& a, MkCtx& c, int src_kind, const Tagged* xsrc,
-                                               unsigned int tag, int token, const float* norm_w, bool quant) {
+                                               unsigned int tag, int token, const float* norm_w, bool quant, bool quant_sum) {
     float ss = 0.f;
     for (int i0 = 0; i0 < a.dim; i0 += 2 * MK_CONSUMERS) {
         const int i = i0 + 2 * (int)threadIdx.x;
@@ -889,7 +785,7 @@ __device__ __forceinline__ float mk_stage_norm(const MegaArgs& a, MkCtx& c, int 
             ss = fmaf(v1, v1, ss);
         }
         if (quant) {
-            xq_store_pair(c, a.dim, i, ok, v0 * nw.x, v1 * nw.y);
+            xq_store_pair(c, a.dim, i, ok, v0 * nw.x, v1 * nw.y, quant_sum);
         } else if (ok) {
             c.xs()[i] = v0 * nw.x;
             c.xs()[i + 1] = v1 * nw.y;
@@ -972,11 +868,20 @@ __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int la
     }
     consumer_sync();
 
-    // ---- scores ----
+    // ---- scores: thread t owns position t; the new position's K row comes from shared memory ----
     const int len = pos + 1;
     const float scale = rsqrtf((float)HD);
     float mx = -INFINITY;
-    if (tid < pos) {
+    if (tid == pos) {
+#pragma unroll
+        for (int i = 0; i < KV; i++) {
+            const float4 ka = reinterpret_cast<const float4*>(kn)[2 * i], kb = reinterpret_cast<const float4*>(kn)[2 * i + 1];
+            __half2 h[4] = {__floats2half2_rn(ka.x, ka.y), __floats2half2_rn(ka.z, ka.w), __floats2half2_rn(kb.x, kb.y),
+                            __floats2half2_rn(kb.z, kb.w)};      // exact: kn already holds fp16-rounded values
+            kreg[i] = *reinterpret_cast<const uint4*>(h);
+        }
+    }
+    if (tid <= pos) {
         float dot = 0.f;
 #pragma unroll
         for (int i = 0; i < KV; i++) dot += dot8_kq(kreg[i], qs + 8 * i);
@@ -984,23 +889,20 @@ __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int la
         c.sc()[tid] = dot;
         mx = dot;
     }
-    for (int t = tid + MK_CONSUMERS; t < pos; t += MK_CONSUMERS) {     // contexts beyond one row per thread
-        const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)t * a.kv_dim);
-        uint4 kk[KV];
-#pragma unroll
-        for (int i = 0; i < KV; i++) kk[i] = __ldcg(kp + i);
+    for (int t = tid + MK_CONSUMERS; t <= pos; t += MK_CONSUMERS) {     // contexts beyond one row per thread
         float dot = 0.f;
+        if (t == pos) {
+            for (int d = 0; d < HD; d++) dot = fmaf(qs[d], kn[d], dot);
+        } else {
+            const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)t * a.kv_dim);
+            uint4 kk[KV];
 #pragma unroll
-        for (int i = 0; i < KV; i++) dot += dot8_kq(kk[i], qs + 8 * i);
+            for (int i = 0; i < KV; i++) kk[i] = __ldcg(kp + i);
+#pragma unroll
+            for (int i = 0; i < KV; i++) dot += dot8_kq(kk[i], qs + 8 * i);
+        }
         dot *= scale;
         c.sc()[t] = dot;
-        mx = fmaxf(mx, dot);
-    }
-    if (tid == 0) {                                                     // the new position, from shared memory
-        float dot = 0.f;
-        for (int d = 0; d < HD; d++) dot = fmaf(qs[d], kn[d], dot);
-        dot *= scale;
-        c.sc()[pos] = dot;
         mx = fmaxf(mx, dot);
     }
     mx = warp_max(mx);
@@ -1115,7 +1017,8 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
                 const float* nw = is_head ? a.final_norm : a.norms + (size_t)l * 2 * a.dim;
                 if (p == PH_GU) { src = a.xhm; tag = base + 3; nw += a.dim; }
                 else if (p == PH_QKV && l == a.ls) kind = a.embed ? SRC_EMBED : SRC_PLAIN;
-                scale = mk_stage_norm(a, c, kind, src, tag, token, nw, (is_head ? a.head_fmt : a.layer_fmt) != FMT_F16);
+                scale = mk_stage_norm(a, c, kind, src, tag, token, nw, (is_head ? a.head_fmt : a.layer_fmt) != FMT_F16,
+                                      (is_head ? a.head_fmt : a.layer_fmt) == FMT_Q4_0);
             } else {
                 if (p == PH_WO && (int)blockIdx.x < a.n_heads) {
                     if (a.head_dim == 64) mk_attention<64>(a, c, l, pos, base + 1, base + 2);
@@ -1124,7 +1027,7 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
                     mk_trace(a, step, l * 10 + 9);
                 }
                 const bool wo = p == PH_WO;
-                if (a.layer_fmt != FMT_F16) mk_gather_q(c, wo ? a.xattn : a.xmid, wo ? base + 2 : base + 4, wo ? a.dim : a.ffn_dim);
+                if (a.layer_fmt != FMT_F16) mk_gather_q(c, wo ? a.xattn : a.xmid, wo ? base + 2 : base + 4, wo ? a.dim : a.ffn_dim, a.layer_fmt == FMT_Q4_0);
                 else mk_gather(c, wo ? a.xattn : a.xmid, wo ? base + 2 : base + 4, c.xs(), wo ? a.dim : a.ffn_dim);
                 consumer_sync();
             }
@@ -1205,8 +1108,6 @@ __global__ void __launch_bounds__(MK_THREADS, 1) mega_decode_kernel(const MegaAr
             const int ib = item_begin(sh.items, blockIdx.x, gridDim.x);
             c.phase_tab()[p] = ib;
             c.phase_tab()[8 + p] = item_begin(sh.items, blockIdx.x + 1, gridDim.x) - ib;
-            c.phase_tab()[16 + p] = rows_per_entry(sh.fmt, sh.K);
-            c.phase_tab()[24 + p] = MK_NW / ((sh.K + 1023) / 1024);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
