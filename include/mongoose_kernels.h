@@ -228,10 +228,10 @@ MG_API int mg_dequant_rows(mg_engine* e, int idx, int row0, int nrows, float* ou
 MG_API int mg_read_kv(mg_engine* e, int layer, int pos0, int npos, uint16_t* k_out, uint16_t* v_out);
 /* Per-phase timeline of ONE greedy step from the current cursor (the counterpart of the reference's
  * per-op [PROFILE] timing at pos 1, cuda_fused_infer_q4.go:147-242).  stamps receives
- * [n_ctas][n_events] SM clock values of each CTA's first thread: per layer, ten stamps (layer start,
- * after the QKV input stage, after QKV, before/after attention, wo input ready, after wo, gate/up input
- * ready, after gate/up, down input ready -> after down), then two for lm_head.  Needs the persistent
- * kernel; capacity is in stamps. */
+ * [n_ctas][n_events] SM clock values of each CTA's first thread, n_events = n_layers*10 + 2: per layer,
+ * event 2p = input of phase p staged, 2p+1 = phase p done (p: 0 QKV, 1 wo, 2 gate/up, 3 down),
+ * 8 = layer start, 9 = attention done (CTAs that run a head); then lm_head input staged / done.
+ * Needs the persistent kernel; capacity is in stamps. */
 MG_API int mg_trace_step(mg_engine* e, long long* stamps, int capacity, int* n_ctas, int* n_events);
 /* The stream the engine enqueues on (for event timing by the caller). */
 MG_API cudaStream_t mg_stream(mg_engine* e);
