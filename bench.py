@@ -41,6 +41,9 @@ from mongoose_b200 import multi  # noqa: E402
 from mongoose_b200 import synthetic  # noqa: E402
 
 PROMPT_LEN = 32
+# DRAM bytes per decoded token (dram__bytes_read.sum + dram__bytes_write.sum of mega_decode_kernel from one
+# ncu capture of a 3-token launch, divided by 3; profiles/mega_decode_kernel_qwen05b_q8.md).
+NCU_TRAFFIC_PER_TOKEN = {"qwen2.5-0.5b-q8_0-b1": 592.4e6}
 WORKLOADS = {
     "qwen2.5-0.5b-q8_0-b1": mc.QWEN25_05B,
     "qwen2.5-0.5b-q4_0-b1": mc.QWEN25_05B_Q4,
@@ -285,7 +288,8 @@ def run_b200_arm(args, cfg, rank, world, local_rank):
                     "last_token_matches_device_loop": bool(e2e_last_tok == tok_last)},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_PER_TOKEN.get(args.workload),
+                         "traffic_unit": "bytes per token (one launch decodes all timed tokens)", "peak_source": peak_src,
                          "kernel": "whole decode step (mega_decode_kernel: one persistent launch for all timed tokens)",
                          "algorithmic_bytes_per_token": bytes_tok, "frac_of_8TBs": achieved / 8000.0},
             "clocks": clocks,
