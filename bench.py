@@ -139,7 +139,9 @@ def cpu_baseline_run(cfg, max_steps: int, nthreads: int, budget_s: float = 25.0,
         else:
             om.set_weight(idx, O.quantize(fmt, synthetic.tensor_f32(seed, idx, rows, cols)), fmt)
     prompt = synthetic.prompt_ids(seed, PROMPT_LEN, cfg.vocab)
-    nthreads = max(1, min(nthreads, O.max_threads()))
+    # the thread count is passed to the OpenMP region explicitly: launchers such as torchrun export
+    # OMP_NUM_THREADS=1, which must not silently turn the all-cores arm into a single-threaded one
+    nthreads = max(1, nthreads)
     tok = int(prompt[0])
     om.cpu_engine_step_token(tok, 0, nthreads)          # pages the weights in
     t0 = time.perf_counter()
@@ -160,7 +162,7 @@ def run_reference_arm(args, cfg, rank):
     """The reference's CPU implementation of the path, timed on the host cores (rank 0 only)."""
     if rank != 0:
         return
-    ncores = os.cpu_count() or 1
+    ncores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     cfg = cfg.with_(max_seq=max(cfg.max_seq, args.steps + 2))
     tps, dt, threads, sample = cpu_baseline_run(cfg, args.steps, ncores, budget_s=40.0)
     line = {
