@@ -48,6 +48,10 @@ WORKLOADS = {
     "qwen2.5-0.5b-q8_0-b1": mc.QWEN25_05B,
     "qwen2.5-0.5b-q4_0-b1": mc.QWEN25_05B_Q4,
     "tiny-q8_0-b1": mc.TINY,
+    # 64 independent sequences (512-token prompt + 512 decode steps each in the full configuration),
+    # sequence i on GPU i mod G, each decoded with batch-1 semantics as the reference would (one
+    # engine pass per token); select sizes with --sequences / --prompt-len / --steps
+    "tinyllama-1.1b-q8_0-seqs": mc.TINYLLAMA_11B,
 }
 FMT_NAME = {mc.FMT_Q8_0: "q8_0", mc.FMT_Q4_0: "q4_0", mc.FMT_F16: "f16"}
 
@@ -60,6 +64,7 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="qwen2.5-0.5b-q8_0-b1", choices=sorted(WORKLOADS))
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
+    ap.add_argument("--sequences", type=int, default=8, help="sequences of the *-seqs workload (full config: 64)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--cpu-steps", type=int, default=0, help="steps of the CPU baseline sample (0 = auto)")
@@ -309,6 +314,71 @@ def run_b200_arm(args, cfg, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_sequences_arm(args, cfg, rank, world, local_rank):
+    """Independent sequences sharded over the GPUs (sequence i on rank i mod G), no communication.
+    A step is one decoded token of one sequence; value counts prompt and generated tokens alike,
+    because the prompt goes through the same decode path."""
+    import torch
+    from mongoose_b200.fused_infer import CUDAFusedInference
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    P, K = args.prompt_len, args.steps
+    cfg = cfg.with_(max_seq=P + K)
+    eng = CUDAFusedInference(cfg, device=local_rank)
+    synthetic.load_engine(eng, cfg, seed=0)
+    eng.BuildFusedDispatch()
+    mine = multi.sequences_for_rank(args.sequences, rank, world)
+    stream = torch.cuda.ExternalStream(eng.stream, device=local_rank)
+    for _ in range(max(args.warmup, 3)):
+        eng.StepToken(1, 0)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    sampler.start()
+    launches0 = eng.LaunchCount()
+    ev0.record(stream)
+    tails = []
+    for sidx in mine:
+        eng.ResetKV()
+        toks = eng.Generate(synthetic.prompt_ids(sidx, P, cfg.vocab), K)
+        tails.append(int(toks[-1]))
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    clocks = sampler.stop()
+    ms_max, = multi.reduce_max([ev0.elapsed_time(ev1)], dist, device="cuda")
+    if rank == 0:
+        tokens_total = args.sequences * (P + K - 1)
+        tps = tokens_total / (ms_max / 1e3)
+        per_gpu_seq = len(mine)
+        bytes_tok = mc.weight_bytes_per_token(cfg) + mc.kv_bytes_per_position(cfg) * (P + K) / 2.0
+        peak, peak_src = measured_peak_gbs()
+        achieved = bytes_tok * (per_gpu_seq * (P + K - 1)) / (ms_max / 1e3) / 1e9
+        print(json.dumps({
+            "metric": "decode_tokens_per_s", "value": tps, "unit": "tok/s", "n_gpus": world, "steps": K,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_max / max(1, per_gpu_seq * (P + K - 1)),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": FMT_NAME[cfg.layer_fmt],
+            "data": "synthetic",
+            "config": {"workload": args.workload, "sequences": args.sequences, "prompt_len": P, "decode_steps": K,
+                       "batch": "1 per sequence, sequences sharded i mod G", "l2": "inputs larger than L2"},
+            "gpu_launches": int(eng.LaunchCount() - launches0),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src, "kernel": "whole decode step",
+                         "algorithmic_bytes_per_token": bytes_tok},
+            "clocks": clocks, "tokens_tail": tails[:4]}), flush=True)
+    eng.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     global PROMPT_LEN
     args = parse_args()
@@ -317,6 +387,9 @@ def main():
     cfg = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference_arm(args, cfg, rank)
+        return
+    if args.workload.endswith("-seqs"):
+        run_sequences_arm(args, cfg, rank, world, local_rank)
         return
     run_b200_arm(args, cfg, rank, world, local_rank)
 

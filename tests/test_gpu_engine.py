@@ -12,7 +12,12 @@ pytestmark = pytest.mark.gpu
 SMALL = [mc.TINY, mc.TINY_Q4,
          mc.TINY.with_(name="tiny-hd64", dim=256, n_heads=4, n_kv_heads=1, head_dim=64, ffn_dim=416, vocab=777),
          mc.TINY.with_(name="tiny-hd128-f16", dim=256, n_heads=2, n_kv_heads=2, head_dim=128, ffn_dim=160,
-                       vocab=130, layer_fmt=mc.FMT_F16, head_fmt=mc.FMT_Q4_0)]
+                       vocab=130, layer_fmt=mc.FMT_F16, head_fmt=mc.FMT_Q4_0),
+         # TinyLlama-1.1B and Qwen2.5-0.5B widths (inputs wider than one 1024 segment, uneven rows per SM)
+         # with two layers and a cut vocabulary so that the CPU oracle stays fast
+         mc.TINYLLAMA_11B.with_(name="tinyllama-width-2L", n_layers=2, vocab=4000, max_seq=48),
+         mc.QWEN25_05B.with_(name="qwen-width-2L-q4", n_layers=2, vocab=3000, max_seq=48, layer_fmt=mc.FMT_Q4_0,
+                             head_fmt=mc.FMT_Q4_0)]
 
 
 @pytest.fixture(params=SMALL, ids=lambda c: c.name)
