@@ -48,6 +48,7 @@ WORKLOADS = {
     "qwen2.5-0.5b-q8_0-b1": mc.QWEN25_05B,
     "qwen2.5-0.5b-q4_0-b1": mc.QWEN25_05B_Q4,
     "tiny-q8_0-b1": mc.TINY,
+    "qwen2.5-7b-q8_0-b1": mc.QWEN25_7B,
     # 64 independent sequences (512-token prompt + 512 decode steps each in the full configuration),
     # sequence i on GPU i mod G, each decoded with batch-1 semantics as the reference would (one
     # engine pass per token); select sizes with --sequences / --prompt-len / --steps

@@ -16,6 +16,9 @@ SMALL = [mc.TINY, mc.TINY_Q4,
          # TinyLlama-1.1B and Qwen2.5-0.5B widths (inputs wider than one 1024 segment, uneven rows per SM)
          # with two layers and a cut vocabulary so that the CPU oracle stays fast
          mc.TINYLLAMA_11B.with_(name="tinyllama-width-2L", n_layers=2, vocab=4000, max_seq=48),
+         # 7B-class width (head_dim 128, K = 18944): too wide for the persistent kernel's ring, so this case
+         # runs the graph of fused kernels
+         mc.QWEN25_7B.with_(name="qwen7b-width-1L", n_layers=1, vocab=2000, max_seq=48),
          mc.QWEN25_05B.with_(name="qwen-width-2L-q4", n_layers=2, vocab=3000, max_seq=48, layer_fmt=mc.FMT_Q4_0,
                              head_fmt=mc.FMT_Q4_0)]
 
