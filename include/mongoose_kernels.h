@@ -233,6 +233,27 @@ MG_API int mg_read_kv(mg_engine* e, int layer, int pos0, int npos, uint16_t* k_o
  * 8 = layer start, 9 = attention done (CTAs that run a head); then lm_head input staged / done.
  * Needs the persistent kernel; capacity is in stamps. */
 MG_API int mg_trace_step(mg_engine* e, long long* stamps, int capacity, int* n_ctas, int* n_events);
+/* ---- tensor-parallel decode over 2/4/8 GPUs of one node, one process per GPU ----------------------
+ * The reference has no tensor parallelism (multigpu.go:32-82, 496-623 manages per-device handles and
+ * peer copies only); these calls split one model over ranks.  QKV, gate and up are split by rows at
+ * whole-head granularity, wo and down by columns (partial sums), lm_head by vocabulary rows; the KV
+ * cache follows its heads.  Per token: two all-reduces of dim fp32 per layer, one all-reduce of the
+ * packed (logit, index) argmax key, and an all-gather of logits when logits are asked for.
+ * Every rank calls mg_set_weight / mg_set_weight_raw with the FULL tensor and keeps its part. */
+typedef struct mg_tp_shard {
+    int q_head0, q_head1;     /* query heads [q_head0, q_head1) */
+    int kv_head0, kv_head1;   /* KV heads that serve them (a KV head may be replicated on several ranks) */
+    int ffn0, ffn1;           /* FFN features, multiples of 32 */
+    int vocab0, vocab1;       /* lm_head rows */
+} mg_tp_shard;
+/* The partition rank `rank` of `size` would hold; pure host arithmetic, needs no GPU.
+ * MG_ERR_UNSUPPORTED when the KV heads neither divide among the ranks nor are divided by them. */
+MG_API int mg_tp_partition(const mg_config* cfg, int rank, int size, mg_tp_shard* out);
+/* A fresh 128-byte communicator id (rank 0 makes it and hands it to the other ranks by any means). */
+MG_API int mg_tp_unique_id(void* id_out, size_t bytes);
+/* Joins the communicator; collective over all ranks.  Call once, after mg_create and before any
+ * weight is set.  NCCL is resolved from libnccl.so.2 at this point, not at load time. */
+MG_API int mg_tp_init(mg_engine* e, int rank, int size, const void* id, size_t bytes);
 /* The stream the engine enqueues on (for event timing by the caller). */
 MG_API cudaStream_t mg_stream(mg_engine* e);
 /* Kernels launched by this engine since creation (graph replays count their kernel nodes). */

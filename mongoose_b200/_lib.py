@@ -24,6 +24,12 @@ class MgConfig(C.Structure):
                 ("device", ci), ("max_batch", ci), ("flags", ci)]
 
 
+class MgTpShard(C.Structure):
+    """struct mg_tp_shard of include/mongoose_kernels.h."""
+    _fields_ = [("q_head0", ci), ("q_head1", ci), ("kv_head0", ci), ("kv_head1", ci),
+                ("ffn0", ci), ("ffn1", ci), ("vocab0", ci), ("vocab1", ci)]
+
+
 # name -> (restype, argtypes): every symbol include/mongoose_kernels.h declares.
 SIGNATURES = {
     # reference ABI (stream is the last argument everywhere)
@@ -74,6 +80,9 @@ SIGNATURES = {
     "mg_dequant_rows": (ci, [vp, ci, ci, ci, vp]),
     "mg_read_kv": (ci, [vp, ci, ci, ci, vp, vp]),
     "mg_trace_step": (ci, [vp, vp, ci, vp, vp]),
+    "mg_tp_partition": (ci, [vp, ci, ci, vp]),
+    "mg_tp_unique_id": (ci, [vp, sz]),
+    "mg_tp_init": (ci, [vp, ci, ci, vp, sz]),
     "mg_stream": (vp, [vp]),
     "mg_launch_count": (C.c_longlong, [vp]),
     "mg_device_bytes": (sz, [vp]),

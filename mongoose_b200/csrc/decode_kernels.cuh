@@ -61,6 +61,8 @@ struct PhaseArgs {
     int head_dim;
     int kv_dim;
     int* out_tokens;
+    int row_base;         // LOGITS: global index of local row 0 (vocab-sharded lm_head)
+    int defer_finalize;   // LOGITS: leave the cursor update to finalize_step_kernel (argmax still to be reduced over ranks)
 };
 
 __device__ __forceinline__ unsigned long long pack_best(float v, unsigned int idx) {
@@ -338,7 +340,7 @@ __global__ void __launch_bounds__(256) phase_kernel(const PhaseArgs a) {
                                 const int row = it * R + r;
                                 if (row < a.rows[0]) {
                                     if (a.out) a.out[row] = acc[r];
-                                    const unsigned long long key = pack_best(acc[r], (unsigned)row);
+                                    const unsigned long long key = pack_best(acc[r], (unsigned)(row + a.row_base));
                                     if (key > best) best = key;
                                 }
                             }
@@ -367,7 +369,9 @@ __global__ void __launch_bounds__(256) phase_kernel(const PhaseArgs a) {
             if (b) atomicMax(&s->best, b);
             __threadfence();
             const unsigned int ticket = atomicAdd(&s->done, 1u);
-            if (ticket == gridDim.x - 1) {
+            if (ticket == gridDim.x - 1 && a.defer_finalize) {
+                s->done = 0u;
+            } else if (ticket == gridDim.x - 1) {
                 __threadfence();
                 const unsigned long long key = atomicMax(&s->best, 0ull);
                 const int tok = (int)(0xffffffffu - (unsigned int)(key & 0xffffffffull));
@@ -380,6 +384,17 @@ __global__ void __launch_bounds__(256) phase_kernel(const PhaseArgs a) {
             }
         }
     }
+}
+
+// Cursor update after the running argmax has been combined over tensor-parallel ranks.
+__global__ void finalize_step_kernel(StepState* s, int* out_tokens) {
+    const unsigned long long key = s->best;
+    const int tok = (int)(0xffffffffu - (unsigned int)(key & 0xffffffffull));
+    if (out_tokens && s->step < s->out_cap) out_tokens[s->step] = tok;
+    s->token = tok;
+    s->step += 1;
+    s->pos += 1;
+    s->best = 0ull;
 }
 
 // ---------------------------------------------------------------------

@@ -11,6 +11,8 @@
 // [layers][max_seq][kv_dim]; activations fp32.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
 
 #include <algorithm>
 #include <cmath>
@@ -50,6 +52,27 @@ struct GraphKey {
 struct CachedGraph {
     cudaGraphExec_t exec = nullptr;
     int kernels = 0;
+};
+
+// The part of the model one tensor-parallel rank holds.  With size == 1 it is the whole model.
+// Q heads [q0, q1) with the KV heads [kv0, kv1) that serve them, FFN features [f0, f1),
+// vocabulary rows [v0, v1).
+struct Shard {
+    int rank = 0, size = 1;
+    int q0 = 0, q1 = 0, kv0 = 0, kv1 = 0, f0 = 0, f1 = 0, v0 = 0, v1 = 0;
+    int v_stride = 0;                   // rows per rank in the gathered logits (ceil(vocab / size))
+};
+
+// NCCL entry points, resolved from the already-loaded libnccl.so.2 when tensor parallelism is
+// switched on; a single-GPU user never needs the library.
+struct NcclApi {
+    void* lib = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
 };
 
 }  // namespace
@@ -93,6 +116,12 @@ struct mg_engine {
     long long launches = 0;
     int capture_kernels = 0;            // kernels enqueued by the current enqueue_step
     size_t dev_bytes = 0;
+    // tensor parallelism (mg_tp_init)
+    Shard sh;
+    ncclComm_t comm = nullptr;
+    float* zero_vec = nullptr;          // residual input of the ranks other than 0 (the all-reduce adds rank 0's)
+    float* logits_all = nullptr;        // gathered logits, [size][v_stride]
+    bool any_weight_set = false;
     std::string err;
 };
 
@@ -153,6 +182,91 @@ bool slot_info(const mg_config& c, int idx, bool* is_matrix, int* rows, int* col
     return true;
 }
 
+// Tensor-parallel partition of one rank.  Q heads stay whole; when the ranks outnumber the KV
+// heads, size / n_kv_heads consecutive ranks share one KV head (each keeps a copy of its K/V rows
+// and cache) and split that head's Q group between them, earlier ranks taking the larger part.
+// FFN features are split in multiples of 32 so that no quantization block straddles two ranks.
+bool make_shard(const mg_config& c, int rank, int size, Shard* out, std::string* why) {
+    Shard s;
+    s.rank = rank; s.size = size;
+    if (size < 1 || rank < 0 || rank >= size) { *why = "rank outside [0, size)"; return false; }
+    const int group = c.n_heads / c.n_kv_heads;
+    if (c.n_kv_heads % size == 0) {
+        const int kvn = c.n_kv_heads / size;
+        s.kv0 = rank * kvn; s.kv1 = s.kv0 + kvn;
+        s.q0 = s.kv0 * group; s.q1 = s.kv1 * group;
+    } else if (size % c.n_kv_heads == 0 && group >= size / c.n_kv_heads) {
+        const int m = size / c.n_kv_heads, kv = rank / m, j = rank % m;
+        const int base = group / m, extra = group % m;
+        s.kv0 = kv; s.kv1 = kv + 1;
+        s.q0 = kv * group + j * base + (j < extra ? j : extra);
+        s.q1 = s.q0 + base + (j < extra ? 1 : 0);
+    } else {
+        *why = "the KV heads neither divide among the ranks nor are divided by them";
+        return false;
+    }
+    const int fb = c.ffn_dim / 32;
+    if (fb < size) { *why = "fewer FFN blocks than ranks"; return false; }
+    const int fbase = fb / size, fextra = fb % size;
+    s.f0 = 32 * (rank * fbase + (rank < fextra ? rank : fextra));
+    s.f1 = s.f0 + 32 * (fbase + (rank < fextra ? 1 : 0));
+    s.v_stride = (c.vocab + size - 1) / size;
+    s.v0 = std::min(c.vocab, rank * s.v_stride);
+    s.v1 = std::min(c.vocab, s.v0 + s.v_stride);
+    *out = s;
+    return true;
+}
+
+NcclApi g_nccl;
+
+bool load_nccl(std::string* why) {
+    if (g_nccl.AllReduce) return true;
+    void* lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!lib) lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!lib) { *why = std::string("libnccl.so.2 not found: ") + dlerror(); return false; }
+    NcclApi a;
+    a.lib = lib;
+    a.GetUniqueId = (decltype(a.GetUniqueId))dlsym(lib, "ncclGetUniqueId");
+    a.CommInitRank = (decltype(a.CommInitRank))dlsym(lib, "ncclCommInitRank");
+    a.CommDestroy = (decltype(a.CommDestroy))dlsym(lib, "ncclCommDestroy");
+    a.AllReduce = (decltype(a.AllReduce))dlsym(lib, "ncclAllReduce");
+    a.AllGather = (decltype(a.AllGather))dlsym(lib, "ncclAllGather");
+    a.GetErrorString = (decltype(a.GetErrorString))dlsym(lib, "ncclGetErrorString");
+    if (!a.GetUniqueId || !a.CommInitRank || !a.CommDestroy || !a.AllReduce || !a.AllGather || !a.GetErrorString) {
+        *why = "libnccl.so.2 lacks an expected symbol";
+        return false;
+    }
+    g_nccl = a;
+    return true;
+}
+
+#define MG_NCCL(e, call)                                                                          \
+    do {                                                                                          \
+        ncclResult_t _r = (call);                                                                 \
+        if (_r != ncclSuccess)                                                                    \
+            return fail((e), MG_ERR_CUDA, "%s failed: %s (%s:%d)", #call, g_nccl.GetErrorString(_r), \
+                        __FILE__, __LINE__);                                                      \
+    } while (0)
+
+// Sub-rectangle of weight slot idx that this rank keeps: rows [r0, r1) x columns [k0, k1).
+void shard_rect(const mg_engine* e, int idx, int rows, int cols, int* r0, int* r1, int* k0, int* k1) {
+    const mg_config& c = e->cfg;
+    const Shard& s = e->sh;
+    *r0 = 0; *r1 = rows; *k0 = 0; *k1 = cols;
+    if (s.size == 1 || idx >= c.n_layers * 12) return;   // the head keeps every row: it is also the embedding table
+    const int hd = c.head_dim;
+    switch (idx % 12) {
+        case 1: *r0 = s.q0 * hd; *r1 = s.q1 * hd; break;
+        case 2: case 3: *r0 = s.kv0 * hd; *r1 = s.kv1 * hd; break;
+        case 4: *k0 = s.q0 * hd; *k1 = s.q1 * hd; break;
+        case 5: case 6: *k0 = s.kv0 * hd; *k1 = s.kv1 * hd; break;
+        case 7: *k0 = s.q0 * hd; *k1 = s.q1 * hd; break;
+        case 9: case 10: *r0 = s.f0; *r1 = s.f1; break;
+        case 11: *k0 = s.f0; *k1 = s.f1; break;
+        default: break;
+    }
+}
+
 size_t raw_row_bytes(int fmt, int K) {
     return fmt == FMT_Q8_0 ? (size_t)(K / 32) * 34 : fmt == FMT_Q4_0 ? (size_t)(K / 32) * 18 : (size_t)K * 2;
 }
@@ -163,10 +277,11 @@ inline int round_half_away(float v) { return (int)(v + (v > 0 ? 0.5f : -0.5f)); 
 // Q8_0: d = amax/127 per block of 32, q = round-half-away(v * 127/amax), clamp +-127.
 // Q4_0: d = amax/8, nib = round-half-away(v * 8/amax) + 8, clamp 0..15, byte j = elem j | elem j+16 << 4.
 // d is stored as fp16 (round to nearest even); the quants use the unrounded fp32 ratio.
-void quantize_planes(int fmt, const float* w, int rows, int K, uint8_t* qs, unsigned short* ds) {
+// `w` points at the first kept element; consecutive source rows are `ld` floats apart.
+void quantize_planes(int fmt, const float* w, size_t ld, int rows, int K, uint8_t* qs, unsigned short* ds) {
     const int nb = K / 32;
     for (int r = 0; r < rows; r++) {
-        const float* src = w + (size_t)r * K;
+        const float* src = w + (size_t)r * ld;
         if (fmt == FMT_F16) {
             __half* o = reinterpret_cast<__half*>(qs) + (size_t)r * K;
             for (int k = 0; k < K; k++) o[k] = __float2half_rn(src[k]);
@@ -207,20 +322,23 @@ void quantize_planes(int fmt, const float* w, int rows, int K, uint8_t* qs, unsi
     }
 }
 
-// Split raw 34/18-byte blocks into the two planes.
-void split_raw_blocks(int fmt, const uint8_t* raw, int rows, int K, uint8_t* qs, unsigned short* ds) {
+// Split raw 34/18-byte blocks into the two planes.  `raw` points at the first kept block (or
+// half); consecutive source rows are `ld_bytes` apart; K is the kept width.
+void split_raw_blocks(int fmt, const uint8_t* raw, size_t ld_bytes, int rows, int K, uint8_t* qs, unsigned short* ds) {
     const int nb = K / 32;
     if (fmt == FMT_F16) {
-        memcpy(qs, raw, (size_t)rows * K * 2);
+        for (int r = 0; r < rows; r++) memcpy(qs + (size_t)r * K * 2, raw + (size_t)r * ld_bytes, (size_t)K * 2);
         return;
     }
     const int bb = fmt == FMT_Q8_0 ? 34 : 18;
     const int qb = bb - 2;
-    for (size_t i = 0; i < (size_t)rows * nb; i++) {
-        const uint8_t* blk = raw + i * bb;
-        memcpy(&ds[i], blk, 2);
-        memcpy(qs + i * qb, blk + 2, qb);
-    }
+    for (int r = 0; r < rows; r++)
+        for (int b = 0; b < nb; b++) {
+            const uint8_t* blk = raw + (size_t)r * ld_bytes + (size_t)b * bb;
+            const size_t i = (size_t)r * nb + b;
+            memcpy(&ds[i], blk, 2);
+            memcpy(qs + i * qb, blk + 2, qb);
+        }
 }
 
 int upload_planes(mg_engine* e, int idx, int fmt, int rows, int K, const std::vector<uint8_t>& qs,
@@ -336,17 +454,25 @@ enum { HEAD_NONE = 0, HEAD_ARGMAX = 1, HEAD_LOGITS = 2 };
 // (cuda_fused_infer.go:414-451) with its 17 launches per layer fused into 5.
 int enqueue_step(mg_engine* e, cudaStream_t s, int ls, int le, int mode, int head) {
     const mg_config& c = e->cfg;
+    const Shard& sh = e->sh;
     const int L = c.n_layers;
+    const bool tp = sh.size > 1;
+    // this rank's share of the model (the whole of it without tensor parallelism)
+    const int n_heads = sh.q1 - sh.q0, n_kv = sh.kv1 - sh.kv0;
+    const int q_dim = n_heads * c.head_dim, kv_dim = n_kv * c.head_dim;
+    const int ffn = sh.f1 - sh.f0, vocab = sh.v1 - sh.v0;
+    const float* resid_h = (tp && sh.rank != 0) ? e->zero_vec : e->h;     // rank 0 alone adds the residual;
+    const float* resid_h2 = (tp && sh.rank != 0) ? e->zero_vec : e->h2;   // the all-reduce sums it in once
     e->capture_kernels = 0;
     for (int l = ls; l < le && l < L; l++) {
         const int b = l * 12;
-        const size_t kvoff = (size_t)l * c.max_seq * c.kv_dim;
+        const size_t kvoff = (size_t)l * c.max_seq * kv_dim;
         {   // RMSNorm + QKV + bias + RoPE + KV append
             PhaseArgs a{};
             a.w[0] = e->mats[b + 1].view(); a.w[1] = e->mats[b + 2].view(); a.w[2] = e->mats[b + 3].view();
-            a.rows[0] = c.dim; a.rows[1] = c.kv_dim; a.rows[2] = c.kv_dim;
+            a.rows[0] = q_dim; a.rows[1] = kv_dim; a.rows[2] = kv_dim;
             a.K = c.dim;
-            a.nitems = (c.dim + 2 * c.kv_dim) / 2;
+            a.nitems = (q_dim + 2 * kv_dim) / 2;
             const bool embed = (mode == MODE_EMBED && l == 0);
             a.pro = embed ? PRO_RMS_EMBED : PRO_RMS;
             a.x_src = e->h;
@@ -361,7 +487,7 @@ int enqueue_step(mg_engine* e, cudaStream_t s, int ls, int le, int mode, int hea
             a.k_cache = e->kc + kvoff;
             a.v_cache = e->vc + kvoff;
             a.cos_tab = e->cos_tab; a.sin_tab = e->sin_tab;
-            a.head_dim = c.head_dim; a.kv_dim = c.kv_dim;
+            a.head_dim = c.head_dim; a.kv_dim = kv_dim;
             int rc = launch_phase(e, s, c.layer_fmt, EPI_QKV, 2, a);
             if (rc) return rc;
         }
@@ -370,64 +496,77 @@ int enqueue_step(mg_engine* e, cudaStream_t s, int ls, int le, int mode, int hea
             if (smem > (size_t)kMaxDynSmem) return fail(e, MG_ERR_UNSUPPORTED, "max_seq %d too large", c.max_seq);
             cudaError_t ce;
             if (c.head_dim == 64)
-                ce = launch(e, s, attn_decode_kernel<64>, c.n_heads, 256, smem, (const float*)e->q,
+                ce = launch(e, s, attn_decode_kernel<64>, n_heads, 256, smem, (const float*)e->q,
                             (const __half*)(e->kc + kvoff), (const __half*)(e->vc + kvoff), e->attn,
-                            (const StepState*)e->st, c.kv_dim, c.n_heads, c.n_kv_heads);
+                            (const StepState*)e->st, kv_dim, n_heads, n_kv);
             else if (c.head_dim == 128)
-                ce = launch(e, s, attn_decode_kernel<128>, c.n_heads, 256, smem, (const float*)e->q,
+                ce = launch(e, s, attn_decode_kernel<128>, n_heads, 256, smem, (const float*)e->q,
                             (const __half*)(e->kc + kvoff), (const __half*)(e->vc + kvoff), e->attn,
-                            (const StepState*)e->st, c.kv_dim, c.n_heads, c.n_kv_heads);
+                            (const StepState*)e->st, kv_dim, n_heads, n_kv);
             else
-                ce = launch(e, s, attn_decode_kernel<32>, c.n_heads, 256, smem, (const float*)e->q,
+                ce = launch(e, s, attn_decode_kernel<32>, n_heads, 256, smem, (const float*)e->q,
                             (const __half*)(e->kc + kvoff), (const __half*)(e->vc + kvoff), e->attn,
-                            (const StepState*)e->st, c.kv_dim, c.n_heads, c.n_kv_heads);
+                            (const StepState*)e->st, kv_dim, n_heads, n_kv);
             MG_CUDA(e, ce);
         }
-        {   // wo + residual: h2 = h + Wo attn
+        {   // wo + residual: h2 = h + Wo attn (a partial sum over this rank's heads under tensor parallelism)
             PhaseArgs a{};
             const int R = pick_rows_per_tile(e, c.dim);
             a.w[0] = e->mats[b + 7].view();
-            a.rows[0] = c.dim; a.K = c.dim;
+            a.rows[0] = c.dim; a.K = q_dim;
             a.nitems = (c.dim + R - 1) / R;
             a.pro = PRO_PLAIN; a.x_src = e->attn;
-            a.resid_in = e->h; a.out = e->h2; a.st = e->st;
+            a.resid_in = resid_h; a.out = e->h2; a.st = e->st;
             int rc = launch_phase(e, s, c.layer_fmt, EPI_RESID, R, a);
             if (rc) return rc;
+            if (tp) MG_NCCL(e, g_nccl.AllReduce(e->h2, e->h2, (size_t)c.dim, ncclFloat, ncclSum, e->comm, s));
         }
         {   // RMSNorm + gate/up + SiLU-gate
             PhaseArgs a{};
-            const int R = (c.ffn_dim >= e->num_sms * 16 * 8) ? 4 : 2;
+            const int R = (ffn >= e->num_sms * 16 * 8) ? 4 : 2;
             a.w[0] = e->mats[b + 9].view(); a.w[1] = e->mats[b + 10].view();
-            a.rows[0] = c.ffn_dim; a.rows[1] = c.ffn_dim; a.K = c.dim;
-            a.nitems = (c.ffn_dim + R / 2 - 1) / (R / 2);
+            a.rows[0] = ffn; a.rows[1] = ffn; a.K = c.dim;
+            a.nitems = (ffn + R / 2 - 1) / (R / 2);
             a.pro = PRO_RMS; a.x_src = e->h2; a.norm_w = e->vecs[b + 8]; a.eps = c.rms_eps;
             a.out = e->mid; a.st = e->st;
             int rc = launch_phase(e, s, c.layer_fmt, EPI_SWIGLU, R, a);
             if (rc) return rc;
         }
-        {   // down + residual: h = h2 + Wd mid
+        {   // down + residual: h = h2 + Wd mid (a partial sum over this rank's FFN features)
             PhaseArgs a{};
             const int R = pick_rows_per_tile(e, c.dim);
             a.w[0] = e->mats[b + 11].view();
-            a.rows[0] = c.dim; a.K = c.ffn_dim;
+            a.rows[0] = c.dim; a.K = ffn;
             a.nitems = (c.dim + R - 1) / R;
             a.pro = PRO_PLAIN; a.x_src = e->mid;
-            a.resid_in = e->h2; a.out = e->h; a.st = e->st;
+            a.resid_in = resid_h2; a.out = e->h; a.st = e->st;
             int rc = launch_phase(e, s, c.layer_fmt, EPI_RESID, R, a);
             if (rc) return rc;
+            if (tp) MG_NCCL(e, g_nccl.AllReduce(e->h, e->h, (size_t)c.dim, ncclFloat, ncclSum, e->comm, s));
         }
     }
     if (le >= L && head != HEAD_NONE) {
+        const DevMatrix& hm = e->mats[L * 12 + 1];
         PhaseArgs a{};
-        a.w[0] = e->mats[L * 12 + 1].view();
-        a.rows[0] = c.vocab; a.K = c.dim;
-        a.nitems = (c.vocab + 3) / 4;
+        a.w[0] = WeightView{hm.qs + (size_t)sh.v0 * plane_row_bytes(hm.fmt, hm.cols),
+                            hm.ds ? hm.ds + (size_t)sh.v0 * (hm.cols / 32) : nullptr};
+        a.rows[0] = vocab; a.K = c.dim;
+        a.nitems = (vocab + 3) / 4;
         a.pro = PRO_RMS; a.x_src = e->h; a.norm_w = e->vecs[L * 12]; a.eps = c.rms_eps;
         a.out = head == HEAD_LOGITS ? e->logits : nullptr;
         a.st = e->st;
         a.out_tokens = e->out_tokens;
+        a.row_base = sh.v0;
+        a.defer_finalize = tp ? 1 : 0;
         int rc = launch_phase(e, s, c.head_fmt, EPI_LOGITS, 4, a);
         if (rc) return rc;
+        if (tp) {
+            // greedy token: maximum over ranks of the packed (logit, lowest index) keys, then the cursor update
+            MG_NCCL(e, g_nccl.AllReduce(&e->st->best, &e->st->best, 1, ncclUint64, ncclMax, e->comm, s));
+            MG_CUDA(e, launch(e, s, finalize_step_kernel, 1, 1, 0, e->st, e->out_tokens));
+            if (head == HEAD_LOGITS)
+                MG_NCCL(e, g_nccl.AllGather(e->logits, e->logits_all, (size_t)sh.v_stride, ncclFloat, e->comm, s));
+        }
     }
     return MG_OK;
 }
@@ -478,6 +617,7 @@ inline int item_rows(const mg_config& c, int p, int item, int m_out[2], int r_ou
 bool mega_feasible(mg_engine* e, std::string* why) {
     const mg_config& c = e->cfg;
     const int G = e->num_sms;
+    if (e->sh.size > 1) { *why = "tensor parallelism uses the per-phase kernels"; return false; }
     int coop = 0;
     cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, c.device);
     if (!coop) { *why = "cooperative launch unsupported"; return false; }
@@ -762,6 +902,10 @@ int mg_create(const mg_config* cfg, mg_engine** out) {
     e->num_sms = prop.multiProcessorCount;
     if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(MG_ERR_CUDA);
 
+    {
+        std::string why;
+        if (!make_shard(c, 0, 1, &e->sh, &why)) return bail(MG_ERR_ARG);
+    }
     const int nw = c.n_layers * 12 + 2;
     e->mats.resize(nw);
     e->vecs.assign(nw, nullptr);
@@ -832,6 +976,9 @@ void mg_destroy(mg_engine* e) {
     cudaFree(e->cos_tab); cudaFree(e->sin_tab); cudaFree(e->kc); cudaFree(e->vc);
     cudaFree(e->h); cudaFree(e->h2); cudaFree(e->q); cudaFree(e->attn); cudaFree(e->mid); cudaFree(e->logits);
     cudaFree(e->st); cudaFree(e->out_tokens);
+    if (e->zero_vec) cudaFree(e->zero_vec);
+    if (e->logits_all) cudaFree(e->logits_all);
+    if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
     if (e->pin_i) cudaFreeHost(e->pin_i);
     if (e->stream) cudaStreamDestroy(e->stream);
     delete e;
@@ -847,16 +994,20 @@ int mg_set_weight(mg_engine* e, int idx, const float* data, size_t count) {
         return fail(e, MG_ERR_ARG, "mg_set_weight: bad slot %d", idx);
     if (count != (size_t)rows * cols)
         return fail(e, MG_ERR_ARG, "mg_set_weight: slot %d wants %d x %d values, got %zu", idx, rows, cols, count);
+    int r0, r1, k0, k1;
+    shard_rect(e, idx, rows, cols, &r0, &r1, &k0, &k1);
+    e->any_weight_set = true;
     if (!is_matrix) {
-        if (!e->vecs[idx] && (rc = dev_alloc(e, &e->vecs[idx], (size_t)cols))) return rc;
-        MG_CUDA(e, cudaMemcpy(e->vecs[idx], data, (size_t)cols * 4, cudaMemcpyHostToDevice));
+        if (!e->vecs[idx] && (rc = dev_alloc(e, &e->vecs[idx], (size_t)(k1 - k0)))) return rc;
+        MG_CUDA(e, cudaMemcpy(e->vecs[idx], data + k0, (size_t)(k1 - k0) * 4, cudaMemcpyHostToDevice));
         e->built = false;
         return MG_OK;
     }
-    std::vector<uint8_t> qs((size_t)rows * plane_row_bytes(fmt, cols));
-    std::vector<unsigned short> ds(fmt == FMT_F16 ? 0 : (size_t)rows * (cols / 32));
-    quantize_planes(fmt, data, rows, cols, qs.data(), ds.data());
-    return upload_planes(e, idx, fmt, rows, cols, qs, ds);
+    const int lr = r1 - r0, lk = k1 - k0;
+    std::vector<uint8_t> qs((size_t)lr * plane_row_bytes(fmt, lk));
+    std::vector<unsigned short> ds(fmt == FMT_F16 ? 0 : (size_t)lr * (lk / 32));
+    quantize_planes(fmt, data + (size_t)r0 * cols + k0, (size_t)cols, lr, lk, qs.data(), ds.data());
+    return upload_planes(e, idx, fmt, lr, lk, qs, ds);
 }
 
 int mg_set_weight_raw(mg_engine* e, int idx, const void* blocks, size_t bytes, int fmt) {
@@ -870,10 +1021,16 @@ int mg_set_weight_raw(mg_engine* e, int idx, const void* blocks, size_t bytes, i
     if (bytes != (size_t)rows * raw_row_bytes(fmt, cols))
         return fail(e, MG_ERR_ARG, "mg_set_weight_raw: slot %d wants %zu bytes, got %zu", idx,
                     (size_t)rows * raw_row_bytes(fmt, cols), bytes);
-    std::vector<uint8_t> qs((size_t)rows * plane_row_bytes(fmt, cols));
-    std::vector<unsigned short> ds(fmt == FMT_F16 ? 0 : (size_t)rows * (cols / 32));
-    split_raw_blocks(fmt, static_cast<const uint8_t*>(blocks), rows, cols, qs.data(), ds.data());
-    return upload_planes(e, idx, fmt, rows, cols, qs, ds);
+    int r0, r1, k0, k1;
+    shard_rect(e, idx, rows, cols, &r0, &r1, &k0, &k1);
+    e->any_weight_set = true;
+    const int lr = r1 - r0, lk = k1 - k0;
+    const size_t ld = raw_row_bytes(fmt, cols);
+    std::vector<uint8_t> qs((size_t)lr * plane_row_bytes(fmt, lk));
+    std::vector<unsigned short> ds(fmt == FMT_F16 ? 0 : (size_t)lr * (lk / 32));
+    split_raw_blocks(fmt, static_cast<const uint8_t*>(blocks) + (size_t)r0 * ld + raw_row_bytes(fmt, k0), ld, lr, lk,
+                     qs.data(), ds.data());
+    return upload_planes(e, idx, fmt, lr, lk, qs, ds);
 }
 
 int mg_build(mg_engine* e) {
@@ -949,7 +1106,8 @@ int mg_partial_step(mg_engine* e, const float* hidden_in, int pos, int layer_sta
     const bool want_logits = layer_end >= c.n_layers && logits_out;
     if ((rc = run_step(e, layer_start, layer_end, MODE_HIDDEN, want_logits ? HEAD_LOGITS : HEAD_NONE))) return rc;
     if (want_logits)
-        MG_CUDA(e, cudaMemcpyAsync(logits_out, e->logits, (size_t)c.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
+        MG_CUDA(e, cudaMemcpyAsync(logits_out, e->sh.size > 1 ? e->logits_all : e->logits, (size_t)c.vocab * 4,
+                                   cudaMemcpyDeviceToHost, e->stream));
     else if (hidden_out)
         MG_CUDA(e, cudaMemcpyAsync(hidden_out, e->h, (size_t)c.dim * 4, cudaMemcpyDeviceToHost, e->stream));
     MG_CUDA(e, cudaStreamSynchronize(e->stream));
@@ -977,7 +1135,8 @@ int mg_step_token(mg_engine* e, int token, int pos, int* next_token, float* logi
     MG_CUDA(e, cudaMemcpyAsync(e->st, e->pin_i, 8, cudaMemcpyHostToDevice, e->stream));
     if ((rc = run_step(e, 0, c.n_layers, MODE_EMBED, logits_out ? HEAD_LOGITS : HEAD_ARGMAX))) return rc;
     if (logits_out)
-        MG_CUDA(e, cudaMemcpyAsync(logits_out, e->logits, (size_t)c.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
+        MG_CUDA(e, cudaMemcpyAsync(logits_out, e->sh.size > 1 ? e->logits_all : e->logits, (size_t)c.vocab * 4,
+                                   cudaMemcpyDeviceToHost, e->stream));
     MG_CUDA(e, cudaMemcpyAsync(e->pin_i + 4, &e->st->token, 4, cudaMemcpyDeviceToHost, e->stream));
     MG_CUDA(e, cudaStreamSynchronize(e->stream));
     if (next_token) *next_token = e->pin_i[4];
@@ -1069,8 +1228,9 @@ int mg_read_kv(mg_engine* e, int layer, int pos0, int npos, uint16_t* k_out, uin
     const mg_config& c = e->cfg;
     if (layer < 0 || layer >= c.n_layers || pos0 < 0 || npos < 0 || pos0 + npos > c.max_seq)
         return fail(e, MG_ERR_ARG, "mg_read_kv: out of range");
-    const size_t off = ((size_t)layer * c.max_seq + pos0) * c.kv_dim;
-    const size_t bytes = (size_t)npos * c.kv_dim * 2;
+    const int kv_dim = (e->sh.kv1 - e->sh.kv0) * c.head_dim;   // this rank's KV heads
+    const size_t off = ((size_t)layer * c.max_seq + pos0) * kv_dim;
+    const size_t bytes = (size_t)npos * kv_dim * 2;
     MG_CUDA(e, cudaStreamSynchronize(e->stream));
     if (k_out) MG_CUDA(e, cudaMemcpy(k_out, e->kc + off, bytes, cudaMemcpyDeviceToHost));
     if (v_out) MG_CUDA(e, cudaMemcpy(v_out, e->vc + off, bytes, cudaMemcpyDeviceToHost));
@@ -1093,6 +1253,55 @@ int mg_trace_step(mg_engine* e, long long* stamps, int capacity, int* n_ctas, in
     if (n_ctas) *n_ctas = G;
     if (n_events) *n_events = ev;
     return check_mega_status(e);
+}
+
+int mg_tp_partition(const mg_config* cfg, int rank, int size, mg_tp_shard* out) {
+    if (!cfg || !out) return MG_ERR_ARG;
+    if (cfg->n_heads <= 0 || cfg->n_kv_heads <= 0 || cfg->n_heads % cfg->n_kv_heads || cfg->ffn_dim % 32 || cfg->vocab <= 0)
+        return MG_ERR_ARG;
+    Shard s;
+    std::string why;
+    if (!make_shard(*cfg, rank, size, &s, &why)) return MG_ERR_UNSUPPORTED;
+    out->q_head0 = s.q0; out->q_head1 = s.q1; out->kv_head0 = s.kv0; out->kv_head1 = s.kv1;
+    out->ffn0 = s.f0; out->ffn1 = s.f1; out->vocab0 = s.v0; out->vocab1 = s.v1;
+    return MG_OK;
+}
+
+int mg_tp_unique_id(void* id_out, size_t bytes) {
+    if (!id_out || bytes < sizeof(ncclUniqueId)) return MG_ERR_ARG;
+    std::string why;
+    if (!load_nccl(&why)) {
+        fprintf(stderr, "[mongoose-b200] %s\n", why.c_str());
+        return MG_ERR_UNSUPPORTED;
+    }
+    ncclUniqueId id;
+    if (g_nccl.GetUniqueId(&id) != ncclSuccess) return MG_ERR_CUDA;
+    memcpy(id_out, &id, sizeof id);
+    return MG_OK;
+}
+
+int mg_tp_init(mg_engine* e, int rank, int size, const void* id, size_t bytes) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if (e->any_weight_set || e->comm) return fail(e, MG_ERR_STATE, "mg_tp_init: call once, before any weight is set");
+    if (size == 1 && rank == 0) return MG_OK;
+    if (!id || bytes < sizeof(ncclUniqueId)) return fail(e, MG_ERR_ARG, "mg_tp_init: need the %zu-byte id of mg_tp_unique_id", sizeof(ncclUniqueId));
+    std::string why;
+    Shard s;
+    if (!make_shard(e->cfg, rank, size, &s, &why)) return fail(e, MG_ERR_UNSUPPORTED, "mg_tp_init: %s", why.c_str());
+    if (s.v1 <= s.v0) return fail(e, MG_ERR_UNSUPPORTED, "mg_tp_init: rank %d would hold no vocabulary rows", rank);
+    if (!load_nccl(&why)) return fail(e, MG_ERR_UNSUPPORTED, "mg_tp_init: %s", why.c_str());
+    ncclUniqueId uid;
+    memcpy(&uid, id, sizeof uid);
+    MG_NCCL(e, g_nccl.CommInitRank(&e->comm, size, uid, rank));
+    if ((rc = dev_alloc(e, &e->zero_vec, (size_t)e->cfg.dim))) return rc;
+    if ((rc = dev_alloc(e, &e->logits_all, (size_t)s.v_stride * size))) return rc;
+    MG_CUDA(e, cudaMemset(e->zero_vec, 0, (size_t)e->cfg.dim * 4));
+    e->sh = s;
+    e->use_mega = false;   // the persistent kernel is single-GPU
+    e->use_pdl = false;    // launches alternate with library collectives; keep plain stream order
+    e->built = false;
+    return MG_OK;
 }
 
 cudaStream_t mg_stream(mg_engine* e) { return e ? e->stream : nullptr; }

@@ -22,8 +22,12 @@ def _np_ptr(a: np.ndarray):
 
 
 class CUDAFusedInference:
-    def __init__(self, cfg: ModelConfig, device: int = 0):
-        """NewCUDAFusedInference (cuda_fused_infer.go:144)."""
+    def __init__(self, cfg: ModelConfig, device: int = 0, tp_rank: int = 0, tp_size: int = 1,
+                 tp_id: bytes | None = None):
+        """NewCUDAFusedInference (cuda_fused_infer.go:144).  With tp_size > 1 this process is one
+        rank of a tensor-parallel group: tp_id is the 128-byte communicator id rank 0 made
+        (mongoose_b200.multi.tp_unique_id), the call is collective, and every rank then sets the
+        full weights and keeps its part."""
         self.cfg = cfg
         self._lib = _lib.load()
         c = _lib.MgConfig(dim=cfg.dim, kv_dim=cfg.kv_dim, head_dim=cfg.head_dim, n_heads=cfg.n_heads,
@@ -36,6 +40,12 @@ class CUDAFusedInference:
         if rc != 0 or not h.value:
             raise MongooseError(f"mg_create failed with status {rc} (is a B200 visible as device {device}?)")
         self._h = h
+        self.tp_rank, self.tp_size = tp_rank, tp_size
+        if tp_size > 1:
+            if tp_id is None or len(tp_id) < 128:
+                raise MongooseError("tensor parallelism needs the 128-byte communicator id")
+            buf = C.create_string_buffer(bytes(tp_id), len(tp_id))
+            self._check(self._lib.mg_tp_init(self._h, tp_rank, tp_size, buf, len(tp_id)), "mg_tp_init")
 
     # -- lifetime ---------------------------------------------------------
     def close(self):

@@ -1,8 +1,10 @@
-"""Host-side logic of multi-GPU runs: one process per GPU, no data-path collective.
+"""Host-side logic of multi-GPU runs: one process per GPU.
 
-The decode path shards by independent sequences (replicas of the weights), so ranks only meet to
-start together and to agree on the slowest rank's time; torch.distributed carries those two steps
-(NCCL on GPUs, gloo in the CPU tests).
+Two ways to use several GPUs.  Independent sequences (replicas of the weights) need no data-path
+collective: ranks only meet to start together and to agree on the slowest rank's time, and
+torch.distributed carries those two steps (NCCL on GPUs, gloo in the CPU tests).  Tensor
+parallelism splits one model over the ranks; its exchanges run inside the C library on its own
+NCCL communicator, and this module only computes partitions and hands the communicator id round.
 """
 from __future__ import annotations
 
@@ -32,3 +34,40 @@ def reduce_max(values, dist=None, device="cpu"):
 def aggregate_rate(world: int, units_per_rank: float, ms_max: float) -> float:
     """Whole-job throughput: every rank processed units_per_rank units in at most ms_max."""
     return world * units_per_rank / (ms_max / 1e3)
+
+
+# -- tensor parallelism ------------------------------------------------------------------------
+def tp_partition(cfg, rank: int, size: int) -> dict:
+    """The part of the model rank `rank` of `size` holds (mg_tp_partition; host arithmetic only).
+    Raises ValueError when the head counts cannot be split over `size` ranks."""
+    import ctypes as C
+    from . import _lib
+    lib = _lib.load()
+    c = _lib.MgConfig(dim=cfg.dim, kv_dim=cfg.kv_dim, head_dim=cfg.head_dim, n_heads=cfg.n_heads,
+                      n_kv_heads=cfg.n_kv_heads, ffn_dim=cfg.ffn_dim, vocab=cfg.vocab, n_layers=cfg.n_layers,
+                      max_seq=cfg.max_seq, rope_theta=float(cfg.rope_theta), rms_eps=float(cfg.eps),
+                      layer_fmt=cfg.layer_fmt, head_fmt=cfg.head_fmt, device=0, max_batch=1, flags=0)
+    out = _lib.MgTpShard()
+    rc = lib.mg_tp_partition(C.byref(c), rank, size, C.byref(out))
+    if rc != 0:
+        raise ValueError(f"{cfg.name}: no tensor-parallel partition for rank {rank} of {size} (status {rc})")
+    return {"q_heads": (out.q_head0, out.q_head1), "kv_heads": (out.kv_head0, out.kv_head1),
+            "ffn": (out.ffn0, out.ffn1), "vocab": (out.vocab0, out.vocab1)}
+
+
+def tp_unique_id() -> bytes:
+    """A fresh 128-byte communicator id (rank 0 calls this)."""
+    import ctypes as C
+    from . import _lib
+    buf = C.create_string_buffer(128)
+    rc = _lib.load().mg_tp_unique_id(buf, 128)
+    if rc != 0:
+        raise RuntimeError(f"mg_tp_unique_id: status {rc}")
+    return buf.raw
+
+
+def share_unique_id(dist, rank: int) -> bytes:
+    """Rank 0 makes the communicator id; every rank returns it (broadcast over `dist`)."""
+    box = [tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    return box[0]

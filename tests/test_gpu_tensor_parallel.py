@@ -1,0 +1,56 @@
+"""Tensor-parallel decode on 2 (and 4) GPUs of one node against the CPU oracle.
+
+Each rank is a child process with its own GPU (tests/tp_worker.py, launched by torchrun); the ranks
+exchange partial sums through NCCL inside the C library.  Skipped where fewer GPUs are visible.
+No rank leaves mid-step and nothing here is expected to fail on the device.
+"""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+from tests.util import free_port
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOL = 1e-4   # relative to max|y|, the same bound as the single-GPU engine tests
+
+
+def run_ranks(world, cases):
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs, {torch.cuda.device_count()} visible")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                          "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+                          os.path.join(ROOT, "tests", "tp_worker.py"), *cases],
+                         capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
+    assert out.returncode == 0, (out.stdout[-1500:], out.stderr[-3000:])
+    lines = [json.loads(l) for l in out.stdout.splitlines() if l.startswith('{"rank"')]
+    assert len(lines) == world
+    return sorted(lines, key=lambda l: l["rank"])
+
+
+def check(lines, cases, n_new=24):
+    for name in cases:
+        toks = lines[0]["results"][name]["tokens"]
+        for l in lines:
+            r = l["results"][name]
+            assert r["logits_err"] <= TOL and r["hidden_err"] <= TOL and r["token_logits_err"] <= TOL, (name, r)
+            assert r["exact"] + r["ties"] == n_new, (name, r)
+            assert r["tokens"] == toks, f"{name}: ranks disagree on the greedy tokens"
+            assert r["launches"] > 0
+
+
+def test_two_ranks_match_the_oracle():
+    cases = ["tiny", "tiny-bias-ragged", "tiny-q4", "hd128-gqa"]
+    check(run_ranks(2, cases), cases)
+
+
+def test_four_ranks_with_replicated_kv_heads_match_the_oracle():
+    # 2 KV heads over 4 ranks: every KV head is held by two ranks that split its Q heads
+    cases = ["tiny", "tiny-bias-ragged", "hd128-gqa"]
+    check(run_ranks(4, cases), cases)

@@ -3,6 +3,8 @@ import os
 import subprocess
 import sys
 
+from tests.util import free_port
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 WORKER = r"""
@@ -27,7 +29,7 @@ def test_two_ranks_agree_on_max_time_and_split_sequences(tmp_path):
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                          "--master-addr", "127.0.0.1", "--master-port", "29617", str(script)],
+                          "--master-addr", "127.0.0.1", "--master-port", str(free_port()), str(script)],
                          capture_output=True, text=True, timeout=240)
     assert out.returncode == 0, out.stderr[-2000:]
     import json

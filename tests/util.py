@@ -10,6 +10,14 @@ from oracle import oracle as O
 REL_TOL = 1e-4   # GPU vs fp64-accumulate oracle, relative to max|y| of the vector
 
 
+def free_port() -> int:
+    """A TCP port nothing is listening on right now (for a torchrun rendezvous on 127.0.0.1)."""
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def rel_err(got, want) -> float:
     got = np.asarray(got, np.float64)
     want = np.asarray(want, np.float64)
