@@ -49,6 +49,10 @@ WORKLOADS = {
     "qwen2.5-0.5b-q4_0-b1": mc.QWEN25_05B_Q4,
     "tiny-q8_0-b1": mc.TINY,
     "qwen2.5-7b-q8_0-b1": mc.QWEN25_7B,
+    # one sequence, the model split over all ranks (tensor parallel; needs --gpus 2, 4 or 8);
+    # on one GPU it is the same as qwen2.5-7b-q8_0-b1
+    "qwen2.5-7b-q8_0-tp": mc.QWEN25_7B,
+    "tiny-q8_0-tp": mc.TINY,
     # 64 independent sequences (512-token prompt + 512 decode steps each in the full configuration),
     # sequence i on GPU i mod G, each decoded with batch-1 semantics as the reference would (one
     # engine pass per token); select sizes with --sequences / --prompt-len / --steps
@@ -203,11 +207,16 @@ def run_b200_arm(args, cfg, rank, world, local_rank):
 
     K, W = args.steps, max(args.warmup, 3)
     cfg = cfg.with_(max_seq=max(cfg.max_seq, PROMPT_LEN + K))
-    eng = CUDAFusedInference(cfg, device=local_rank)
+    tp = args.workload.endswith("-tp") and world > 1    # one sequence over all ranks, else one per rank
+    if tp:
+        eng = CUDAFusedInference(cfg, device=local_rank, tp_rank=rank, tp_size=world,
+                                 tp_id=multi.share_unique_id(dist, rank))
+    else:
+        eng = CUDAFusedInference(cfg, device=local_rank)
     seed = 0                                            # same weights on every replica
-    synthetic.load_engine(eng, cfg, seed=seed)
+    synthetic.load_engine(eng, cfg, seed=seed)          # under tensor parallelism each rank keeps its part
     eng.BuildFusedDispatch()
-    prompt = synthetic.prompt_ids(rank, PROMPT_LEN, cfg.vocab)    # each rank decodes its own sequence
+    prompt = synthetic.prompt_ids(0 if tp else rank, PROMPT_LEN, cfg.vocab)   # replicas decode their own sequence
     stream = torch.cuda.ExternalStream(eng.stream, device=local_rank)
 
     def barrier():
@@ -277,20 +286,22 @@ def run_b200_arm(args, cfg, rank, world, local_rank):
     ms_max, e2e_ms_max = multi.reduce_max([ms, e2e_s * 1e3], dist, device="cuda")
 
     if rank == 0:
-        tps = multi.aggregate_rate(world, K, ms_max)
-        bytes_tok = algorithmic_bytes_per_token(cfg, first_pos, K)
+        jobs = 1 if tp else world                                   # sequences decoded side by side
+        tps = multi.aggregate_rate(jobs, K, ms_max)
+        bytes_tok = algorithmic_bytes_per_token(cfg, first_pos, K) / (world if tp else 1)
         peak, peak_src = measured_peak_gbs()
         achieved = bytes_tok * (K / (ms_max / 1e3)) / 1e9          # per GPU
         line = {
             "metric": "decode_tokens_per_s", "value": tps, "unit": "tok/s", "n_gpus": world, "steps": K,
-            "warmup": W, "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak",
+            "warmup": W, "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "strong" if tp else "weak",
             "vs_baseline": None, "dtype": FMT_NAME[cfg.layer_fmt], "data": "synthetic",
             "config": {"workload": args.workload, "prompt_len": PROMPT_LEN, "batch": 1,
-                       "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+                       "parallelism": (f"tensor parallel x{world} (NCCL all-reduce of partial sums)" if tp else
+                                       f"replicas x{world}" if world > 1 else "single GPU"),
                        "l2": "inputs larger than L2 (weights streamed per token: %d MB)" %
                              (mc.weight_bytes_per_token(cfg) // 2 ** 20),
                        "timing": "CUDA events on the engine stream, max over ranks"},
-            "e2e": {"value": multi.aggregate_rate(world, K, e2e_ms_max), "unit": "tok/s",
+            "e2e": {"value": multi.aggregate_rate(jobs, K, e2e_ms_max), "unit": "tok/s",
                     "h2d_bytes_per_step": cfg.dim * 4 + 8, "d2h_bytes_per_step": cfg.vocab * 4,
                     "api": "PartialStep(hiddenIn, pos, 0, L, nil, logitsOut) with pinned host buffers",
                     "last_token_matches_device_loop": bool(e2e_last_tok == tok_last)},
@@ -298,7 +309,8 @@ def run_b200_arm(args, cfg, rank, world, local_rank):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_PER_TOKEN.get(args.workload),
                          "traffic_unit": "bytes per token (one launch decodes all timed tokens)", "peak_source": peak_src,
-                         "kernel": "whole decode step (mega_decode_kernel: one persistent launch for all timed tokens)",
+                         "kernel": ("whole decode step (mega_decode_kernel: one persistent launch for all timed tokens)"
+                                    if launches == 1 else "whole decode step (graph of fused phase kernels)"),
                          "algorithmic_bytes_per_token": bytes_tok, "frac_of_8TBs": achieved / 8000.0},
             "clocks": clocks,
             "tokens_tail": [int(x) for x in gen_tokens[-4:]],

@@ -35,6 +35,76 @@ struct StepState {
 enum : int { PRO_PLAIN = 0, PRO_RMS = 1, PRO_RMS_EMBED = 2 };
 enum : int { EPI_QKV = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_LOGITS = 3 };
 
+// ---------------------------------------------------------------------
+// Tensor-parallel exchange fused into the phase kernels.  A rank's wo / down kernel writes its
+// partial sums straight into every rank's receive buffer (peer stores over NVLink), and the
+// kernel that consumes the vector (gate/up, the next layer's QKV, lm_head) adds the received
+// rows while it stages its input, in rank order, so every rank forms the same bits.  There is no
+// separate all-reduce launch.  Arrival is signalled per (slot, sender) by a counter value the
+// sender's last CTA releases after a system-scope fence; waits are bounded and report through
+// XchgStatus instead of spinning for ever.
+// ---------------------------------------------------------------------
+constexpr int kMaxRanks = 8;
+
+struct XchgStatus {
+    int error;      // 0 = ok, 1 = a receive wait ran out
+    int slot;       // exchange slot that was waited on
+    int sender;     // rank whose row had not arrived
+    unsigned int want, seen;
+};
+
+struct PushArgs {
+    int n;                              // ranks; 0 = no exchange
+    float* dst[kMaxRanks];              // rank p's receive row for the sending rank, [rows]
+    unsigned int* flag[kMaxRanks];      // rank p's arrival counter for the sending rank
+    unsigned int* count;                // sender-local: exchanges of this slot done so far
+    unsigned int* ticket;               // sender-local: CTAs of this launch that have finished
+};
+
+struct GatherArgs {
+    int n;                              // ranks; 0 = read x_src
+    int slot;
+    const float* rows;                  // local receive buffer, [n][K]
+    const unsigned int* flags;          // local arrival counters, [n]
+    const unsigned int* count;          // the value they must reach: this rank's own exchange count
+    XchgStatus* status;
+};
+
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+
+// One thread waits until every sender's counter has reached this rank's own count.  About two
+// seconds of SM clock at most; a wait that runs out records where and returns.
+__device__ __noinline__ void xchg_wait(const GatherArgs g) {
+    const unsigned int want = *reinterpret_cast<const volatile unsigned int*>(g.count);
+    const long long deadline = clock64() + 4000000000ll;
+    for (int r = 0; r < g.n; r++) {
+        unsigned int seen = ld_acquire_sys(g.flags + r);
+        while ((int)(seen - want) < 0) {
+            if (clock64() > deadline) {
+                if (atomicCAS(&g.status->error, 0, 1) == 0) {
+                    g.status->slot = g.slot; g.status->sender = r; g.status->want = want; g.status->seen = seen;
+                }
+                return;
+            }
+            seen = ld_acquire_sys(g.flags + r);
+        }
+    }
+}
+
+// x[i] = sum over senders of their row, in rank order.
+__device__ __forceinline__ float xchg_sum(const GatherArgs& g, int K, int i) {
+    float v = __ldcg(g.rows + i);
+    for (int r = 1; r < g.n; r++) v += __ldcg(g.rows + (size_t)r * K + i);
+    return v;
+}
+
 struct PhaseArgs {
     WeightView w[3];      // QKV: wq,wk,wv; SWIGLU: gate,up; else w[0]
     int rows[3];
@@ -63,6 +133,8 @@ struct PhaseArgs {
     int* out_tokens;
     int row_base;         // LOGITS: global index of local row 0 (vocab-sharded lm_head)
     int defer_finalize;   // LOGITS: leave the cursor update to finalize_step_kernel (argmax still to be reduced over ranks)
+    PushArgs push;        // RESID: send the output rows to every rank instead of (or besides) `out`
+    GatherArgs gather;    // RMS prologue: the hidden state is the sum of the received rows; CTA 0 keeps it in h_store
 };
 
 __device__ __forceinline__ unsigned long long pack_best(float v, unsigned int idx) {
@@ -102,6 +174,15 @@ __device__ __forceinline__ void stage_x(const PhaseArgs& a, float* xs, float* re
         const int token = a.st->token;
         for (int i = threadIdx.x; i < K; i += blockDim.x) {
             const float v = embed_value(a.embed, a.embed_fmt, K, token, i);
+            xs[i] = v;
+            if (blockIdx.x == 0) a.h_store[i] = v;
+            ss = fmaf(v, v, ss);
+        }
+    } else if (a.gather.n > 0) {
+        if (threadIdx.x == 0) xchg_wait(a.gather);
+        __syncthreads();
+        for (int i = threadIdx.x; i < K; i += blockDim.x) {
+            const float v = xchg_sum(a.gather, K, i);
             xs[i] = v;
             if (blockIdx.x == 0) a.h_store[i] = v;
             ss = fmaf(v, v, ss);
@@ -318,7 +399,11 @@ __global__ void __launch_bounds__(256) phase_kernel(const PhaseArgs a) {
 #pragma unroll
                             for (int r = 0; r < R; r++) {
                                 const int row = it * R + r;
-                                if (row < a.rows[0]) a.out[row] = a.resid_in[row] + acc[r];
+                                if (row < a.rows[0]) {
+                                    const float v = a.resid_in[row] + acc[r];
+                                    if (a.out) a.out[row] = v;
+                                    for (int p = 0; p < a.push.n; p++) a.push.dst[p][row] = v;
+                                }
                             }
                         }
                     } else if (EPI == EPI_SWIGLU) {
@@ -356,6 +441,24 @@ __global__ void __launch_bounds__(256) phase_kernel(const PhaseArgs a) {
         }
     }
 
+    if (EPI == EPI_RESID) {
+        if (a.push.n > 0) {
+            // every row this CTA sent is ordered before its ticket; the last CTA to finish tells the receivers
+            __threadfence_system();
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const unsigned int ticket = atomicAdd(a.push.ticket, 1u);
+                if (ticket == gridDim.x - 1) {
+                    *a.push.ticket = 0u;
+                    const unsigned int epoch = *a.push.count + 1u;
+                    *a.push.count = epoch;
+                    __threadfence_system();
+                    for (int p = 0; p < a.push.n; p++) st_release_sys(a.push.flag[p], epoch);
+                }
+            }
+        }
+    }
+
     if (EPI == EPI_LOGITS) {
         // CTA-level argmax, one atomic per CTA, last CTA advances the cursor.
         unsigned long long* sbest = reinterpret_cast<unsigned long long*>(red);   // 8-byte aligned: K is a multiple of 32
@@ -384,6 +487,14 @@ __global__ void __launch_bounds__(256) phase_kernel(const PhaseArgs a) {
             }
         }
     }
+}
+
+// Sum of the received rows into a plain vector (the hidden state a layer range hands back to the
+// host when no kernel of the same step consumes it).
+__global__ void __launch_bounds__(256) xchg_reduce_kernel(const GatherArgs g, float* out, int K) {
+    if (threadIdx.x == 0) xchg_wait(g);
+    __syncthreads();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < K; i += gridDim.x * blockDim.x) out[i] = xchg_sum(g, K, i);
 }
 
 // Cursor update after the running argmax has been combined over tensor-parallel ranks.

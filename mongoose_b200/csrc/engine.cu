@@ -122,6 +122,11 @@ struct mg_engine {
     float* zero_vec = nullptr;          // residual input of the ranks other than 0 (the all-reduce adds rank 0's)
     float* logits_all = nullptr;        // gathered logits, [size][v_stride]
     bool any_weight_set = false;
+    // exchange fused into the kernels: receive buffer of this rank, mapped into every peer
+    bool tp_fused = false;
+    uint8_t* xchg = nullptr;            // [2 slots][size][dim] floats, then arrival counters, counts, tickets
+    uint8_t* xchg_peer[kMaxRanks] = {}; // rank p's buffer as seen from here (own entry = xchg)
+    XchgStatus* xchg_status = nullptr;
     std::string err;
 };
 
@@ -447,6 +452,41 @@ int pick_rows_per_tile(const mg_engine* e, int rows) {
     return 1;
 }
 
+// Layout of the exchange buffer (the same on every rank).
+inline size_t xchg_rows_bytes(const mg_engine* e) { return (size_t)2 * e->sh.size * e->cfg.dim * sizeof(float); }
+inline size_t xchg_bytes(const mg_engine* e) { return xchg_rows_bytes(e) + 256; }
+inline float* xchg_row(const mg_engine* e, uint8_t* base, int slot, int sender) {
+    return reinterpret_cast<float*>(base) + ((size_t)slot * e->sh.size + sender) * e->cfg.dim;
+}
+inline unsigned int* xchg_words(const mg_engine* e, uint8_t* base) {
+    return reinterpret_cast<unsigned int*>(base + xchg_rows_bytes(e));   // [0..15] arrival, [16..17] count, [18..19] ticket
+}
+
+PushArgs make_push(const mg_engine* e, int slot) {
+    PushArgs p{};
+    if (!e->tp_fused) return p;
+    p.n = e->sh.size;
+    for (int r = 0; r < p.n; r++) {
+        p.dst[r] = xchg_row(e, e->xchg_peer[r], slot, e->sh.rank);
+        p.flag[r] = xchg_words(e, e->xchg_peer[r]) + slot * kMaxRanks + e->sh.rank;
+    }
+    p.count = xchg_words(e, e->xchg) + 16 + slot;
+    p.ticket = xchg_words(e, e->xchg) + 18 + slot;
+    return p;
+}
+
+GatherArgs make_gather(const mg_engine* e, int slot) {
+    GatherArgs g{};
+    if (!e->tp_fused) return g;
+    g.n = e->sh.size;
+    g.slot = slot;
+    g.rows = xchg_row(e, e->xchg, slot, 0);
+    g.flags = xchg_words(e, e->xchg) + slot * kMaxRanks;
+    g.count = xchg_words(e, e->xchg) + 16 + slot;
+    g.status = e->xchg_status;
+    return g;
+}
+
 enum { MODE_EMBED = 0, MODE_HIDDEN = 1 };
 enum { HEAD_NONE = 0, HEAD_ARGMAX = 1, HEAD_LOGITS = 2 };
 
@@ -476,6 +516,7 @@ int enqueue_step(mg_engine* e, cudaStream_t s, int ls, int le, int mode, int hea
             const bool embed = (mode == MODE_EMBED && l == 0);
             a.pro = embed ? PRO_RMS_EMBED : PRO_RMS;
             a.x_src = e->h;
+            if (l > ls) a.gather = make_gather(e, 1);   // the previous layer's down rows; CTA 0 keeps the sum in h
             a.norm_w = e->vecs[b + 0];
             a.eps = c.rms_eps;
             a.embed = e->mats[L * 12 + 1].view();
@@ -516,10 +557,12 @@ int enqueue_step(mg_engine* e, cudaStream_t s, int ls, int le, int mode, int hea
             a.rows[0] = c.dim; a.K = q_dim;
             a.nitems = (c.dim + R - 1) / R;
             a.pro = PRO_PLAIN; a.x_src = e->attn;
-            a.resid_in = resid_h; a.out = e->h2; a.st = e->st;
+            a.resid_in = resid_h; a.out = e->tp_fused ? nullptr : e->h2; a.st = e->st;
+            a.push = make_push(e, 0);
             int rc = launch_phase(e, s, c.layer_fmt, EPI_RESID, R, a);
             if (rc) return rc;
-            if (tp) MG_NCCL(e, g_nccl.AllReduce(e->h2, e->h2, (size_t)c.dim, ncclFloat, ncclSum, e->comm, s));
+            if (tp && !e->tp_fused)
+                MG_NCCL(e, g_nccl.AllReduce(e->h2, e->h2, (size_t)c.dim, ncclFloat, ncclSum, e->comm, s));
         }
         {   // RMSNorm + gate/up + SiLU-gate
             PhaseArgs a{};
@@ -528,6 +571,7 @@ int enqueue_step(mg_engine* e, cudaStream_t s, int ls, int le, int mode, int hea
             a.rows[0] = ffn; a.rows[1] = ffn; a.K = c.dim;
             a.nitems = (ffn + R / 2 - 1) / (R / 2);
             a.pro = PRO_RMS; a.x_src = e->h2; a.norm_w = e->vecs[b + 8]; a.eps = c.rms_eps;
+            a.gather = make_gather(e, 0); a.h_store = e->h2;
             a.out = e->mid; a.st = e->st;
             int rc = launch_phase(e, s, c.layer_fmt, EPI_SWIGLU, R, a);
             if (rc) return rc;
@@ -539,12 +583,18 @@ int enqueue_step(mg_engine* e, cudaStream_t s, int ls, int le, int mode, int hea
             a.rows[0] = c.dim; a.K = ffn;
             a.nitems = (c.dim + R - 1) / R;
             a.pro = PRO_PLAIN; a.x_src = e->mid;
-            a.resid_in = resid_h2; a.out = e->h; a.st = e->st;
+            a.resid_in = resid_h2; a.out = e->tp_fused ? nullptr : e->h; a.st = e->st;
+            a.push = make_push(e, 1);
             int rc = launch_phase(e, s, c.layer_fmt, EPI_RESID, R, a);
             if (rc) return rc;
-            if (tp) MG_NCCL(e, g_nccl.AllReduce(e->h, e->h, (size_t)c.dim, ncclFloat, ncclSum, e->comm, s));
+            if (tp && !e->tp_fused)
+                MG_NCCL(e, g_nccl.AllReduce(e->h, e->h, (size_t)c.dim, ncclFloat, ncclSum, e->comm, s));
         }
     }
+    const bool ran_layers = std::min(le, L) > ls;
+    const bool head_runs = le >= L && head != HEAD_NONE;
+    if (e->tp_fused && ran_layers && !head_runs)   // nothing downstream adds the last down rows: do it here
+        MG_CUDA(e, launch(e, s, xchg_reduce_kernel, 4, 256, 0, make_gather(e, 1), e->h, c.dim));
     if (le >= L && head != HEAD_NONE) {
         const DevMatrix& hm = e->mats[L * 12 + 1];
         PhaseArgs a{};
@@ -553,6 +603,7 @@ int enqueue_step(mg_engine* e, cudaStream_t s, int ls, int le, int mode, int hea
         a.rows[0] = vocab; a.K = c.dim;
         a.nitems = (vocab + 3) / 4;
         a.pro = PRO_RMS; a.x_src = e->h; a.norm_w = e->vecs[L * 12]; a.eps = c.rms_eps;
+        if (ran_layers) { a.gather = make_gather(e, 1); a.h_store = e->h; }
         a.out = head == HEAD_LOGITS ? e->logits : nullptr;
         a.st = e->st;
         a.out_tokens = e->out_tokens;
@@ -805,6 +856,15 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
 
 // After a synchronisation: did any wait inside the persistent kernel give up?
 int check_mega_status(mg_engine* e) {
+    if (e->tp_fused) {
+        XchgStatus x{};
+        MG_CUDA(e, cudaMemcpy(&x, e->xchg_status, sizeof x, cudaMemcpyDeviceToHost));
+        if (x.error) {
+            cudaMemset(e->xchg_status, 0, sizeof x);
+            return fail(e, MG_ERR_TIMEOUT, "tensor-parallel exchange: rows of rank %d never arrived (slot %d, count %u of %u)",
+                        x.sender, x.slot, x.seen, x.want);
+        }
+    }
     if (!e->mega_ok) return MG_OK;
     MegaStatus s{};
     MG_CUDA(e, cudaMemcpy(&s, e->mk_status, sizeof s, cudaMemcpyDeviceToHost));
@@ -976,6 +1036,15 @@ void mg_destroy(mg_engine* e) {
     cudaFree(e->cos_tab); cudaFree(e->sin_tab); cudaFree(e->kc); cudaFree(e->vc);
     cudaFree(e->h); cudaFree(e->h2); cudaFree(e->q); cudaFree(e->attn); cudaFree(e->mid); cudaFree(e->logits);
     cudaFree(e->st); cudaFree(e->out_tokens);
+    if (e->comm && e->zero_vec) {
+        // no rank unmaps or frees its receive buffer while a peer may still be writing to it
+        if (g_nccl.AllReduce(e->zero_vec, e->zero_vec, 1, ncclFloat, ncclSum, e->comm, e->stream) == ncclSuccess)
+            cudaStreamSynchronize(e->stream);
+    }
+    for (int p = 0; p < kMaxRanks; p++)
+        if (e->xchg_peer[p] && e->xchg_peer[p] != e->xchg) cudaIpcCloseMemHandle(e->xchg_peer[p]);
+    if (e->xchg) cudaFree(e->xchg);
+    if (e->xchg_status) cudaFree(e->xchg_status);
     if (e->zero_vec) cudaFree(e->zero_vec);
     if (e->logits_all) cudaFree(e->logits_all);
     if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
@@ -1298,6 +1367,56 @@ int mg_tp_init(mg_engine* e, int rank, int size, const void* id, size_t bytes) {
     if ((rc = dev_alloc(e, &e->logits_all, (size_t)s.v_stride * size))) return rc;
     MG_CUDA(e, cudaMemset(e->zero_vec, 0, (size_t)e->cfg.dim * 4));
     e->sh = s;
+    // Receive buffer of the fused exchange, mapped into every peer through CUDA IPC.  Where a peer
+    // cannot be mapped (or MG_TP_NCCL=1 asks for it) the partial sums go through ncclAllReduce.
+    const char* env = getenv("MG_TP_NCCL");
+    bool want_fused = !(env && env[0] == '1') && size <= kMaxRanks;
+    {
+        if ((rc = dev_alloc(e, &e->xchg, xchg_bytes(e)))) return rc;
+        if ((rc = dev_alloc(e, &e->xchg_status, (size_t)1))) return rc;
+        MG_CUDA(e, cudaMemset(e->xchg, 0, xchg_bytes(e)));
+        MG_CUDA(e, cudaMemset(e->xchg_status, 0, sizeof(XchgStatus)));
+        cudaIpcMemHandle_t mine{};
+        int ok = want_fused && cudaIpcGetMemHandle(&mine, e->xchg) == cudaSuccess ? 1 : 0;
+        if (!ok) cudaGetLastError();
+        // every rank learns every handle (and whether its owner could make one) in one all-gather
+        const size_t rec = sizeof(cudaIpcMemHandle_t) + 8;
+        uint8_t* d_all = nullptr;
+        MG_CUDA(e, cudaMalloc((void**)&d_all, rec * size));
+        std::vector<uint8_t> h_all(rec * size, 0);
+        memcpy(h_all.data() + rec * rank, &mine, sizeof mine);
+        h_all[rec * rank + sizeof mine] = (uint8_t)ok;
+        MG_CUDA(e, cudaMemcpy(d_all, h_all.data(), rec * size, cudaMemcpyHostToDevice));
+        MG_NCCL(e, g_nccl.AllGather(d_all + rec * rank, d_all, rec, ncclChar, e->comm, e->stream));
+        MG_CUDA(e, cudaStreamSynchronize(e->stream));
+        MG_CUDA(e, cudaMemcpy(h_all.data(), d_all, rec * size, cudaMemcpyDeviceToHost));
+        int all_ok = 1;
+        for (int p = 0; p < size; p++) all_ok &= h_all[rec * p + sizeof mine];
+        int opened = all_ok;
+        if (all_ok) {
+            for (int p = 0; p < size && opened; p++) {
+                if (p == rank) { e->xchg_peer[p] = e->xchg; continue; }
+                cudaIpcMemHandle_t hnd;
+                memcpy(&hnd, h_all.data() + rec * p, sizeof hnd);
+                void* ptr = nullptr;
+                if (cudaIpcOpenMemHandle(&ptr, hnd, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                    cudaGetLastError();
+                    opened = 0;
+                } else {
+                    e->xchg_peer[p] = static_cast<uint8_t*>(ptr);
+                }
+            }
+        }
+        // agree: the fused path is used only if every rank mapped every peer
+        int* d_flag = reinterpret_cast<int*>(d_all);
+        MG_CUDA(e, cudaMemcpy(d_flag, &opened, sizeof(int), cudaMemcpyHostToDevice));
+        MG_NCCL(e, g_nccl.AllReduce(d_flag, d_flag, 1, ncclInt, ncclMin, e->comm, e->stream));
+        MG_CUDA(e, cudaStreamSynchronize(e->stream));
+        MG_CUDA(e, cudaMemcpy(&opened, d_flag, sizeof(int), cudaMemcpyDeviceToHost));
+        cudaFree(d_all);
+        e->tp_fused = opened != 0;
+        if (!e->tp_fused) e->err = "tensor-parallel exchange through ncclAllReduce (peer mapping unavailable or MG_TP_NCCL=1)";
+    }
     e->use_mega = false;   // the persistent kernel is single-GPU
     e->use_pdl = false;    // launches alternate with library collectives; keep plain stream order
     e->built = false;

@@ -43,6 +43,7 @@ def main():
         tp_id = multi.share_unique_id(dist, rank)
         eng = CUDAFusedInference(cfg, device=local, tp_rank=rank, tp_size=world, tp_id=tp_id)
         om = O.OracleModel(cfg)
+        note = eng._lib.mg_last_error(eng._h).decode()      # says so when the exchange goes through NCCL
         fill_models(cfg, seed=3, jitter=0.1, engine=eng, oracle_model=om, raw_slots=True, bias=bias)
         rng = np.random.default_rng(5)
         worst = 0.0
@@ -77,7 +78,8 @@ def main():
         exact, ties, _ = greedy_parity(toks, om, prompt, n_new)
         results[name] = {"logits_err": worst, "hidden_err": worst_hidden, "token_logits_err": tok_err,
                          "exact": exact, "ties": len(ties), "tokens": [int(x) for x in toks],
-                         "launches": eng.LaunchCount()}
+                         "launches": eng.LaunchCount(),
+                         "nccl_exchange": "ncclAllReduce" in note}
         eng.close(); om.close()
         dist.barrier()
     print(json.dumps({"rank": rank, "world": world, "results": results}), flush=True)
