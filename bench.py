@@ -53,6 +53,8 @@ WORKLOADS = {
     # on one GPU it is the same as qwen2.5-7b-q8_0-b1
     "qwen2.5-7b-q8_0-tp": mc.QWEN25_7B,
     "tiny-q8_0-tp": mc.TINY,
+    # 7B-class layer shapes with few layers and a cut vocabulary: loads in seconds (smoke runs of the exchange)
+    "qwen2.5-7b-width-4l-q8_0-tp": mc.QWEN25_7B.with_(name="qwen2.5-7b-width-4l", n_layers=4, vocab=16000),
     # 64 independent sequences (512-token prompt + 512 decode steps each in the full configuration),
     # sequence i on GPU i mod G, each decoded with batch-1 semantics as the reference would (one
     # engine pass per token); select sizes with --sequences / --prompt-len / --steps
@@ -296,7 +298,9 @@ def run_b200_arm(args, cfg, rank, world, local_rank):
             "warmup": W, "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "strong" if tp else "weak",
             "vs_baseline": None, "dtype": FMT_NAME[cfg.layer_fmt], "data": "synthetic",
             "config": {"workload": args.workload, "prompt_len": PROMPT_LEN, "batch": 1,
-                       "parallelism": (f"tensor parallel x{world} (NCCL all-reduce of partial sums)" if tp else
+                       "parallelism": (f"tensor parallel x{world} (partial sums exchanged " +
+                                        ("by ncclAllReduce)" if os.environ.get("MG_TP_NCCL") == "1" else
+                                         "inside the kernels over peer memory)") if tp else
                                        f"replicas x{world}" if world > 1 else "single GPU"),
                        "l2": "inputs larger than L2 (weights streamed per token: %d MB)" %
                              (mc.weight_bytes_per_token(cfg) // 2 ** 20),

@@ -40,9 +40,10 @@ enum : int { EPI_QKV = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_LOGITS = 3 };
 // partial sums straight into every rank's receive buffer (peer stores over NVLink), and the
 // kernel that consumes the vector (gate/up, the next layer's QKV, lm_head) adds the received
 // rows while it stages its input, in rank order, so every rank forms the same bits.  There is no
-// separate all-reduce launch.  Arrival is signalled per (slot, sender) by a counter value the
-// sender's last CTA releases after a system-scope fence; waits are bounded and report through
-// XchgStatus instead of spinning for ever.
+// separate all-reduce launch and no fence: every element travels as one 8-byte word
+// {value, exchange number}, stores of 8 aligned bytes are single accesses, and the receiver
+// re-reads a word until it carries the number of the exchange it is waiting for.  Waits are
+// bounded and report through XchgStatus instead of spinning for ever.
 // ---------------------------------------------------------------------
 constexpr int kMaxRanks = 8;
 
@@ -55,53 +56,62 @@ struct XchgStatus {
 
 struct PushArgs {
     int n;                              // ranks; 0 = no exchange
-    float* dst[kMaxRanks];              // rank p's receive row for the sending rank, [rows]
-    unsigned int* flag[kMaxRanks];      // rank p's arrival counter for the sending rank
-    unsigned int* count;                // sender-local: exchanges of this slot done so far
+    unsigned long long* dst[kMaxRanks]; // rank p's receive row for the sending rank, [rows] words
+    unsigned int* count;                // sender-local: exchanges of this slot completed so far
     unsigned int* ticket;               // sender-local: CTAs of this launch that have finished
 };
 
 struct GatherArgs {
     int n;                              // ranks; 0 = read x_src
     int slot;
-    const float* rows;                  // local receive buffer, [n][K]
-    const unsigned int* flags;          // local arrival counters, [n]
-    const unsigned int* count;          // the value they must reach: this rank's own exchange count
+    const unsigned long long* rows;     // local receive buffer, [n][K] words
+    const unsigned int* count;          // number of the exchange to wait for: this rank's own completed count
     XchgStatus* status;
 };
 
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
 }
 
-// One thread waits until every sender's counter has reached this rank's own count.  About two
-// seconds of SM clock at most; a wait that runs out records where and returns.
-__device__ __noinline__ void xchg_wait(const GatherArgs g) {
-    const unsigned int want = *reinterpret_cast<const volatile unsigned int*>(g.count);
-    const long long deadline = clock64() + 4000000000ll;
-    for (int r = 0; r < g.n; r++) {
-        unsigned int seen = ld_acquire_sys(g.flags + r);
-        while ((int)(seen - want) < 0) {
-            if (clock64() > deadline) {
-                if (atomicCAS(&g.status->error, 0, 1) == 0) {
-                    g.status->slot = g.slot; g.status->sender = r; g.status->want = want; g.status->seen = seen;
-                }
-                return;
-            }
-            seen = ld_acquire_sys(g.flags + r);
-        }
+// Control words another kernel of the same stream wrote are read from L2: with programmatic
+// launch this grid's CTAs share an SM (and its L1) with CTAs of the grid that read the old value
+// just before its last CTA replaced it.
+__device__ __forceinline__ unsigned int ld_l2_u32(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Deadline of one kernel's receive waits: about a second of SM clock, or none at all once an
+// earlier wait has run out (the step's result is void by then; the host reports it).
+__device__ __forceinline__ long long xchg_deadline(const XchgStatus* st) {
+    return ld_l2_u32(reinterpret_cast<const unsigned int*>(&st->error)) ? 0ll : clock64() + 2000000000ll;
+}
+
+__device__ __noinline__ void xchg_timeout(const GatherArgs& g, int sender, unsigned int want, unsigned int seen) {
+    if (atomicCAS(&g.status->error, 0, 1) == 0) {
+        g.status->slot = g.slot; g.status->sender = sender; g.status->want = want; g.status->seen = seen;
     }
 }
 
-// x[i] = sum over senders of their row, in rank order.
-__device__ __forceinline__ float xchg_sum(const GatherArgs& g, int K, int i) {
-    float v = __ldcg(g.rows + i);
-    for (int r = 1; r < g.n; r++) v += __ldcg(g.rows + (size_t)r * K + i);
+// x[i] = sum over senders of their element i, in rank order.  About a second of SM clock at
+// most per element; a wait that runs out records where and yields 0 for that term.
+__device__ __forceinline__ float xchg_sum(const GatherArgs& g, int K, int i, unsigned int want, long long deadline) {
+    float v = 0.f;
+    for (int r = 0; r < g.n; r++) {
+        const unsigned long long* p = g.rows + (size_t)r * K + i;
+        unsigned long long w = ld_relaxed_sys_u64(p);
+        while ((unsigned int)(w >> 32) != want) {
+            if (clock64() > deadline) { xchg_timeout(g, r, want, (unsigned int)(w >> 32)); w = 0ull; break; }
+            w = ld_relaxed_sys_u64(p);
+        }
+        v += __uint_as_float((unsigned int)w);
+    }
     return v;
 }
 
@@ -179,10 +189,10 @@ __device__ __forceinline__ void stage_x(const PhaseArgs& a, float* xs, float* re
             ss = fmaf(v, v, ss);
         }
     } else if (a.gather.n > 0) {
-        if (threadIdx.x == 0) xchg_wait(a.gather);
-        __syncthreads();
+        const unsigned int want = ld_l2_u32(a.gather.count);
+        const long long deadline = xchg_deadline(a.gather.status);
         for (int i = threadIdx.x; i < K; i += blockDim.x) {
-            const float v = xchg_sum(a.gather, K, i);
+            const float v = xchg_sum(a.gather, K, i, want, deadline);
             xs[i] = v;
             if (blockIdx.x == 0) a.h_store[i] = v;
             ss = fmaf(v, v, ss);
@@ -396,13 +406,16 @@ __global__ void __launch_bounds__(256) phase_kernel(const PhaseArgs a) {
                         }
                     } else if (EPI == EPI_RESID) {
                         if (lane == 0) {
+                            const unsigned long long tag =
+                                a.push.n > 0 ? (unsigned long long)(ld_l2_u32(a.push.count) + 1u) << 32 : 0ull;
 #pragma unroll
                             for (int r = 0; r < R; r++) {
                                 const int row = it * R + r;
                                 if (row < a.rows[0]) {
                                     const float v = a.resid_in[row] + acc[r];
                                     if (a.out) a.out[row] = v;
-                                    for (int p = 0; p < a.push.n; p++) a.push.dst[p][row] = v;
+                                    for (int p = 0; p < a.push.n; p++)
+                                        st_relaxed_sys_u64(a.push.dst[p] + row, tag | __float_as_uint(v));
                                 }
                             }
                         }
@@ -443,17 +456,13 @@ __global__ void __launch_bounds__(256) phase_kernel(const PhaseArgs a) {
 
     if (EPI == EPI_RESID) {
         if (a.push.n > 0) {
-            // every row this CTA sent is ordered before its ticket; the last CTA to finish tells the receivers
-            __threadfence_system();
+            // the exchange number advances once every CTA has read it for its own rows
             __syncthreads();
             if (threadIdx.x == 0) {
                 const unsigned int ticket = atomicAdd(a.push.ticket, 1u);
                 if (ticket == gridDim.x - 1) {
                     *a.push.ticket = 0u;
-                    const unsigned int epoch = *a.push.count + 1u;
-                    *a.push.count = epoch;
-                    __threadfence_system();
-                    for (int p = 0; p < a.push.n; p++) st_release_sys(a.push.flag[p], epoch);
+                    *a.push.count = ld_l2_u32(a.push.count) + 1u;
                 }
             }
         }
@@ -492,13 +501,16 @@ __global__ void __launch_bounds__(256) phase_kernel(const PhaseArgs a) {
 // Sum of the received rows into a plain vector (the hidden state a layer range hands back to the
 // host when no kernel of the same step consumes it).
 __global__ void __launch_bounds__(256) xchg_reduce_kernel(const GatherArgs g, float* out, int K) {
-    if (threadIdx.x == 0) xchg_wait(g);
-    __syncthreads();
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < K; i += gridDim.x * blockDim.x) out[i] = xchg_sum(g, K, i);
+    pdl_wait();
+    const unsigned int want = ld_l2_u32(g.count);
+    const long long deadline = xchg_deadline(g.status);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < K; i += gridDim.x * blockDim.x)
+        out[i] = xchg_sum(g, K, i, want, deadline);
 }
 
 // Cursor update after the running argmax has been combined over tensor-parallel ranks.
 __global__ void finalize_step_kernel(StepState* s, int* out_tokens) {
+    pdl_wait();
     const unsigned long long key = s->best;
     const int tok = (int)(0xffffffffu - (unsigned int)(key & 0xffffffffull));
     if (out_tokens && s->step < s->out_cap) out_tokens[s->step] = tok;

@@ -124,7 +124,7 @@ struct mg_engine {
     bool any_weight_set = false;
     // exchange fused into the kernels: receive buffer of this rank, mapped into every peer
     bool tp_fused = false;
-    uint8_t* xchg = nullptr;            // [2 slots][size][dim] floats, then arrival counters, counts, tickets
+    uint8_t* xchg = nullptr;            // [2 slots][size][dim] tagged words, then this rank's counters
     uint8_t* xchg_peer[kMaxRanks] = {}; // rank p's buffer as seen from here (own entry = xchg)
     XchgStatus* xchg_status = nullptr;
     std::string err;
@@ -452,26 +452,24 @@ int pick_rows_per_tile(const mg_engine* e, int rows) {
     return 1;
 }
 
-// Layout of the exchange buffer (the same on every rank).
-inline size_t xchg_rows_bytes(const mg_engine* e) { return (size_t)2 * e->sh.size * e->cfg.dim * sizeof(float); }
+// Layout of the exchange buffer (the same on every rank): [2 slots][size][dim] 8-byte words
+// {value, exchange number}, then this rank's own counters (count[2], ticket[2]).
+inline size_t xchg_rows_bytes(const mg_engine* e) { return (size_t)2 * e->sh.size * e->cfg.dim * 8; }
 inline size_t xchg_bytes(const mg_engine* e) { return xchg_rows_bytes(e) + 256; }
-inline float* xchg_row(const mg_engine* e, uint8_t* base, int slot, int sender) {
-    return reinterpret_cast<float*>(base) + ((size_t)slot * e->sh.size + sender) * e->cfg.dim;
+inline unsigned long long* xchg_row(const mg_engine* e, uint8_t* base, int slot, int sender) {
+    return reinterpret_cast<unsigned long long*>(base) + ((size_t)slot * e->sh.size + sender) * e->cfg.dim;
 }
 inline unsigned int* xchg_words(const mg_engine* e, uint8_t* base) {
-    return reinterpret_cast<unsigned int*>(base + xchg_rows_bytes(e));   // [0..15] arrival, [16..17] count, [18..19] ticket
+    return reinterpret_cast<unsigned int*>(base + xchg_rows_bytes(e));   // [0..1] count, [2..3] ticket
 }
 
 PushArgs make_push(const mg_engine* e, int slot) {
     PushArgs p{};
     if (!e->tp_fused) return p;
     p.n = e->sh.size;
-    for (int r = 0; r < p.n; r++) {
-        p.dst[r] = xchg_row(e, e->xchg_peer[r], slot, e->sh.rank);
-        p.flag[r] = xchg_words(e, e->xchg_peer[r]) + slot * kMaxRanks + e->sh.rank;
-    }
-    p.count = xchg_words(e, e->xchg) + 16 + slot;
-    p.ticket = xchg_words(e, e->xchg) + 18 + slot;
+    for (int r = 0; r < p.n; r++) p.dst[r] = xchg_row(e, e->xchg_peer[r], slot, e->sh.rank);
+    p.count = xchg_words(e, e->xchg) + slot;
+    p.ticket = xchg_words(e, e->xchg) + 2 + slot;
     return p;
 }
 
@@ -481,8 +479,7 @@ GatherArgs make_gather(const mg_engine* e, int slot) {
     g.n = e->sh.size;
     g.slot = slot;
     g.rows = xchg_row(e, e->xchg, slot, 0);
-    g.flags = xchg_words(e, e->xchg) + slot * kMaxRanks;
-    g.count = xchg_words(e, e->xchg) + 16 + slot;
+    g.count = xchg_words(e, e->xchg) + slot;
     g.status = e->xchg_status;
     return g;
 }
@@ -861,8 +858,8 @@ int check_mega_status(mg_engine* e) {
         MG_CUDA(e, cudaMemcpy(&x, e->xchg_status, sizeof x, cudaMemcpyDeviceToHost));
         if (x.error) {
             cudaMemset(e->xchg_status, 0, sizeof x);
-            return fail(e, MG_ERR_TIMEOUT, "tensor-parallel exchange: rows of rank %d never arrived (slot %d, count %u of %u)",
-                        x.sender, x.slot, x.seen, x.want);
+            return fail(e, MG_ERR_TIMEOUT, "tensor-parallel exchange: rows of rank %d never arrived (slot %d, exchange %u, last seen %u)",
+                        x.sender, x.slot, x.want, x.seen);
         }
     }
     if (!e->mega_ok) return MG_OK;
@@ -1415,6 +1412,10 @@ int mg_tp_init(mg_engine* e, int rank, int size, const void* id, size_t bytes) {
         MG_CUDA(e, cudaMemcpy(&opened, d_flag, sizeof(int), cudaMemcpyDeviceToHost));
         cudaFree(d_all);
         e->tp_fused = opened != 0;
+        if (e->tp_fused) {   // only this library's kernels sit between the phases: early launch is safe again
+            const char* nopdl = getenv("MG_NO_PDL");
+            e->use_pdl = !(nopdl && nopdl[0] == '1');
+        }
         if (!e->tp_fused) e->err = "tensor-parallel exchange through ncclAllReduce (peer mapping unavailable or MG_TP_NCCL=1)";
     }
     e->use_mega = false;   // the persistent kernel is single-GPU
