@@ -211,6 +211,91 @@ __device__ __forceinline__ void stage_x(const PhaseArgs& a, float* xs, float* re
 }
 
 // ---------------------------------------------------------------------
+// Prologue for int8 / 4-bit weights: the activation vector goes to shared
+// memory as 24-bit fixed point, so that the dot products run as dp4a on the
+// integer pipe (a third of the instructions of converting every weight to
+// fp32) at fp32-class accuracy.  Every group of 16 activations is scaled by
+// its own s = max|u| / (2^23 - 1) and rounded to t = a2*65536 + a1*256 + a0
+// (a2 signed, a1 and a0 unsigned bytes).  Layout at xq: byte planes
+// P0 | P1 | P2 (K bytes each), then one float2 {s, s * sum(t)} per group.
+// The RMSNorm weights are folded into the quantized values; the RMS factor
+// itself is returned and applied to the finished dot products.
+// ---------------------------------------------------------------------
+__device__ __forceinline__ float stage_xq(const PhaseArgs& a, uint8_t* xq, float* red, bool want_sum) {
+    const int K = a.K;
+    uint8_t* P0 = xq;
+    uint8_t* P1 = xq + K;
+    uint8_t* P2 = xq + 2 * (size_t)K;
+    float2* sc = reinterpret_cast<float2*>(xq + 3 * (size_t)K);
+    const bool gather = a.pro != PRO_PLAIN && a.pro != PRO_RMS_EMBED && a.gather.n > 0;
+    const bool keep = blockIdx.x == 0 && (gather || a.pro == PRO_RMS_EMBED);
+    const int token = a.pro == PRO_RMS_EMBED ? a.st->token : 0;
+    unsigned int want = 0;
+    long long deadline = 0;
+    if (gather) {
+        want = ld_l2_u32(a.gather.count);
+        deadline = xchg_deadline(a.gather.status);
+    }
+    float ss = 0.f;
+    for (int base = 0; base < K; base += 2 * blockDim.x) {
+        const int i = base + 2 * threadIdx.x;     // lanes 8j..8j+7 of a warp hold one group of 16
+        const bool ok = i < K;
+        float v0 = 0.f, v1 = 0.f;
+        if (ok) {
+            if (a.pro == PRO_RMS_EMBED) {
+                v0 = embed_value(a.embed, a.embed_fmt, K, token, i);
+                v1 = embed_value(a.embed, a.embed_fmt, K, token, i + 1);
+            } else if (gather) {
+                v0 = xchg_sum(a.gather, K, i, want, deadline);
+                v1 = xchg_sum(a.gather, K, i + 1, want, deadline);
+            } else {
+                const float2 t = *reinterpret_cast<const float2*>(a.x_src + i);
+                v0 = t.x; v1 = t.y;
+            }
+            if (keep) *reinterpret_cast<float2*>(a.h_store + i) = make_float2(v0, v1);
+        }
+        ss = fmaf(v0, v0, fmaf(v1, v1, ss));
+        float u0 = v0, u1 = v1;
+        if (ok && a.pro != PRO_PLAIN) {
+            const float2 w = *reinterpret_cast<const float2*>(a.norm_w + i);
+            u0 *= w.x; u1 *= w.y;
+        }
+        float m = fmaxf(fabsf(u0), fabsf(u1));
+        m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 1));
+        m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 2));
+        m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 4));
+        // an approximate reciprocal is enough: t is clamped, and the value represented is t * (m / 8388607)
+        const float inv = m > 0.f ? 8388607.0f * __frcp_rn(m) : 0.f;
+        // the group maximum may round to 2^23, which would not fit the signed top byte: clamp
+        const int t0 = max(-8388607, min(8388607, __float2int_rn(u0 * inv)));
+        const int t1 = max(-8388607, min(8388607, __float2int_rn(u1 * inv)));
+        int ts = 0;
+        if (want_sum) {
+            ts = t0 + t1;
+            ts += __shfl_xor_sync(MG_FULL_MASK, ts, 1);
+            ts += __shfl_xor_sync(MG_FULL_MASK, ts, 2);
+            ts += __shfl_xor_sync(MG_FULL_MASK, ts, 4);
+        }
+        if (ok) {
+            const unsigned int x = (unsigned)t0, y = (unsigned)t1;
+            *reinterpret_cast<unsigned short*>(P0 + i) = (unsigned short)((x & 0xffu) | ((y & 0xffu) << 8));
+            *reinterpret_cast<unsigned short*>(P1 + i) = (unsigned short)(((x >> 8) & 0xffu) | (y & 0xff00u));
+            *reinterpret_cast<unsigned short*>(P2 + i) = (unsigned short)(((x >> 16) & 0xffu) | ((y >> 8) & 0xff00u));
+            if ((threadIdx.x & 7) == 0) {
+                const float g = m * (1.0f / 8388607.0f);
+                sc[i >> 4] = make_float2(g, g * (float)ts);
+            }
+        }
+    }
+    if (a.pro == PRO_PLAIN) {
+        __syncthreads();
+        return 1.0f;
+    }
+    const float tot = block_sum(ss, red);
+    return rsqrtf(tot / (float)K + a.eps);
+}
+
+// ---------------------------------------------------------------------
 // Tile addressing: which rows (matrix, row) make up item `it`.
 // ---------------------------------------------------------------------
 template <int EPI, int R>
@@ -334,7 +419,14 @@ __global__ void __launch_bounds__(256) phase_kernel(const PhaseArgs a) {
     pdl_launch_dependents();
     pdl_wait();
 
-    stage_x(a, xs, red);
+    constexpr bool kInt = (FMT != FMT_F16);          // int8 / 4-bit weights: integer dot products
+    float rms = 1.0f;
+    if (kInt) rms = stage_xq(a, reinterpret_cast<uint8_t*>(smem), red, FMT == FMT_Q4_0);
+    else stage_x(a, xs, red);
+    const uint8_t* P0 = reinterpret_cast<const uint8_t*>(smem);
+    const uint8_t* P1 = P0 + a.K;
+    const uint8_t* P2 = P0 + 2 * (size_t)a.K;
+    const float2* gsc = reinterpret_cast<const float2*>(P0 + 3 * (size_t)a.K);
 
     const int pos = (EPI == EPI_QKV) ? a.st->pos : 0;
     unsigned long long best = 0ull;
@@ -353,15 +445,41 @@ __global__ void __launch_bounds__(256) phase_kernel(const PhaseArgs a) {
                 // ---- consume stage j ----
                 const int c = step * 32 + lane;
                 if (c < nchunks) {
-                    float4 xv[C::kWeights / 4];
-                    const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)c * C::kWeights);
+                    if (FMT == FMT_Q8_0) {
+                        // chunk c = activation group c
+                        const uint4 p0 = lds16(P0 + (size_t)c * 16), p1 = lds16(P1 + (size_t)c * 16),
+                                    p2 = lds16(P2 + (size_t)c * 16);
+                        const float gs = gsc[c].x;
 #pragma unroll
-                    for (int i = 0; i < C::kWeights / 4; i++) xv[i] = xp[i];
+                        for (int r = 0; r < R; r++) {
+                            const float f = group_dot_s8(st[j].w[r], p0, p1, p2);
+                            acc[r] = fmaf(half_bits_to_float(st[j].d[r]) * gs, f, acc[r]);
+                        }
+                    } else if (FMT == FMT_Q4_0) {
+                        // chunk c = block c = groups 2c (low nibbles) and 2c+1 (high nibbles)
+                        const int ga = 2 * c, gb = 2 * c + 1;
+                        const uint4 a0 = lds16(P0 + (size_t)ga * 16), a1 = lds16(P1 + (size_t)ga * 16),
+                                    a2 = lds16(P2 + (size_t)ga * 16);
+                        const uint4 b0 = lds16(P0 + (size_t)gb * 16), b1 = lds16(P1 + (size_t)gb * 16),
+                                    b2 = lds16(P2 + (size_t)gb * 16);
+                        const float2 sa = gsc[ga], sb = gsc[gb];
+                        const float off = 8.0f * (sa.y + sb.y);      // sum (nib - 8) x = sum nib x - 8 sum x
 #pragma unroll
-                    for (int r = 0; r < R; r++) {
-                        const float p = C::dot(st[j].w[r], xv);
-                        if (C::kScaled) acc[r] = fmaf(half_bits_to_float(st[j].d[r]), p, acc[r]);
-                        else acc[r] += p;
+                        for (int r = 0; r < R; r++) {
+                            const uint4 w = st[j].w[r];
+                            const float fa = group_dot_u4(w.x & 0x0f0f0f0fu, w.y & 0x0f0f0f0fu, w.z & 0x0f0f0f0fu,
+                                                          w.w & 0x0f0f0f0fu, a0, a1, a2);
+                            const float fb = group_dot_u4((w.x >> 4) & 0x0f0f0f0fu, (w.y >> 4) & 0x0f0f0f0fu,
+                                                          (w.z >> 4) & 0x0f0f0f0fu, (w.w >> 4) & 0x0f0f0f0fu, b0, b1, b2);
+                            acc[r] = fmaf(half_bits_to_float(st[j].d[r]), fmaf(sa.x, fa, sb.x * fb) - off, acc[r]);
+                        }
+                    } else {
+                        float4 xv[C::kWeights / 4];
+                        const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)c * C::kWeights);
+#pragma unroll
+                        for (int i = 0; i < C::kWeights / 4; i++) xv[i] = xp[i];
+#pragma unroll
+                        for (int r = 0; r < R; r++) acc[r] += C::dot(st[j].w[r], xv);
                     }
                 }
                 // ---- refill stage j with iteration t0 + j + D ----
@@ -377,7 +495,7 @@ __global__ void __launch_bounds__(256) phase_kernel(const PhaseArgs a) {
                 // ---- end of tile: reduce + epilogue ----
                 if (++step == steps) {
 #pragma unroll
-                    for (int r = 0; r < R; r++) acc[r] = warp_sum(acc[r]);
+                    for (int r = 0; r < R; r++) acc[r] = warp_sum(acc[r]) * rms;
                     const int it = gw + k * nwarps;
                     if (EPI == EPI_QKV) {
                         if (lane == 0) {

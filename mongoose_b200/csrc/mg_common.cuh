@@ -185,4 +185,51 @@ __host__ __device__ inline int plane_row_bytes(int fmt, int K) {
     return fmt == FMT_Q8_0 ? K : fmt == FMT_Q4_0 ? K / 2 : K * 2;
 }
 
+// ---------------------------------------------------------------------
+// Integer dot products against fixed-point activations: a group of 16
+// activations is s * t_i with 24-bit integers t = a2*65536 + a1*256 + a0
+// (a2 signed byte, a1 and a0 unsigned bytes) held as three byte planes.
+// ---------------------------------------------------------------------
+__device__ __forceinline__ uint4 lds16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+// signed weights x {unsigned, unsigned, signed} activation bytes
+__device__ __forceinline__ int dp4a_su(uint32_t w, uint32_t a, int acc) {
+    int r;
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(a), "r"(acc));
+    return r;
+}
+__device__ __forceinline__ int dp4a_ss(uint32_t w, uint32_t a, int acc) {
+    int r;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(a), "r"(acc));
+    return r;
+}
+__device__ __forceinline__ int dp4a_uu(uint32_t w, uint32_t a, int acc) {
+    int r;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(a), "r"(acc));
+    return r;
+}
+__device__ __forceinline__ int dp4a_us(uint32_t w, uint32_t a, int acc) {
+    int r;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(a), "r"(acc));
+    return r;
+}
+
+// 16 signed int8 weights (one uint4) against one activation group: exact integer sum, as float.
+__device__ __forceinline__ float group_dot_s8(uint4 w, uint4 p0, uint4 p1, uint4 p2) {
+    int i0 = dp4a_su(w.x, p0.x, 0), i1 = dp4a_su(w.x, p1.x, 0), i2 = dp4a_ss(w.x, p2.x, 0);
+    i0 = dp4a_su(w.y, p0.y, i0); i1 = dp4a_su(w.y, p1.y, i1); i2 = dp4a_ss(w.y, p2.y, i2);
+    i0 = dp4a_su(w.z, p0.z, i0); i1 = dp4a_su(w.z, p1.z, i1); i2 = dp4a_ss(w.z, p2.z, i2);
+    i0 = dp4a_su(w.w, p0.w, i0); i1 = dp4a_su(w.w, p1.w, i1); i2 = dp4a_ss(w.w, p2.w, i2);
+    return fmaf((float)i2, 65536.0f, fmaf((float)i1, 256.0f, (float)i0));
+}
+// 16 unsigned nibbles (as bytes in four words) against one activation group.
+__device__ __forceinline__ float group_dot_u4(uint32_t n0, uint32_t n1, uint32_t n2, uint32_t n3, uint4 p0, uint4 p1,
+                                              uint4 p2) {
+    int i0 = dp4a_uu(n0, p0.x, 0), i1 = dp4a_uu(n0, p1.x, 0), i2 = dp4a_us(n0, p2.x, 0);
+    i0 = dp4a_uu(n1, p0.y, i0); i1 = dp4a_uu(n1, p1.y, i1); i2 = dp4a_us(n1, p2.y, i2);
+    i0 = dp4a_uu(n2, p0.z, i0); i1 = dp4a_uu(n2, p1.z, i1); i2 = dp4a_us(n2, p2.z, i2);
+    i0 = dp4a_uu(n3, p0.w, i0); i1 = dp4a_uu(n3, p1.w, i1); i2 = dp4a_us(n3, p2.w, i2);
+    return fmaf((float)i2, 65536.0f, fmaf((float)i1, 256.0f, (float)i0));
+}
+
+
 }  // namespace mg

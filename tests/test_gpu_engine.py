@@ -23,9 +23,17 @@ SMALL = [mc.TINY, mc.TINY_Q4,
                              head_fmt=mc.FMT_Q4_0)]
 
 
-@pytest.fixture(params=SMALL, ids=lambda c: c.name)
-def pair(request, cuda, oracle, mglib):
-    cfg = request.param
+# Every case runs on the engine's default path (the persistent kernel where the model fits it);
+# the cases below run once more on the graph of per-phase kernels, which larger models use.
+KERNELS_PATH = ["tiny", "tiny-q4_0", "tiny-hd64", "tiny-hd128-f16", "qwen-width-2L-q4", "tinyllama-width-2L"]
+CASES = [(c, False) for c in SMALL] + [(c, True) for c in SMALL if c.name in KERNELS_PATH]
+
+
+@pytest.fixture(params=CASES, ids=lambda p: p[0].name + ("+kernels" if p[1] else ""))
+def pair(request, cuda, oracle, mglib, monkeypatch):
+    cfg, kernels_path = request.param
+    if kernels_path:
+        monkeypatch.setenv("MG_NO_MEGA", "1")     # read when the engine is created
     eng = CUDAFusedInference(cfg)
     om = oracle.OracleModel(cfg)
     blocks = fill_models(cfg, seed=1, jitter=0.1, engine=eng, oracle_model=om, raw_slots=True)
