@@ -106,7 +106,7 @@ struct mg_engine {
     bool trace_next = false;
     float* h_in = nullptr;              // hidden-state input of PartialStep on the persistent path
     unsigned int epoch = 16;
-    int mk_nslot = 0, mk_xs = 0, mk_sc = 0;
+    int mk_nslot = 0, mk_slot = MK_SLOT, mk_xs = 0, mk_sc = 0;
     PhaseGeom mk_geom[5] = {};
     size_t mk_smem = 0;
     size_t tape_bytes = 0;
@@ -445,10 +445,12 @@ int launch_phase(mg_engine* e, cudaStream_t s, int fmt, int epi, int R, PhaseArg
     return MG_OK;
 }
 
+// Rows per warp tile: the smallest of 1, 2, 4 that gives every warp at most one tile, so that no
+// warp runs a second pass while others idle and the rows of a tile share the activation loads.
 int pick_rows_per_tile(const mg_engine* e, int rows) {
     const int warps = e->num_sms * 16;
-    if (rows >= warps * 8) return 4;
-    if (rows >= warps * 2) return 2;
+    if (rows > warps * 2) return 4;
+    if (rows > warps) return 2;
     return 1;
 }
 
@@ -671,13 +673,26 @@ bool mega_feasible(mg_engine* e, std::string* why) {
     if (!coop) { *why = "cooperative launch unsupported"; return false; }
     if (c.n_heads > G) { *why = "more query heads than SMs"; return false; }
     if (c.max_seq > 16384) { *why = "max_seq too large for the score buffer"; return false; }
-    for (int p = 0; p <= PH_HEAD; p++) {
-        const PhaseShape s = phase_shape_of(p, c.dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
-        int max_rows = 0;
-        for (int cta = 0; cta < G; cta++)
-            max_rows = std::max(max_rows, (item_begin(s.items, cta + 1, G) - item_begin(s.items, cta, G)) * s.rpi);
-        e->mk_geom[p] = choose_geom(s.fmt, s.K, max_rows, s.rpi == 2, MK_NW, MK_SLOT);
-        if (e->mk_geom[p].ni == 0) { *why = "a weight tile does not fit a ring slot"; return false; }
+    // Ring slot: the default size, or, for matrices so wide that even a one-row tile exceeds it,
+    // the smallest multiple of 1 KiB that holds such a tile.
+    int slot = MK_SLOT;
+    for (int pass = 0; pass < 2; pass++) {
+        bool ok = true;
+        for (int p = 0; p <= PH_HEAD; p++) {
+            const PhaseShape s = phase_shape_of(p, c.dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
+            int max_rows = 0;
+            for (int cta = 0; cta < G; cta++)
+                max_rows = std::max(max_rows, (item_begin(s.items, cta + 1, G) - item_begin(s.items, cta, G)) * s.rpi);
+            e->mk_geom[p] = choose_geom(s.fmt, s.K, max_rows, s.rpi == 2, MK_NW, slot);
+            if (e->mk_geom[p].ni == 0) {
+                ok = false;
+                const int lpr = s.rpi == 2 ? 16 : 32;
+                const int need = tile_bytes_of(s.fmt, (chunks_per_row(s.fmt, s.K) + lpr - 1) / lpr);
+                slot = std::max(slot, (need + 1023) & ~1023);
+            }
+        }
+        if (ok) break;
+        if (pass == 1) { *why = "a weight tile does not fit a ring slot"; return false; }
     }
     int xs = c.dim > c.ffn_dim ? c.dim : c.ffn_dim;
     if (xs < 3 * c.head_dim) xs = 3 * c.head_dim;
@@ -686,10 +701,10 @@ bool mega_feasible(mg_engine* e, std::string* why) {
     int dev_max = 0;
     cudaDeviceGetAttribute(&dev_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, c.device);
     int nslot = MK_MAX_SLOTS;
-    while (nslot >= 4 && mk_smem_bytes(nslot, xs, c.dim, sc) > (size_t)dev_max) nslot--;
+    while (nslot >= 4 && mk_smem_bytes(nslot, slot, xs, c.dim, sc) > (size_t)dev_max) nslot--;
     if (nslot < 4) { *why = "activations leave no room for the weight ring in shared memory"; return false; }
-    e->mk_nslot = nslot; e->mk_xs = xs; e->mk_sc = sc;
-    e->mk_smem = mk_smem_bytes(nslot, xs, c.dim, sc);
+    e->mk_nslot = nslot; e->mk_slot = slot; e->mk_xs = xs; e->mk_sc = sc;
+    e->mk_smem = mk_smem_bytes(nslot, slot, xs, c.dim, sc);
     return true;
 }
 
@@ -721,7 +736,7 @@ int build_mega(mg_engine* e) {
         off[(size_t)cta * ncol + L * 4] = total; total += phase_bytes(PH_HEAD, cta);
         off[(size_t)cta * ncol + L * 4 + 1] = total;
     }
-    std::vector<uint8_t> tape((size_t)total + MK_SLOT, 0);
+    std::vector<uint8_t> tape((size_t)total + e->mk_slot, 0);
 
     // fill: one (layer, phase) at a time so that only that phase's matrices are on the host
     std::vector<uint8_t> hq[3];
@@ -831,7 +846,7 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
     e->epoch += (unsigned)n_steps * (unsigned)(L * MK_EPOCHS_PER_LAYER + 8);
     a.hd_shift = c.head_dim == 32 ? 5 : c.head_dim == 64 ? 6 : 7;
     for (int p = 0; p < 5; p++) a.geom[p] = e->mk_geom[p];
-    a.nslot = e->mk_nslot; a.xs_floats = e->mk_xs; a.sc_floats = e->mk_sc;
+    a.nslot = e->mk_nslot; a.slot_bytes = e->mk_slot; a.xs_floats = e->mk_xs; a.sc_floats = e->mk_sc;
     a.tape = e->tape; a.tape_off = e->tape_off; a.tape_bytes = e->tape_bytes;
     a.norms = e->mk_norms; a.qkv_bias = e->mk_bias;
     a.final_norm = e->vecs[L * 12];

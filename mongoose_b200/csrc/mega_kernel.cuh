@@ -41,7 +41,7 @@ namespace mg {
 constexpr int MK_NW = 15;                       // consumer warps
 constexpr int MK_CONSUMERS = MK_NW * 32;        // 480
 constexpr int MK_THREADS = MK_CONSUMERS + 32;   // + producer warp = 512 threads, 128 registers each
-constexpr int MK_SLOT = 16384;                  // ring slot bytes
+constexpr int MK_SLOT = 16384;                  // default ring slot bytes (MegaArgs::slot_bytes holds the size in use)
 constexpr int MK_MAX_SLOTS = 14;
 constexpr int MK_PART_FLOATS = 2048;
 constexpr int MK_EPOCHS_PER_LAYER = 8;
@@ -85,6 +85,7 @@ struct MegaArgs {
     unsigned int epoch;     // first epoch of this launch
     int hd_shift;           // log2(head_dim)
     int nslot;
+    int slot_bytes;       // ring slot size: MK_SLOT, or larger when one tile of the widest matrix needs it
     int xs_floats;          // size of the staged-activation buffer (multiple of 4)
     PhaseGeom geom[5];
     int sc_floats;          // attention score buffer: max_seq rounded up to a multiple of 4
@@ -259,7 +260,7 @@ struct MkCtx {
         if (++slot == a.nslot) { slot = 0; par ^= 1u; }
     }
     __device__ __forceinline__ uint8_t* ring() const { return mk_smem; }
-    __device__ __forceinline__ float* xs() const { return reinterpret_cast<float*>(mk_smem + (size_t)a.nslot * MK_SLOT); }
+    __device__ __forceinline__ float* xs() const { return reinterpret_cast<float*>(mk_smem + (size_t)a.nslot * a.slot_bytes); }
     __device__ __forceinline__ float* hs() const { return xs() + a.xs_floats; }
     __device__ __forceinline__ float* part() const { return hs() + a.dim; }
     __device__ __forceinline__ float* red() const { return part() + MK_PART_FLOATS; }
@@ -483,13 +484,13 @@ __device__ __forceinline__ void mk_produce_phase(MkCtx& c, const MegaArgs& a, co
         const int slot = c.slot;
         const uint32_t par = c.par;
         mk_wait_bar(c, &c.empty()[slot], par ^ 1u, MK_ERR_EMPTY);
-        if ((unsigned long long)(src - a.tape) + bytes > a.tape_bytes || bytes == 0 || bytes > MK_SLOT || (bytes & 15u) ||
+        if ((unsigned long long)(src - a.tape) + bytes > a.tape_bytes || bytes == 0 || bytes > (uint32_t)a.slot_bytes || (bytes & 15u) ||
             ((unsigned long long)(src - a.tape) & 15ull)) {
             mk_fail(c, MK_ERR_RANGE, 300000 + p);
             return;
         }
         mbar_expect_tx(&c.full()[slot], bytes);
-        bulk_g2s(c.ring() + (size_t)slot * MK_SLOT, src, bytes, &c.full()[slot]);
+        bulk_g2s(c.ring() + (size_t)slot * a.slot_bytes, src, bytes, &c.full()[slot]);
         src += bytes;
         c.advance();
     }
@@ -689,8 +690,8 @@ __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int
         mk_wait_bar(c, &c.full()[slot], c.par, MK_ERR_FULL);
         if (tl < nt) {
             // tiles are dealt to the warps round-robin over the whole phase
-            const uint8_t* base = c.ring() + (size_t)slot * MK_SLOT;
-            if (slot < 0 || slot >= a.nslot || nt * g.tile_bytes > MK_SLOT || g.ni <= 0) {
+            const uint8_t* base = c.ring() + (size_t)slot * a.slot_bytes;
+            if (slot < 0 || slot >= a.nslot || nt * g.tile_bytes > a.slot_bytes || g.ni <= 0) {
                 mk_fail(c, MK_ERR_RANGE, 200000 + p);
                 tl = nt + ((tl - nt) % MK_NW + MK_NW) % MK_NW;      // skip this entry's tiles
             }
@@ -1049,8 +1050,8 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
     }
 }
 
-__host__ __device__ inline size_t mk_smem_bytes(int nslot, int xs_floats, int dim, int sc_floats) {
-    return (size_t)nslot * MK_SLOT + ((size_t)xs_floats + dim + MK_PART_FLOATS + 64 + MK_ROPE_FLOATS + sc_floats) * 4 +
+__host__ __device__ inline size_t mk_smem_bytes(int nslot, int slot_bytes, int xs_floats, int dim, int sc_floats) {
+    return (size_t)nslot * slot_bytes + ((size_t)xs_floats + dim + MK_PART_FLOATS + 64 + MK_ROPE_FLOATS + sc_floats) * 4 +
            2 * MK_MAX_SLOTS * 8 + 16 + 144;
 }
 

@@ -94,7 +94,12 @@ def test_full_range_equals_layer_by_layer(pair):
     mid = np.empty(cfg.dim, np.float32)
     eng.PartialStep(h, 0, 0, 1, hiddenOut=mid)
     eng.PartialStep(mid, 0, 1, cfg.n_layers, logitsOut=lb)
-    assert np.array_equal(la, lb)
+    if cfg.n_layers > 1:
+        assert np.array_equal(la, lb)
+    else:
+        # a head-only call (no layer in the range) always runs the per-phase lm_head kernel, whose
+        # summation order differs from the persistent kernel's: equal to rounding, not bit for bit
+        assert_close(lb, la, tol=2e-6, what="head-only call vs full range")
 
 
 def test_step_token_uses_tied_embedding(pair, oracle):
