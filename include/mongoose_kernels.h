@@ -233,6 +233,21 @@ MG_API int mg_read_kv(mg_engine* e, int layer, int pos0, int npos, uint16_t* k_o
  * 8 = layer start, 9 = attention done (CTAs that run a head); then lm_head input staged / done.
  * Needs the persistent kernel; capacity is in stamps. */
 MG_API int mg_trace_step(mg_engine* e, long long* stamps, int capacity, int* n_ctas, int* n_events);
+/* ---- replay API (CaptureGraph / Launch / UpdateAndLaunch / ValidateGraphCapture, cuda_graph.go:313-739) ----
+ * The reference captures a layer range into a CUDA graph and replays it with the position patched
+ * in a device-side parameter block.  Here every step already replays a cached graph (or runs the
+ * persistent kernel) and reads its position from device memory, so these calls only expose that:
+ * nothing is captured per position and UpdateAndLaunch has nothing to update. */
+/* UploadHidden (cuda_graph.go:651): hidden state of the next launch. */
+MG_API int mg_upload_hidden(mg_engine* e, const float* hidden);
+/* CUDAGraph.Launch(pos) (cuda_graph.go:663-671): layers [layer_start, layer_end) at `pos` on the
+ * device-resident hidden state; asynchronous, no host copies.  Read the result with mg_export_hidden. */
+MG_API int mg_graph_launch(mg_engine* e, int pos, int layer_start, int layer_end);
+/* ValidateGraphCapture (cuda_graph.go:554-601): the range at position 0 through plain one-by-one
+ * kernel launches and through the replay path; max_diff receives the largest absolute difference of
+ * the two hidden states (the reference accepts < 1e-3).  Resets the KV cache. */
+MG_API int mg_validate_replay(mg_engine* e, const float* hidden_in, int layer_start, int layer_end, float* max_diff);
+
 /* ---- tensor-parallel decode over 2/4/8 GPUs of one node, one process per GPU ----------------------
  * The reference has no tensor parallelism (multigpu.go:32-82, 496-623 manages per-device handles and
  * peer copies only); these calls split one model over ranks.  QKV, gate and up are split by rows at

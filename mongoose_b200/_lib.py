@@ -80,6 +80,9 @@ SIGNATURES = {
     "mg_dequant_rows": (ci, [vp, ci, ci, ci, vp]),
     "mg_read_kv": (ci, [vp, ci, ci, ci, vp, vp]),
     "mg_trace_step": (ci, [vp, vp, ci, vp, vp]),
+    "mg_upload_hidden": (ci, [vp, vp]),
+    "mg_graph_launch": (ci, [vp, ci, ci, ci]),
+    "mg_validate_replay": (ci, [vp, vp, ci, ci, vp]),
     "mg_tp_partition": (ci, [vp, ci, ci, vp]),
     "mg_tp_unique_id": (ci, [vp, sz]),
     "mg_tp_init": (ci, [vp, ci, ci, vp, sz]),

@@ -1195,6 +1195,59 @@ int mg_partial_step(mg_engine* e, const float* hidden_in, int pos, int layer_sta
     return check_mega_status(e);
 }
 
+int mg_upload_hidden(mg_engine* e, const float* hidden) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if (!hidden) return MG_ERR_ARG;
+    MG_CUDA(e, cudaMemcpyAsync(e->h, hidden, (size_t)e->cfg.dim * 4, cudaMemcpyHostToDevice, e->stream));
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    return MG_OK;
+}
+
+int mg_graph_launch(mg_engine* e, int pos, int layer_start, int layer_end) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if ((rc = ensure_built(e))) return rc;
+    const mg_config& c = e->cfg;
+    if (pos < 0 || pos >= c.max_seq || layer_start < 0 || layer_end < layer_start)
+        return fail(e, MG_ERR_ARG, "mg_graph_launch: bad arguments (pos %d, layers [%d,%d))", pos, layer_start, layer_end);
+    if (layer_end > c.n_layers) layer_end = c.n_layers;
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));   // the pinned cursor words are reused
+    e->pin_i[0] = pos; e->pin_i[1] = 0;
+    MG_CUDA(e, cudaMemcpyAsync(e->st, e->pin_i, 8, cudaMemcpyHostToDevice, e->stream));
+    return run_step(e, layer_start, layer_end, MODE_HIDDEN, HEAD_NONE);
+}
+
+int mg_validate_replay(mg_engine* e, const float* hidden_in, int layer_start, int layer_end, float* max_diff) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if ((rc = ensure_built(e))) return rc;
+    if (!hidden_in || !max_diff) return MG_ERR_ARG;
+    const int dim = e->cfg.dim;
+    std::vector<float> plain(dim), replay(dim);
+    // plain launches of the per-phase kernels, one by one, no graph and no persistent kernel
+    const bool mega = e->mega_ok, graph = e->use_graph;
+    e->mega_ok = false; e->use_graph = false;
+    rc = mg_reset_kv(e);
+    if (!rc) rc = mg_partial_step(e, hidden_in, 0, layer_start, layer_end, nullptr, nullptr);
+    if (!rc) rc = mg_export_hidden(e, plain.data());
+    e->mega_ok = mega; e->use_graph = graph;
+    if (rc) return rc;
+    // the path every other call uses
+    if ((rc = mg_reset_kv(e))) return rc;
+    if ((rc = mg_upload_hidden(e, hidden_in))) return rc;
+    if ((rc = mg_graph_launch(e, 0, layer_start, layer_end))) return rc;
+    if ((rc = mg_export_hidden(e, replay.data()))) return rc;
+    if ((rc = check_mega_status(e))) return rc;
+    float d = 0.f;
+    for (int i = 0; i < dim; i++) {
+        const float x = fabsf(plain[i] - replay[i]);
+        if (!(x <= d)) d = x;      // NaN propagates into the result
+    }
+    *max_diff = d;
+    return MG_OK;
+}
+
 int mg_export_hidden(mg_engine* e, float* hidden_out) {
     int rc = check_engine(e);
     if (rc) return rc;

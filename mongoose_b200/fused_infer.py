@@ -17,6 +17,34 @@ class MongooseError(RuntimeError):
     pass
 
 
+class GraphCaptureConfig:
+    """GraphCaptureConfig (cuda_graph.go:293-298).  StreamCount and PipelineBreak are accepted for
+    source compatibility; the engine runs a layer range on one stream."""
+
+    def __init__(self, LayerStart: int = 0, LayerEnd: int = 0, StreamCount: int = 1, PipelineBreak: int = 0):
+        self.LayerStart, self.LayerEnd = LayerStart, LayerEnd
+        self.StreamCount, self.PipelineBreak = StreamCount, PipelineBreak
+
+
+class CUDAGraph:
+    """CUDAGraph (cuda_graph.go:300-311): a replayable layer range.  The engine keeps its own cached
+    graphs (or the persistent kernel) and reads the position from device memory, so the handle only
+    remembers the range."""
+
+    def __init__(self, engine: "CUDAFusedInference", cfg: GraphCaptureConfig):
+        self._eng, self.config, self.captured = engine, cfg, True
+
+    def Launch(self, pos: int) -> None:
+        """Replay at `pos` on the device-resident hidden state; asynchronous (cuda_graph.go:663-671)."""
+        if not self.captured:
+            return
+        e = self._eng
+        e._check(e._lib.mg_graph_launch(e._h, pos, self.config.LayerStart, self.config.LayerEnd), "CUDAGraph.Launch")
+
+    def Destroy(self) -> None:
+        self.captured = False
+
+
 def _np_ptr(a: np.ndarray):
     return a.ctypes.data_as(C.c_void_p)
 
@@ -94,6 +122,85 @@ class CUDAFusedInference:
                                        _host_ptr(hiddenOut), _host_ptr(logitsOut))
         self._check(rc, "PartialStep")
         return 0
+
+    # -- fp16 weights (cuda_fused_infer.go:274-361, cuda_fused_infer_fp16.go:201-282) ------------
+    @property
+    def WeightsFP16(self) -> bool:
+        from .configs import FMT_F16
+        return self.cfg.layer_fmt == FMT_F16 and self.cfg.head_fmt == FMT_F16
+
+    def _require_fp16(self, what: str):
+        if not self.WeightsFP16:
+            raise MongooseError(f"{what}: this engine was created for quantized weights; create it with "
+                                f"layer_fmt = head_fmt = FMT_F16 (one format per engine)")
+
+    def SetWeightFP16(self, idx: int, data) -> None:
+        """fp32 tensor stored as fp16, no quantization; norms stay fp32 and biases are skipped, as
+        in the reference (cuda_fused_infer.go:276-316)."""
+        self._require_fp16("SetWeightFP16")
+        if idx < self.cfg.n_layers * 12 and idx % 12 in (4, 5, 6):
+            return
+        self.SetWeight(idx, data)
+
+    def SetWeightRawFP16(self, idx: int, fp16Bytes, nElems: int, normData=None) -> None:
+        """Raw fp16 bytes for matrix slots, normData (fp32) for norm slots, biases skipped
+        (cuda_fused_infer.go:318-361)."""
+        from .configs import FMT_F16
+        self._require_fp16("SetWeightRawFP16")
+        nL = self.cfg.n_layers
+        w = idx % 12 if idx < nL * 12 else -1
+        if w in (4, 5, 6):
+            return
+        if w in (0, 8) or idx == nL * 12:
+            self.SetWeight(idx, normData)
+            return
+        a = np.ascontiguousarray(fp16Bytes).view(np.uint8)
+        if a.size != 2 * nElems:
+            raise MongooseError(f"SetWeightRawFP16({idx}): {a.size} bytes for {nElems} elements")
+        self.SetWeightRaw(idx, a, FMT_F16)
+
+    def PartialStepFP16(self, hiddenIn, pos: int, layerStart: int, layerEnd: int, hiddenOut=None,
+                        logitsOut=None) -> int:
+        """PartialStep on fp16 weights (cuda_fused_infer_fp16.go:201-282): the same fused kernels
+        with the fp16 weight path instead of M=1 cuBLAS calls."""
+        self._require_fp16("PartialStepFP16")
+        return self.PartialStep(hiddenIn, pos, layerStart, layerEnd, hiddenOut, logitsOut)
+
+    # -- replay API (cuda_graph.go:313-739) -----------------------------------------------------
+    def CaptureGraph(self, cfg: GraphCaptureConfig, pos: int = 0):
+        """Returns a handle for replaying layers [LayerStart, LayerEnd); None for an unsupported
+        StreamCount, like the reference (cuda_graph.go:315-325)."""
+        if cfg.StreamCount == 0:
+            cfg.StreamCount = 1
+        if cfg.StreamCount not in (1, 2):
+            return None
+        self.BuildFusedDispatch()
+        return CUDAGraph(self, cfg)
+
+    def UpdateAndLaunch(self, g: CUDAGraph, pos: int) -> bool:
+        """The reference re-captures and patches the executable graph for a new position
+        (cuda_graph.go:673-715); here the position is a device-side value, so this is Launch."""
+        if not g.captured:
+            return False
+        g.Launch(pos)
+        return True
+
+    def UploadHidden(self, data) -> None:
+        self._check(self._lib.mg_upload_hidden(self._h, _host_ptr(np.ascontiguousarray(data, np.float32))),
+                    "UploadHidden")
+
+    def ReadHidden(self) -> np.ndarray:
+        return self.ExportHidden()
+
+    def ValidateGraphCapture(self, hiddenIn, layerStart: int, layerEnd: int) -> bool:
+        """Plain launches against the replay path on the same input at position 0; True when the
+        hidden states agree to 1e-3 like the reference's check (cuda_graph.go:554-601)."""
+        d = C.c_float(0.0)
+        a = np.ascontiguousarray(hiddenIn, np.float32)
+        self._check(self._lib.mg_validate_replay(self._h, _np_ptr(a), layerStart, layerEnd, C.byref(d)),
+                    "ValidateGraphCapture")
+        self.last_validate_diff = float(d.value)
+        return bool(d.value < 1e-3)
 
     def ExportHidden(self) -> np.ndarray:
         out = np.empty(self.cfg.dim, np.float32)

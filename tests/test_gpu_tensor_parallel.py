@@ -29,7 +29,9 @@ def run_ranks(world, cases, nccl_exchange=False):
                           os.path.join(ROOT, "tests", "tp_worker.py"), *cases],
                          capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
     assert out.returncode == 0, (out.stdout[-1500:], out.stderr[-3000:])
-    lines = [json.loads(l) for l in out.stdout.splitlines() if l.startswith('{"rank"')]
+    found = [l for l in out.stdout.splitlines() if l.startswith("TP_RESULTS ")]
+    assert len(found) == 1, (out.stdout[-1500:], out.stderr[-3000:])
+    lines = json.loads(found[0][len("TP_RESULTS "):])
     assert len(lines) == world
     return sorted(lines, key=lambda l: l["rank"])
 
@@ -48,7 +50,7 @@ def check(lines, cases, n_new=24, nccl_exchange=False):
 
 def test_two_ranks_match_the_oracle():
     """Partial sums exchanged inside the kernels (peer stores into mapped receive buffers)."""
-    cases = ["tiny", "tiny-bias-ragged", "tiny-q4", "hd128-gqa"]
+    cases = ["tiny", "tiny-bias-ragged", "tiny-q4", "hd128-gqa", "tiny-kv1"]
     check(run_ranks(2, cases), cases)
 
 

@@ -3,7 +3,8 @@ test_gpu_tensor_parallel.py; not collected by pytest).
 
 Every rank builds the same seeded model, hands the FULL tensors to its engine (which keeps its
 shard) and to a CPU oracle, and compares: logits of PartialStep/StepToken within 1e-4 relative,
-greedy tokens identical (ties by the oracle's own logits excepted).  Prints one JSON line.
+greedy tokens identical (ties by the oracle's own logits excepted).  Rank 0 prints every rank's
+results as one JSON line.
 """
 import json
 import os
@@ -28,6 +29,8 @@ CASES = {
     "tiny": (mc.TINY, False),
     "tiny-bias-ragged": (mc.TINY.with_(name="tiny-ragged", vocab=1001), True),
     "tiny-q4": (mc.TINY_Q4, False),
+    # one KV head for four Q heads: with two ranks the KV head (rows, bias, cache) is held by both
+    "tiny-kv1": (mc.TINY.with_(name="tiny-kv1", n_kv_heads=1), True),
     "hd128-gqa": (mc.TINY.with_(name="hd128-gqa", dim=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn_dim=1184,
                                vocab=1500, n_layers=2), True),
 }
@@ -82,7 +85,11 @@ def main():
                          "nccl_exchange": "ncclAllReduce" in note}
         eng.close(); om.close()
         dist.barrier()
-    print(json.dumps({"rank": rank, "world": world, "results": results}), flush=True)
+    # one writer: lines of several ranks on a shared pipe can interleave
+    everyone = [None] * world
+    dist.all_gather_object(everyone, {"rank": rank, "world": world, "results": results})
+    if rank == 0:
+        print("TP_RESULTS " + json.dumps(everyone), flush=True)
     dist.destroy_process_group()
 
 
