@@ -107,6 +107,7 @@ struct mg_engine {
     float* h_in = nullptr;              // hidden-state input of PartialStep on the persistent path
     unsigned int epoch = 16;
     int mk_nslot = 0, mk_slot = MK_SLOT, mk_xs = 0, mk_sc = 0;
+    int mk_prefetch = 0;                // L2 prefetch distance of the tape, bytes
     PhaseGeom mk_geom[5] = {};
     size_t mk_smem = 0;
     size_t tape_bytes = 0;
@@ -683,7 +684,14 @@ bool mega_feasible(mg_engine* e, std::string* why) {
             int max_rows = 0;
             for (int cta = 0; cta < G; cta++)
                 max_rows = std::max(max_rows, (item_begin(s.items, cta + 1, G) - item_begin(s.items, cta, G)) * s.rpi);
-            e->mk_geom[p] = choose_geom(s.fmt, s.K, max_rows, s.rpi == 2, MK_NW, slot);
+            // MG_GEOM_SHIFT="q,w,g,d,h" pins log2(lanes per row) of the five phases (-1 = choose); tuning aid
+            int force = -1;
+            if (const char* gs = getenv("MG_GEOM_SHIFT")) {
+                int v[5] = {-1, -1, -1, -1, -1};
+                sscanf(gs, "%d,%d,%d,%d,%d", &v[0], &v[1], &v[2], &v[3], &v[4]);
+                force = v[p];
+            }
+            e->mk_geom[p] = choose_geom(s.fmt, s.K, max_rows, s.rpi == 2, MK_NW, slot, force);
             if (e->mk_geom[p].ni == 0) {
                 ok = false;
                 const int lpr = s.rpi == 2 ? 16 : 32;
@@ -846,7 +854,7 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
     e->epoch += (unsigned)n_steps * (unsigned)(L * MK_EPOCHS_PER_LAYER + 8);
     a.hd_shift = c.head_dim == 32 ? 5 : c.head_dim == 64 ? 6 : 7;
     for (int p = 0; p < 5; p++) a.geom[p] = e->mk_geom[p];
-    a.nslot = e->mk_nslot; a.slot_bytes = e->mk_slot; a.xs_floats = e->mk_xs; a.sc_floats = e->mk_sc;
+    a.nslot = e->mk_nslot; a.slot_bytes = e->mk_slot; a.prefetch_bytes = e->mk_prefetch; a.xs_floats = e->mk_xs; a.sc_floats = e->mk_sc;
     a.tape = e->tape; a.tape_off = e->tape_off; a.tape_bytes = e->tape_bytes;
     a.norms = e->mk_norms; a.qkv_bias = e->mk_bias;
     a.final_norm = e->vecs[L * 12];
@@ -1029,6 +1037,11 @@ int mg_create(const mg_config* cfg, mg_engine** out) {
     if (env && env[0] == '1') e->use_mega = false;
     env = getenv("MG_NO_PDL");
     if (env && env[0] == '1') e->use_pdl = false;
+    // L2 prefetch distance of the persistent kernel's weight stream; 64 KiB measured best on
+    // 7B-class widths (layer time 85 -> 75 us), neutral on the 0.5 B model, 384 KiB thrashes L2
+    env = getenv("MG_PREFETCH_KB");
+    e->mk_prefetch = (env ? atoi(env) : 64) * 1024;
+    if (e->mk_prefetch < 0 || e->mk_prefetch > (1 << 20)) e->mk_prefetch = 0;
     *out = e;
     return MG_OK;
 }

@@ -86,6 +86,7 @@ struct MegaArgs {
     int hd_shift;           // log2(head_dim)
     int nslot;
     int slot_bytes;       // ring slot size: MK_SLOT, or larger when one tile of the widest matrix needs it
+    int prefetch_bytes;   // how far ahead of the ring the producer asks L2 for this CTA's tape (0 = off)
     int xs_floats;          // size of the staged-activation buffer (multiple of 4)
     PhaseGeom geom[5];
     int sc_floats;          // attention score buffer: max_seq rounded up to a multiple of 4
@@ -150,11 +151,13 @@ __host__ __device__ inline int tile_bytes_of(int fmt, int ni) { return ni * 32 *
 // Lanes per row for a phase whose busiest CTA has max_rows rows: the choice that minimises the
 // chunks a warp walks through (tiles per warp x chunks per lane) among those whose tile fits a ring
 // slot; row pairs must stay inside a tile, so pair phases use at most 16 lanes per row.
-__host__ inline PhaseGeom choose_geom(int fmt, int K, int max_rows, bool pairs, int n_warps, int slot_bytes) {
+__host__ inline PhaseGeom choose_geom(int fmt, int K, int max_rows, bool pairs, int n_warps, int slot_bytes,
+                                      int force_shift = -1) {
     PhaseGeom best{};
     long long best_cost = -1;
     const int nch = chunks_per_row(fmt, K);
     for (int sh = 0; sh <= (pairs ? 4 : 5); sh++) {
+        if (force_shift >= 0 && sh != force_shift) continue;
         const int lpr = 1 << sh, rpt = 32 >> sh;
         const int ni = (nch + lpr - 1) / lpr;
         const int tb = tile_bytes_of(fmt, ni);
@@ -222,6 +225,10 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+// Hint: bring [src, src + bytes) into L2 (16-byte granularity; no completion to wait for).
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(MK_CONSUMERS) : "memory"); }
 
 // Exchange words are 64-bit {value (low), tag (high)}: each is read and written as ONE 8-byte
@@ -254,7 +261,8 @@ struct MkCtx {
     unsigned int entry;           // running ring-entry counter of this thread's role (diagnostics)
     int slot;                     // ring slot of the next entry
     unsigned int par;             // phase parity of that slot
-    __device__ __forceinline__ MkCtx(const MegaArgs& args) : a(args), entry(0), slot(0), par(0) {}
+    unsigned long long pf;        // producer: tape offset up to which L2 prefetches have been issued
+    __device__ __forceinline__ MkCtx(const MegaArgs& args) : a(args), entry(0), slot(0), par(0), pf(0) {}
     __device__ __forceinline__ void advance() {
         entry++;
         if (++slot == a.nslot) { slot = 0; par ^= 1u; }
@@ -493,6 +501,23 @@ __device__ __forceinline__ void mk_produce_phase(MkCtx& c, const MegaArgs& a, co
         bulk_g2s(c.ring() + (size_t)slot * a.slot_bytes, src, bytes, &c.full()[slot]);
         src += bytes;
         c.advance();
+        if (a.prefetch_bytes > 0) {
+            // The ring alone keeps nslot * slot_bytes in flight per SM, too little to saturate HBM when
+            // the activations crowd the ring (wide models).  The tape of a CTA is one contiguous run
+            // through all phases and layers, so the producer also asks L2 for the bytes a fixed distance
+            // ahead; the ring then fills from L2 and DRAM runs ahead of it.
+            const unsigned long long pos = (unsigned long long)(src - a.tape);
+            unsigned long long want = pos + (unsigned long long)a.prefetch_bytes;
+            if (want > a.tape_bytes) want = a.tape_bytes;
+            if (c.pf < pos) c.pf = pos;
+            while (c.pf + 16 <= want) {
+                unsigned long long n = want - c.pf;
+                if (n > 8192ull) n = 8192ull;
+                n &= ~15ull;
+                bulk_prefetch_l2(a.tape + c.pf, (uint32_t)n);
+                c.pf += n;
+            }
+        }
     }
 }
 
