@@ -248,6 +248,30 @@ MG_API int mg_graph_launch(mg_engine* e, int pos, int layer_start, int layer_end
  * the two hidden states (the reference accepts < 1e-3).  Resets the KV cache. */
 MG_API int mg_validate_replay(mg_engine* e, const float* hidden_in, int layer_start, int layer_end, float* max_diff);
 
+/* ---- layer-range pipeline (SetLayerRange, PartialStepContinue, QueueHiddenToL3, WaitL3, WaitMailbox;
+ * cuda_fused_infer.go:461-737) ----------------------------------------------------------------------
+ * A stage is an engine that holds a contiguous range of layers (the last stage also the final norm and
+ * lm_head).  The reference hands the hidden state from stage to stage through a pinned host buffer
+ * ("L3 bridge") and a mailbox counter polled without a time limit; here the hand-over between GPUs of
+ * one process is a peer copy over NVLink ordered by events, and every host-side wait has a deadline. */
+/* SetLayerRange (cuda_fused_infer.go:542-556): only these layers need weights; steps outside fail. */
+MG_API int mg_set_layer_range(mg_engine* e, int layer_start, int layer_end);
+/* PartialStepContinue (cuda_fused_infer.go:463-528): PartialStep on the hidden state already on the
+ * device (uploaded, left by the previous range, or queued by the previous stage). */
+MG_API int mg_partial_step_continue(mg_engine* e, int pos, int layer_start, int layer_end, float* hidden_out,
+                                    float* logits_out);
+/* Hands src's device-resident hidden state to dst (another GPU: cudaMemcpyPeerAsync) on src's stream
+ * and makes dst's stream wait for it; asynchronous. */
+MG_API int mg_queue_hidden_to(mg_engine* src, mg_engine* dst);
+/* WaitMailbox (cuda_fused_infer.go:575-591) with a deadline: MG_OK once the hidden state last queued
+ * to e has arrived, MG_ERR_TIMEOUT after timeout_ms (also when nothing was queued). */
+MG_API int mg_wait_mailbox(mg_engine* e, int timeout_ms);
+/* QueueHiddenToL3 / WaitL3 / GetL3Hidden (cuda_fused_infer.go:686-726): asynchronous copy of the hidden
+ * state to a pinned host buffer on a second stream; the compute stream is not blocked. */
+MG_API int mg_queue_hidden_to_l3(mg_engine* e);
+MG_API int mg_wait_l3(mg_engine* e, int timeout_ms);
+MG_API const float* mg_l3_hidden(mg_engine* e);
+
 /* ---- tensor-parallel decode over 2/4/8 GPUs of one node, one process per GPU ----------------------
  * The reference has no tensor parallelism (multigpu.go:32-82, 496-623 manages per-device handles and
  * peer copies only); these calls split one model over ranks.  QKV, gate and up are split by rows at

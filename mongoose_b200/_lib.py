@@ -80,6 +80,13 @@ SIGNATURES = {
     "mg_dequant_rows": (ci, [vp, ci, ci, ci, vp]),
     "mg_read_kv": (ci, [vp, ci, ci, ci, vp, vp]),
     "mg_trace_step": (ci, [vp, vp, ci, vp, vp]),
+    "mg_set_layer_range": (ci, [vp, ci, ci]),
+    "mg_partial_step_continue": (ci, [vp, ci, ci, ci, vp, vp]),
+    "mg_queue_hidden_to": (ci, [vp, vp]),
+    "mg_wait_mailbox": (ci, [vp, ci]),
+    "mg_queue_hidden_to_l3": (ci, [vp]),
+    "mg_wait_l3": (ci, [vp, ci]),
+    "mg_l3_hidden": (vp, [vp]),
     "mg_upload_hidden": (ci, [vp, vp]),
     "mg_graph_launch": (ci, [vp, ci, ci, ci]),
     "mg_validate_replay": (ci, [vp, vp, ci, ci, vp]),

@@ -15,6 +15,8 @@
 #include <nccl.h>
 
 #include <algorithm>
+#include <chrono>
+#include <thread>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -117,6 +119,15 @@ struct mg_engine {
     long long launches = 0;
     int capture_kernels = 0;            // kernels enqueued by the current enqueue_step
     size_t dev_bytes = 0;
+    // layer-range pipeline (mg_set_layer_range, mg_queue_hidden_to, L3 bridge)
+    int own_ls = 0, own_le = 0;         // layers this engine holds weights for; [0, n_layers) by default
+    cudaEvent_t sent_event = nullptr;   // recorded after this engine's hidden state has been copied to the next stage
+    mg_engine* mail_from = nullptr;     // stage whose hidden state was last queued to this engine
+    unsigned int mail_queued = 0, mail_taken = 0;
+    float* l3 = nullptr;                // pinned host copy of the hidden state (the reference's "L3 bridge")
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t compute_done = nullptr, l3_done = nullptr;
+    bool l3_queued = false;
     // tensor parallelism (mg_tp_init)
     Shard sh;
     ncclComm_t comm = nullptr;
@@ -738,10 +749,16 @@ int build_mega(mg_engine* e) {
     auto phase_bytes = [&](int p, int cta) {
         return (unsigned long long)phase_tiles(p, cta) * e->mk_geom[p].tile_bytes;
     };
+    // a pipeline stage streams only the layers it owns (and lm_head only with the last layer)
+    auto owned = [&](int l) { return l < L ? (l >= e->own_ls && l < e->own_le) : e->own_le >= L; };
     for (int cta = 0; cta < G; cta++) {
         for (int l = 0; l < L; l++)
-            for (int p = 0; p < 4; p++) { off[(size_t)cta * ncol + l * 4 + p] = total; total += phase_bytes(p, cta); }
-        off[(size_t)cta * ncol + L * 4] = total; total += phase_bytes(PH_HEAD, cta);
+            for (int p = 0; p < 4; p++) {
+                off[(size_t)cta * ncol + l * 4 + p] = total;
+                if (owned(l)) total += phase_bytes(p, cta);
+            }
+        off[(size_t)cta * ncol + L * 4] = total;
+        if (owned(L)) total += phase_bytes(PH_HEAD, cta);
         off[(size_t)cta * ncol + L * 4 + 1] = total;
     }
     std::vector<uint8_t> tape((size_t)total + e->mk_slot, 0);
@@ -752,6 +769,7 @@ int build_mega(mg_engine* e) {
     MG_CUDA(e, cudaStreamSynchronize(e->stream));
     for (int l = 0; l <= L; l++)
         for (int p = (l < L ? 0 : PH_HEAD); p <= (l < L ? 3 : PH_HEAD); p++) {
+            if (!owned(l)) continue;
             int slots[3], nm = 0;
             phase_matrices(c, l, p, slots, &nm);
             const PhaseShape s = phase_shape_of(p, c.dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
@@ -807,6 +825,7 @@ int build_mega(mg_engine* e) {
     MG_CUDA(e, cudaMalloc((void**)&e->mk_norms, (size_t)L * 2 * c.dim * 4));
     bool any_bias = false;
     for (int l = 0; l < L; l++) {
+        if (!owned(l)) continue;
         MG_CUDA(e, cudaMemcpy(e->mk_norms + (size_t)l * 2 * c.dim, e->vecs[l * 12 + 0], (size_t)c.dim * 4, cudaMemcpyDeviceToDevice));
         MG_CUDA(e, cudaMemcpy(e->mk_norms + (size_t)l * 2 * c.dim + c.dim, e->vecs[l * 12 + 8], (size_t)c.dim * 4, cudaMemcpyDeviceToDevice));
         any_bias = any_bias || e->vecs[l * 12 + 4] || e->vecs[l * 12 + 5] || e->vecs[l * 12 + 6];
@@ -816,6 +835,7 @@ int build_mega(mg_engine* e) {
         MG_CUDA(e, cudaMalloc((void**)&e->mk_bias, (size_t)L * bw * 4));
         MG_CUDA(e, cudaMemset(e->mk_bias, 0, (size_t)L * bw * 4));     // an unset bias adds zero
         for (int l = 0; l < L; l++) {
+            if (!owned(l)) continue;
             const size_t offs[3] = {0, (size_t)c.dim, (size_t)c.dim + c.kv_dim};
             const size_t lens[3] = {(size_t)c.dim, (size_t)c.kv_dim, (size_t)c.kv_dim};
             for (int k = 0; k < 3; k++)
@@ -895,7 +915,18 @@ int check_mega_status(mg_engine* e) {
     return MG_OK;
 }
 
+// A step may only touch layers this engine holds (the whole model unless mg_set_layer_range narrowed it).
+int check_range(mg_engine* e, int ls, int le, bool head, bool embed) {
+    const int L = e->cfg.n_layers;
+    if (std::min(le, L) > ls && (ls < e->own_ls || std::min(le, L) > e->own_le))
+        return fail(e, MG_ERR_STATE, "layers [%d,%d) requested, this engine holds [%d,%d)", ls, le, e->own_ls, e->own_le);
+    if ((head || embed) && e->own_le < L && !e->mats[L * 12 + 1].set)
+        return fail(e, MG_ERR_STATE, "lm_head (and the tied embedding) live on the stage that holds the last layer");
+    return MG_OK;
+}
+
 int run_step(mg_engine* e, int ls, int le, int mode, int head) {
+    if (int rc = check_range(e, ls, le, head != HEAD_NONE && le >= e->cfg.n_layers, mode == MODE_EMBED)) return rc;
     if (e->mega_ok && le > ls) return launch_mega(e, ls, le, mode, head, 1);
     if (!e->use_graph) {
         int rc = enqueue_step(e, e->stream, ls, le, mode, head);
@@ -986,6 +1017,13 @@ int mg_create(const mg_config* cfg, mg_engine** out) {
         std::string why;
         if (!make_shard(c, 0, 1, &e->sh, &why)) return bail(MG_ERR_ARG);
     }
+    e->own_ls = 0; e->own_le = c.n_layers;
+    if (cudaEventCreateWithFlags(&e->sent_event, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&e->compute_done, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&e->l3_done, cudaEventDisableTiming) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&e->copy_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaMallocHost((void**)&e->l3, (size_t)c.dim * sizeof(float)) != cudaSuccess)
+        return bail(MG_ERR_CUDA);
     const int nw = c.n_layers * 12 + 2;
     e->mats.resize(nw);
     e->vecs.assign(nw, nullptr);
@@ -1074,6 +1112,11 @@ void mg_destroy(mg_engine* e) {
     if (e->logits_all) cudaFree(e->logits_all);
     if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
     if (e->pin_i) cudaFreeHost(e->pin_i);
+    if (e->copy_stream) { cudaStreamSynchronize(e->copy_stream); cudaStreamDestroy(e->copy_stream); }
+    if (e->l3) cudaFreeHost(e->l3);
+    if (e->sent_event) cudaEventDestroy(e->sent_event);
+    if (e->compute_done) cudaEventDestroy(e->compute_done);
+    if (e->l3_done) cudaEventDestroy(e->l3_done);
     if (e->stream) cudaStreamDestroy(e->stream);
     delete e;
 }
@@ -1136,6 +1179,9 @@ int mg_build(mg_engine* e) {
         slot_info(c, idx, &is_matrix, &rows, &cols, &fmt);
         const int w = idx < c.n_layers * 12 ? idx % 12 : -1;
         if (w >= 4 && w <= 6) continue;   // biases are optional (cuda_fused_infer.go:255)
+        // a pipeline stage holds its own layers; the final norm and lm_head go with the last layer
+        if (w >= 0 && (idx / 12 < e->own_ls || idx / 12 >= e->own_le)) continue;
+        if (w < 0 && e->own_le < c.n_layers) continue;
         if (is_matrix ? !e->mats[idx].set : e->vecs[idx] == nullptr)
             return fail(e, MG_ERR_STATE, "mg_build: weight slot %d has not been set", idx);
     }
@@ -1207,6 +1253,117 @@ int mg_partial_step(mg_engine* e, const float* hidden_in, int pos, int layer_sta
     MG_CUDA(e, cudaStreamSynchronize(e->stream));
     return check_mega_status(e);
 }
+
+int mg_set_layer_range(mg_engine* e, int layer_start, int layer_end) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if (layer_start < 0 || layer_end <= layer_start || layer_end > e->cfg.n_layers)
+        return fail(e, MG_ERR_ARG, "mg_set_layer_range: bad range [%d,%d) of %d layers", layer_start, layer_end, e->cfg.n_layers);
+    if (e->sh.size > 1) return fail(e, MG_ERR_UNSUPPORTED, "mg_set_layer_range: not combined with tensor parallelism");
+    e->own_ls = layer_start; e->own_le = layer_end;
+    e->built = false;
+    return MG_OK;
+}
+
+int mg_partial_step_continue(mg_engine* e, int pos, int layer_start, int layer_end, float* hidden_out, float* logits_out) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if ((rc = ensure_built(e))) return rc;
+    const mg_config& c = e->cfg;
+    if (pos < 0 || pos >= c.max_seq || layer_start < 0 || layer_end < layer_start)
+        return fail(e, MG_ERR_ARG, "mg_partial_step_continue: bad arguments (pos %d, layers [%d,%d))", pos, layer_start, layer_end);
+    if (layer_end > c.n_layers) layer_end = c.n_layers;
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));   // pin_i is reused; a queued hidden state has landed after this
+    e->pin_i[0] = pos; e->pin_i[1] = 0;
+    MG_CUDA(e, cudaMemcpyAsync(e->st, e->pin_i, 8, cudaMemcpyHostToDevice, e->stream));
+    const bool want_logits = layer_end >= c.n_layers && logits_out;
+    if ((rc = run_step(e, layer_start, layer_end, MODE_HIDDEN, want_logits ? HEAD_LOGITS : HEAD_NONE))) return rc;
+    if (want_logits)
+        MG_CUDA(e, cudaMemcpyAsync(logits_out, e->logits, (size_t)c.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
+    else if (hidden_out)
+        MG_CUDA(e, cudaMemcpyAsync(hidden_out, e->h, (size_t)c.dim * 4, cudaMemcpyDeviceToHost, e->stream));
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    return check_mega_status(e);
+}
+
+int mg_queue_hidden_to(mg_engine* src, mg_engine* dst) {
+    int rc = check_engine(src);
+    if (rc) return rc;
+    if (!dst || dst == src || dst->cfg.dim != src->cfg.dim)
+        return fail(src, MG_ERR_ARG, "mg_queue_hidden_to: the next stage must be another engine of the same width");
+    const size_t bytes = (size_t)src->cfg.dim * sizeof(float);
+    // the copy must not land while the next stage is still working on its previous hidden state
+    if ((rc = check_engine(dst))) return rc;
+    MG_CUDA(dst, cudaEventRecord(dst->compute_done, dst->stream));
+    if ((rc = check_engine(src))) return rc;
+    MG_CUDA(src, cudaStreamWaitEvent(src->stream, dst->compute_done, 0));
+    if (src->cfg.device != dst->cfg.device) {
+        // over NVLink when the two GPUs can address each other, staged by the driver otherwise
+        int can = 0;
+        cudaDeviceCanAccessPeer(&can, src->cfg.device, dst->cfg.device);
+        if (can && cudaDeviceEnablePeerAccess(dst->cfg.device, 0) != cudaSuccess) cudaGetLastError();   // already on: fine
+        MG_CUDA(src, cudaMemcpyPeerAsync(dst->h, dst->cfg.device, src->h, src->cfg.device, bytes, src->stream));
+    } else {
+        MG_CUDA(src, cudaMemcpyAsync(dst->h, src->h, bytes, cudaMemcpyDeviceToDevice, src->stream));
+    }
+    MG_CUDA(src, cudaEventRecord(src->sent_event, src->stream));
+    // the next stage's stream orders itself after the copy; its host thread may also ask with mg_wait_mailbox
+    if ((rc = check_engine(dst))) return rc;
+    MG_CUDA(dst, cudaStreamWaitEvent(dst->stream, src->sent_event, 0));
+    dst->mail_from = src;
+    dst->mail_queued++;
+    return MG_OK;
+}
+
+int mg_wait_mailbox(mg_engine* e, int timeout_ms) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    const auto t0 = std::chrono::steady_clock::now();
+    auto expired = [&]() {
+        return std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() >= timeout_ms;
+    };
+    for (;;) {
+        if (e->mail_queued != e->mail_taken && e->mail_from) {
+            const cudaError_t q = cudaEventQuery(e->mail_from->sent_event);
+            if (q == cudaSuccess) { e->mail_taken = e->mail_queued; return MG_OK; }
+            if (q != cudaErrorNotReady) return fail(e, MG_ERR_CUDA, "mg_wait_mailbox: %s", cudaGetErrorString(q));
+        }
+        if (expired())
+            return fail(e, MG_ERR_TIMEOUT, "mg_wait_mailbox: no hidden state arrived within %d ms (%s)", timeout_ms,
+                        e->mail_queued != e->mail_taken ? "copy still in flight" : "nothing was queued");
+        std::this_thread::yield();
+    }
+}
+
+int mg_queue_hidden_to_l3(mg_engine* e) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    MG_CUDA(e, cudaEventRecord(e->compute_done, e->stream));
+    MG_CUDA(e, cudaStreamWaitEvent(e->copy_stream, e->compute_done, 0));
+    MG_CUDA(e, cudaMemcpyAsync(e->l3, e->h, (size_t)e->cfg.dim * sizeof(float), cudaMemcpyDeviceToHost, e->copy_stream));
+    MG_CUDA(e, cudaEventRecord(e->l3_done, e->copy_stream));
+    // later steps overwrite the hidden state: they start once the copy (dim floats) has read it
+    MG_CUDA(e, cudaStreamWaitEvent(e->stream, e->l3_done, 0));
+    e->l3_queued = true;
+    return MG_OK;
+}
+
+int mg_wait_l3(mg_engine* e, int timeout_ms) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if (!e->l3_queued) return fail(e, MG_ERR_STATE, "mg_wait_l3: nothing was queued");
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        const cudaError_t q = cudaEventQuery(e->l3_done);
+        if (q == cudaSuccess) return MG_OK;
+        if (q != cudaErrorNotReady) return fail(e, MG_ERR_CUDA, "mg_wait_l3: %s", cudaGetErrorString(q));
+        if (std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() >= timeout_ms)
+            return fail(e, MG_ERR_TIMEOUT, "mg_wait_l3: the copy did not finish within %d ms", timeout_ms);
+        std::this_thread::yield();
+    }
+}
+
+const float* mg_l3_hidden(mg_engine* e) { return e ? e->l3 : nullptr; }
 
 int mg_upload_hidden(mg_engine* e, const float* hidden) {
     int rc = check_engine(e);
@@ -1295,6 +1452,7 @@ int mg_enqueue_greedy(mg_engine* e, int n_steps) {
     if (rc) return rc;
     if ((rc = ensure_built(e))) return rc;
     if (n_steps <= 0) return MG_OK;
+    if ((rc = check_range(e, 0, e->cfg.n_layers, true, true))) return rc;
     if (e->mega_ok) return launch_mega(e, 0, e->cfg.n_layers, MODE_EMBED, HEAD_ARGMAX, n_steps);
     for (int i = 0; i < n_steps; i++)
         if ((rc = run_step(e, 0, e->cfg.n_layers, MODE_EMBED, HEAD_ARGMAX))) return rc;
@@ -1312,6 +1470,7 @@ int mg_generate(mg_engine* e, const int* prompt, int n_prompt, int n_new, int st
                     n_prompt, n_new, start_pos, c.max_seq);
     for (int i = 0; i < n_prompt; i++)
         if (prompt[i] < 0 || prompt[i] >= c.vocab) return fail(e, MG_ERR_ARG, "mg_generate: prompt id out of range");
+    if ((rc = check_range(e, 0, c.n_layers, true, true))) return rc;
     MG_CUDA(e, cudaStreamSynchronize(e->stream));
     e->pin_i[0] = start_pos; e->pin_i[1] = prompt[0]; e->pin_i[2] = 0;
     for (int i = 0; i < n_prompt; i++) e->pin_i[8 + i] = prompt[i];

@@ -166,6 +166,52 @@ class CUDAFusedInference:
         self._require_fp16("PartialStepFP16")
         return self.PartialStep(hiddenIn, pos, layerStart, layerEnd, hiddenOut, logitsOut)
 
+    # -- layer-range pipeline (cuda_fused_infer.go:461-737) -------------------------------------
+    def SetLayerRange(self, layerStart: int, layerEnd: int) -> None:
+        """This engine is a pipeline stage holding layers [layerStart, layerEnd); the last stage also
+        holds the final norm and lm_head (cuda_fused_infer.go:542-556)."""
+        self._check(self._lib.mg_set_layer_range(self._h, layerStart, layerEnd), "SetLayerRange")
+
+    def PartialStepContinue(self, pos: int, layerStart: int, layerEnd: int, hiddenOut=None, logitsOut=None) -> int:
+        """PartialStep without the upload: the hidden state is already on the device
+        (cuda_fused_infer.go:463-528)."""
+        rc = self._lib.mg_partial_step_continue(self._h, pos, layerStart, layerEnd, _host_ptr(hiddenOut),
+                                                _host_ptr(logitsOut))
+        self._check(rc, "PartialStepContinue")
+        return 0
+
+    def QueueHiddenTo(self, nxt: "CUDAFusedInference") -> None:
+        """Hand the device-resident hidden state to the next stage (peer copy over NVLink between
+        GPUs); asynchronous.  Replaces the reference's hop through host memory."""
+        self._check(self._lib.mg_queue_hidden_to(self._h, nxt._h), "QueueHiddenTo")
+
+    def WaitMailbox(self, timeout_ms: int = 1000) -> None:
+        """Returns once the hidden state queued to this stage has arrived; raises after timeout_ms
+        (the reference polls without a limit, cuda_fused_infer.go:575-591)."""
+        self._check(self._lib.mg_wait_mailbox(self._h, timeout_ms), "WaitMailbox")
+
+    def HasMailbox(self) -> bool:
+        return True
+
+    def HasL3(self) -> bool:
+        return True
+
+    def QueueHiddenToL3(self) -> None:
+        """Asynchronous copy of the hidden state to the pinned host buffer on the copy stream
+        (cuda_fused_infer.go:686-703)."""
+        self._check(self._lib.mg_queue_hidden_to_l3(self._h), "QueueHiddenToL3")
+
+    def WaitL3(self, timeout_ms: int = 1000) -> None:
+        self._check(self._lib.mg_wait_l3(self._h, timeout_ms), "WaitL3")
+
+    def GetL3Hidden(self) -> np.ndarray:
+        """The pinned host buffer as an array; valid after QueueHiddenToL3 + WaitL3."""
+        p = self._lib.mg_l3_hidden(self._h)
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(self.cfg.dim,)).copy()
+
+    def ReadHiddenBlocking(self) -> np.ndarray:
+        return self.ExportHidden()
+
     # -- replay API (cuda_graph.go:313-739) -----------------------------------------------------
     def CaptureGraph(self, cfg: GraphCaptureConfig, pos: int = 0):
         """Returns a handle for replaying layers [LayerStart, LayerEnd); None for an unsupported

@@ -19,8 +19,12 @@ mx = multi.reduce_max(ms, dist)
 dist.barrier()
 seqs = multi.sequences_for_rank(7, rank, world)
 prompt = synthetic.prompt_ids(rank, 4, 1000).tolist()
-print(json.dumps({"rank": rank, "max": mx, "seqs": seqs, "prompt": prompt,
-                  "rate": multi.aggregate_rate(world, 200, mx[0])}), flush=True)
+mine = {"rank": rank, "max": mx, "seqs": seqs, "prompt": prompt,
+        "rate": multi.aggregate_rate(world, 200, mx[0])}
+everyone = [None] * world
+dist.all_gather_object(everyone, mine)          # one writer: lines of two ranks on one pipe can interleave
+if rank == 0:
+    print("RESULTS " + json.dumps(everyone), flush=True)
 dist.destroy_process_group()
 """ % ROOT
 
@@ -33,7 +37,9 @@ def test_two_ranks_agree_on_max_time_and_split_sequences(tmp_path):
                          capture_output=True, text=True, timeout=240)
     assert out.returncode == 0, out.stderr[-2000:]
     import json
-    lines = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+    found = [l for l in out.stdout.splitlines() if l.startswith("RESULTS ")]
+    assert len(found) == 1, out.stdout[-1000:]
+    lines = json.loads(found[0][len("RESULTS "):])
     assert len(lines) == 2
     by = {l["rank"]: l for l in lines}
     for r in (0, 1):

@@ -91,7 +91,10 @@ parts = [None] * world
 dist.all_gather_object(parts, mine)
 box = [os.urandom(128) if rank == 0 else None]
 dist.broadcast_object_list(box, src=0)
-print(json.dumps({"rank": rank, "parts": parts, "id": box[0].hex()}), flush=True)
+everyone = [None] * world
+dist.all_gather_object(everyone, {"rank": rank, "parts": parts, "id": box[0].hex()})
+if rank == 0:
+    print("RESULTS " + json.dumps(everyone), flush=True)
 dist.destroy_process_group()
 """ % ROOT
 
@@ -104,7 +107,9 @@ def test_two_gloo_ranks_agree_on_the_partition_and_the_id(tmp_path):
                          capture_output=True, text=True, timeout=240)
     assert out.returncode == 0, out.stderr[-2000:]
     import json
-    lines = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+    found = [l for l in out.stdout.splitlines() if l.startswith("RESULTS ")]
+    assert len(found) == 1, out.stdout[-1000:]
+    lines = json.loads(found[0][len("RESULTS "):])
     assert len(lines) == 2
     a, b = sorted(lines, key=lambda l: l["rank"])
     assert a["parts"] == b["parts"] and a["id"] == b["id"] and len(a["id"]) == 256
