@@ -5,9 +5,11 @@
 // loads; lanes stride over the row's 16-byte chunks, so a warp instruction
 // reads 512 contiguous bytes per row.  The activation vector is staged once
 // per CTA in shared memory (after the fused RMSNorm / embedding prologue)
-// and shared by the R rows of a tile.  Weights are dequantized in registers,
-// block scales applied once per chunk, accumulation is fp32, and the R sums
-// are reduced with warp shuffles.  The epilogue is fused: RoPE + fp16 KV
+// and shared by the R rows of a tile: as 24-bit fixed point for int8 / 4-bit
+// weights (integer dp4a dot products, exact per group of 16), as fp32 for
+// fp16 weights.  Block scales are applied once per chunk, accumulation across
+// chunks is fp32, and the R sums are reduced with warp shuffles.  The
+// epilogue is fused: RoPE + fp16 KV
 // append for QKV, residual add for wo/down, SiLU-gate for gate/up, argmax
 // for lm_head.
 //
