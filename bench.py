@@ -94,13 +94,25 @@ def measured_peak_gbs():
 
 class ClockSampler:
     """nvidia-smi sampling of SM clocks and throttle reasons during the timed region."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
         self.idx = gpu_index
         self.proc = None
+        self.t0 = self.t1 = None
+
+    # nvidia-smi needs a few hundred ms to come up, longer than a short timed region: start it
+    # early (start), then bracket the timed region (begin / end); stop() keeps the samples whose
+    # timestamps fall inside the bracket (widened by one sampling period).
+    def begin(self):
+        import datetime
+        self.t0 = datetime.datetime.now()
+
+    def end(self):
+        import datetime
+        self.t1 = datetime.datetime.now()
 
     def start(self):
         try:
@@ -119,12 +131,21 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
+        import datetime
         sm, mx, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        slack = datetime.timedelta(milliseconds=25)
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
+            if self.t0 is not None and self.t1 is not None:
+                try:
+                    ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f")
+                except ValueError:
+                    continue
+                if ts < self.t0 - slack or ts > self.t1 + slack:
+                    continue
             try:
                 sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
             except ValueError:
@@ -237,6 +258,9 @@ def run_b200_arm(args, cfg, rank, world, local_rank):
         eng.SetCursor(tok, PROMPT_LEN)
         return PROMPT_LEN
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()                                     # comes up during the warm-up
+
     # ---- warm-up: W greedy steps on the same graph, then start over ----
     feed_prompt()
     eng.EnqueueGreedy(min(W, cfg.max_seq - PROMPT_LEN))
@@ -244,15 +268,15 @@ def run_b200_arm(args, cfg, rank, world, local_rank):
 
     # ---- timed: device-resident greedy decode ----
     first_pos = feed_prompt()
-    sampler = ClockSampler(local_rank)
     launches0 = eng.LaunchCount()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    sampler.start()
+    sampler.begin()
     ev0.record(stream)
     eng.EnqueueGreedy(K)
     ev1.record(stream)
     eng.Sync()
+    sampler.end()
     barrier()
     clocks = sampler.stop()
     ms = ev0.elapsed_time(ev1)
@@ -350,14 +374,15 @@ def run_sequences_arm(args, cfg, rank, world, local_rank):
     eng.BuildFusedDispatch()
     mine = multi.sequences_for_rank(args.sequences, rank, world)
     stream = torch.cuda.ExternalStream(eng.stream, device=local_rank)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         eng.StepToken(1, 0)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local_rank)
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
-    sampler.start()
+    sampler.begin()
     launches0 = eng.LaunchCount()
     ev0.record(stream)
     tails = []
@@ -367,6 +392,7 @@ def run_sequences_arm(args, cfg, rank, world, local_rank):
         tails.append(int(toks[-1]))
     ev1.record(stream)
     torch.cuda.synchronize()
+    sampler.end()
     if dist is not None:
         dist.barrier()
     clocks = sampler.stop()
