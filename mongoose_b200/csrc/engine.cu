@@ -466,10 +466,15 @@ int pick_rows_per_tile(const mg_engine* e, int rows) {
     return 1;
 }
 
-// Layout of the exchange buffer (the same on every rank): [2 slots][size][dim] 8-byte words
-// {value, exchange number}, then this rank's own counters (count[2], ticket[2]).
-inline size_t xchg_rows_bytes(const mg_engine* e) { return (size_t)2 * e->sh.size * e->cfg.dim * 8; }
-inline size_t xchg_bytes(const mg_engine* e) { return xchg_rows_bytes(e) + 256; }
+// Layout of the exchange buffer (the same on every rank): [4 slots][size][dim] 8-byte words
+// {value, exchange number} (slots 0, 1: per-phase kernels after wo / down; slots 2, 3: persistent
+// kernel), then this rank's own counters (count[2], ticket[2]), then [size][2] words for the
+// persistent kernel's argmax exchange.
+inline size_t xchg_rows_bytes(const mg_engine* e) { return (size_t)4 * e->sh.size * e->cfg.dim * 8; }
+inline size_t xchg_bytes(const mg_engine* e) { return xchg_rows_bytes(e) + 256 + (size_t)e->sh.size * 16; }
+inline unsigned long long* xchg_best(const mg_engine* e, uint8_t* base) {
+    return reinterpret_cast<unsigned long long*>(base + xchg_rows_bytes(e) + 256);
+}
 inline unsigned long long* xchg_row(const mg_engine* e, uint8_t* base, int slot, int sender) {
     return reinterpret_cast<unsigned long long*>(base) + ((size_t)slot * e->sh.size + sender) * e->cfg.dim;
 }
@@ -650,6 +655,21 @@ void free_mega(mg_engine* e) {
     e->mega_ok = false;
 }
 
+// The model as the persistent kernel of THIS rank sees it: dim is the model width, every other size
+// is the rank's share (the whole model without tensor parallelism); q_dim = rows of Q held here.
+mg_config mega_cfg(const mg_engine* e, int* q_dim, int* vocab_base) {
+    mg_config c = e->cfg;
+    const Shard& sh = e->sh;
+    c.n_heads = sh.q1 - sh.q0;
+    c.n_kv_heads = sh.kv1 - sh.kv0;
+    c.kv_dim = c.n_kv_heads * c.head_dim;
+    c.ffn_dim = sh.f1 - sh.f0;
+    c.vocab = sh.v1 - sh.v0;
+    *q_dim = c.n_heads * c.head_dim;
+    *vocab_base = sh.v0;
+    return c;
+}
+
 // Matrix slots that feed phase p of layer l, in the order the phase's items name them.
 void phase_matrices(const mg_config& c, int l, int p, int out[3], int* n) {
     const int b = l * 12;
@@ -663,10 +683,10 @@ void phase_matrices(const mg_config& c, int l, int p, int out[3], int* n) {
 }
 
 // Rows (matrix ordinal within the phase, row) of work item `item`, in tape order.
-inline int item_rows(const mg_config& c, int p, int item, int m_out[2], int r_out[2]) {
+inline int item_rows(const mg_config& c, int q_dim, int p, int item, int m_out[2], int r_out[2]) {
     if (p == PH_QKV) {
         int m, r0, r1;
-        qkv_pair(item, c.dim, c.kv_dim, c.head_dim, &m, &r0, &r1);
+        qkv_pair(item, q_dim, c.kv_dim, c.head_dim, &m, &r0, &r1);
         m_out[0] = m_out[1] = m; r_out[0] = r0; r_out[1] = r1;
         return 2;
     }
@@ -677,9 +697,11 @@ inline int item_rows(const mg_config& c, int p, int item, int m_out[2], int r_ou
 
 // Decide whether the persistent kernel can run this model and with how many ring slots.
 bool mega_feasible(mg_engine* e, std::string* why) {
-    const mg_config& c = e->cfg;
+    int q_dim, vocab_base;
+    const mg_config c = mega_cfg(e, &q_dim, &vocab_base);
     const int G = e->num_sms;
-    if (e->sh.size > 1) { *why = "tensor parallelism uses the per-phase kernels"; return false; }
+    if (e->sh.size > 1 && !e->tp_fused) { *why = "tensor parallelism through NCCL uses the per-phase kernels"; return false; }
+    if (e->sh.size > 1 && e->own_le - e->own_ls != c.n_layers) { *why = "layer ranges are not combined with tensor parallelism"; return false; }
     int coop = 0;
     cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, c.device);
     if (!coop) { *why = "cooperative launch unsupported"; return false; }
@@ -691,7 +713,7 @@ bool mega_feasible(mg_engine* e, std::string* why) {
     for (int pass = 0; pass < 2; pass++) {
         bool ok = true;
         for (int p = 0; p <= PH_HEAD; p++) {
-            const PhaseShape s = phase_shape_of(p, c.dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
+            const PhaseShape s = phase_shape_of(p, c.dim, q_dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
             int max_rows = 0;
             for (int cta = 0; cta < G; cta++)
                 max_rows = std::max(max_rows, (item_begin(s.items, cta + 1, G) - item_begin(s.items, cta, G)) * s.rpi);
@@ -714,6 +736,7 @@ bool mega_feasible(mg_engine* e, std::string* why) {
         if (pass == 1) { *why = "a weight tile does not fit a ring slot"; return false; }
     }
     int xs = c.dim > c.ffn_dim ? c.dim : c.ffn_dim;
+    if (xs < q_dim) xs = q_dim;
     if (xs < 3 * c.head_dim) xs = 3 * c.head_dim;
     xs = (xs + 3) & ~3;
     const int sc = (c.max_seq + 3) & ~3;
@@ -731,17 +754,43 @@ int build_mega(mg_engine* e) {
     free_mega(e);
     if (!e->use_mega) return MG_OK;
     std::string why;
-    if (!mega_feasible(e, &why)) {
+    bool ok = mega_feasible(e, &why);
+    if (ok) {
+        int per_sm = 0;
+        if (cudaFuncSetAttribute((const void*)mega_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)e->mk_smem) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mega_decode_kernel, MK_THREADS, e->mk_smem) != cudaSuccess ||
+            per_sm < 1) {
+            cudaGetLastError();
+            ok = false;
+            why = "one CTA does not fit an SM";
+        }
+    }
+    if (e->sh.size > 1) {
+        // every rank must take the same path: the persistent kernels of the ranks wait for one another
+        int* d_ok = nullptr;
+        int h_ok = ok ? 1 : 0;
+        MG_CUDA(e, cudaMalloc((void**)&d_ok, sizeof(int)));
+        MG_CUDA(e, cudaMemcpy(d_ok, &h_ok, sizeof(int), cudaMemcpyHostToDevice));
+        MG_NCCL(e, g_nccl.AllReduce(d_ok, d_ok, 1, ncclInt, ncclMin, e->comm, e->stream));
+        MG_CUDA(e, cudaStreamSynchronize(e->stream));
+        MG_CUDA(e, cudaMemcpy(&h_ok, d_ok, sizeof(int), cudaMemcpyDeviceToHost));
+        cudaFree(d_ok);
+        if (ok && !h_ok) why = "another rank cannot run it";
+        ok = h_ok != 0;
+    }
+    if (!ok) {
         e->err = "persistent kernel not used: " + why;
         return MG_OK;
     }
-    const mg_config& c = e->cfg;
+    int q_dim, vocab_base;
+    const mg_config c = mega_cfg(e, &q_dim, &vocab_base);
     const int G = e->num_sms, L = c.n_layers;
     const int ncol = L * 4 + 2;
     std::vector<unsigned long long> off((size_t)G * ncol);
     unsigned long long total = 0;
     auto phase_tiles = [&](int p, int cta) {
-        const PhaseShape s = phase_shape_of(p, c.dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
+        const PhaseShape s = phase_shape_of(p, c.dim, q_dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
         const int nrows = (item_begin(s.items, cta + 1, G) - item_begin(s.items, cta, G)) * s.rpi;
         const int rpt = 32 >> e->mk_geom[p].lpr_shift;
         return (nrows + rpt - 1) / rpt;
@@ -772,14 +821,17 @@ int build_mega(mg_engine* e) {
             if (!owned(l)) continue;
             int slots[3], nm = 0;
             phase_matrices(c, l, p, slots, &nm);
-            const PhaseShape s = phase_shape_of(p, c.dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
+            const PhaseShape s = phase_shape_of(p, c.dim, q_dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
             const int rq = row_q_bytes(s.fmt, s.K), rd = row_d_bytes(s.fmt, s.K);
             for (int m = 0; m < nm; m++) {
                 const DevMatrix& M = e->mats[slots[m]];
-                hq[m].resize((size_t)M.rows * rq);
-                MG_CUDA(e, cudaMemcpy(hq[m].data(), M.qs, hq[m].size(), cudaMemcpyDeviceToHost));
-                hd[m].resize(rd ? (size_t)M.rows * (s.K / 32) : 0);
-                if (rd) MG_CUDA(e, cudaMemcpy(hd[m].data(), M.ds, hd[m].size() * 2, cudaMemcpyDeviceToHost));
+                // lm_head is stored whole (it is also the embedding table): this rank streams rows [v0, v1)
+                const int row0 = p == PH_HEAD ? vocab_base : 0;
+                const int nr = p == PH_HEAD ? c.vocab : M.rows;
+                hq[m].resize((size_t)nr * rq);
+                MG_CUDA(e, cudaMemcpy(hq[m].data(), M.qs + (size_t)row0 * rq, hq[m].size(), cudaMemcpyDeviceToHost));
+                hd[m].resize(rd ? (size_t)nr * (s.K / 32) : 0);
+                if (rd) MG_CUDA(e, cudaMemcpy(hd[m].data(), M.ds + (size_t)row0 * (s.K / 32), hd[m].size() * 2, cudaMemcpyDeviceToHost));
             }
             const PhaseGeom g = e->mk_geom[p];
             const int lpr = 1 << g.lpr_shift, rpt = 32 >> g.lpr_shift;
@@ -794,7 +846,7 @@ int build_mega(mg_engine* e) {
                 std::vector<const unsigned short*> srcd(nrows);
                 for (int r = 0; r < nrows; r++) {
                     int mm[2], rr[2];
-                    item_rows(c, p, ib + r / s.rpi, mm, rr);
+                    item_rows(c, q_dim, p, ib + r / s.rpi, mm, rr);
                     const int k = r % s.rpi;
                     srcq[r] = hq[mm[k]].data() + (size_t)rr[k] * rq;
                     srcd[r] = rd ? hd[mm[k]].data() + (size_t)rr[k] * (s.K / 32) : nullptr;
@@ -831,39 +883,31 @@ int build_mega(mg_engine* e) {
         any_bias = any_bias || e->vecs[l * 12 + 4] || e->vecs[l * 12 + 5] || e->vecs[l * 12 + 6];
     }
     if (any_bias) {
-        const size_t bw = (size_t)c.dim + 2 * c.kv_dim;
+        const size_t bw = (size_t)q_dim + 2 * c.kv_dim;
         MG_CUDA(e, cudaMalloc((void**)&e->mk_bias, (size_t)L * bw * 4));
         MG_CUDA(e, cudaMemset(e->mk_bias, 0, (size_t)L * bw * 4));     // an unset bias adds zero
         for (int l = 0; l < L; l++) {
             if (!owned(l)) continue;
-            const size_t offs[3] = {0, (size_t)c.dim, (size_t)c.dim + c.kv_dim};
-            const size_t lens[3] = {(size_t)c.dim, (size_t)c.kv_dim, (size_t)c.kv_dim};
+            const size_t offs[3] = {0, (size_t)q_dim, (size_t)q_dim + c.kv_dim};
+            const size_t lens[3] = {(size_t)q_dim, (size_t)c.kv_dim, (size_t)c.kv_dim};
             for (int k = 0; k < 3; k++)
                 if (e->vecs[l * 12 + 4 + k])
                     MG_CUDA(e, cudaMemcpy(e->mk_bias + l * bw + offs[k], e->vecs[l * 12 + 4 + k], lens[k] * 4, cudaMemcpyDeviceToDevice));
         }
     }
-    const size_t nx = (size_t)3 * c.dim + 2 * c.kv_dim + c.dim + c.ffn_dim + 2;   // xh xhm xq | xkv | xattn | xmid | xtok
+    const size_t nx = (size_t)2 * c.dim + 2 * q_dim + 2 * c.kv_dim + c.ffn_dim + 2;   // xh xhm | xq | xkv | xattn | xmid | xtok
     MG_CUDA(e, cudaMalloc((void**)&e->xbuf, nx * sizeof(Tagged)));
     MG_CUDA(e, cudaMemset(e->xbuf, 0, nx * sizeof(Tagged)));
     MG_CUDA(e, cudaMalloc((void**)&e->mk_status, sizeof(MegaStatus)));
     MG_CUDA(e, cudaMemset(e->mk_status, 0, sizeof(MegaStatus)));
-    MG_CUDA(e, cudaFuncSetAttribute((const void*)mega_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)e->mk_smem));
-    int per_sm = 0;
-    MG_CUDA(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mega_decode_kernel, MK_THREADS, e->mk_smem));
-    if (per_sm < 1) {
-        free_mega(e);
-        e->err = "persistent kernel not used: one CTA does not fit an SM";
-        return MG_OK;
-    }
     e->mega_ok = true;
     return MG_OK;
 }
 
 // One launch of the persistent kernel: n_steps tokens through layers [ls, le).
 int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
-    const mg_config& c = e->cfg;
+    int q_dim, vocab_base;
+    const mg_config c = mega_cfg(e, &q_dim, &vocab_base);
     const int L = c.n_layers;
     MegaArgs a{};
     a.dim = c.dim; a.kv_dim = c.kv_dim; a.head_dim = c.head_dim; a.n_heads = c.n_heads; a.n_kv_heads = c.n_kv_heads;
@@ -881,8 +925,20 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
     a.embed_w = e->mats[L * 12 + 1].view();
     a.cos_tab = e->cos_tab; a.sin_tab = e->sin_tab; a.kc = e->kc; a.vc = e->vc;
     Tagged* x = e->xbuf;
-    a.xh = x; x += c.dim; a.xhm = x; x += c.dim; a.xq = x; x += c.dim; a.xkv = x; x += 2 * c.kv_dim;
-    a.xattn = x; x += c.dim; a.xmid = x; x += c.ffn_dim; a.xtok = x;
+    a.xh = x; x += c.dim; a.xhm = x; x += c.dim; a.xq = x; x += q_dim; a.xkv = x; x += 2 * c.kv_dim;
+    a.xattn = x; x += q_dim; a.xmid = x; x += c.ffn_dim; a.xtok = x;
+    a.q_dim = q_dim; a.tp_n = e->sh.size; a.tp_rank = e->sh.rank; a.vocab_base = vocab_base; a.vocab_total = e->cfg.vocab;
+    if (e->sh.size > 1) {
+        // the hidden-state exchanges go through the receive buffers every rank has mapped
+        a.xhm = reinterpret_cast<Tagged*>(xchg_row(e, e->xchg, 2, 0));
+        a.xh = reinterpret_cast<Tagged*>(xchg_row(e, e->xchg, 3, 0));
+        a.xbest = reinterpret_cast<Tagged*>(xchg_best(e, e->xchg));
+        for (int p = 0; p < e->sh.size; p++) {
+            a.xhm_peer[p] = reinterpret_cast<Tagged*>(xchg_row(e, e->xchg_peer[p], 2, 0));
+            a.xh_peer[p] = reinterpret_cast<Tagged*>(xchg_row(e, e->xchg_peer[p], 3, 0));
+            a.xbest_peer[p] = reinterpret_cast<Tagged*>(xchg_best(e, e->xchg_peer[p]));
+        }
+    }
     a.h_in = e->h; a.h_out = e->h; a.logits = e->logits; a.st = e->st; a.out_tokens = e->out_tokens;
     a.status = e->mk_status;
     a.trace = e->trace_next ? e->mk_trace : nullptr;
@@ -927,7 +983,12 @@ int check_range(mg_engine* e, int ls, int le, bool head, bool embed) {
 
 int run_step(mg_engine* e, int ls, int le, int mode, int head) {
     if (int rc = check_range(e, ls, le, head != HEAD_NONE && le >= e->cfg.n_layers, mode == MODE_EMBED)) return rc;
-    if (e->mega_ok && le > ls) return launch_mega(e, ls, le, mode, head, 1);
+    if (e->mega_ok && le > ls) {
+        if (int rc = launch_mega(e, ls, le, mode, head, 1)) return rc;
+        if (e->sh.size > 1 && head == HEAD_LOGITS && le >= e->cfg.n_layers)   // every rank gets every rank's slice
+            MG_NCCL(e, g_nccl.AllGather(e->logits, e->logits_all, (size_t)e->sh.v_stride, ncclFloat, e->comm, e->stream));
+        return MG_OK;
+    }
     if (!e->use_graph) {
         int rc = enqueue_step(e, e->stream, ls, le, mode, head);
         e->launches += e->capture_kernels;
@@ -1658,7 +1719,6 @@ int mg_tp_init(mg_engine* e, int rank, int size, const void* id, size_t bytes) {
         }
         if (!e->tp_fused) e->err = "tensor-parallel exchange through ncclAllReduce (peer mapping unavailable or MG_TP_NCCL=1)";
     }
-    e->use_mega = false;   // the persistent kernel is single-GPU
     e->use_pdl = false;    // launches alternate with library collectives; keep plain stream order
     e->built = false;
     return MG_OK;

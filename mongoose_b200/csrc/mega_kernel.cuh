@@ -106,6 +106,17 @@ struct MegaArgs {
     __half* vc;
     // exchange buffers
     Tagged *xh, *xhm, *xq, *xkv, *xattn, *xmid, *xtok;
+    // Tensor parallelism (tp_n > 1): dim is the model width, every other size above is this rank's
+    // share.  xh / xhm are then receive buffers [tp_n][dim] that every rank writes its partial sums
+    // into (peer stores), xbest [tp_n][2] receives the ranks' argmax keys.
+    int q_dim;              // rows of Q on this rank (= dim on one GPU)
+    int tp_n, tp_rank;
+    int vocab_base;         // global index of this rank's first lm_head row
+    int vocab_total;        // rows of the embedding table
+    Tagged* xh_peer[8];     // rank p's xh / xhm / xbest as mapped here (own entry = the local buffer)
+    Tagged* xhm_peer[8];
+    Tagged* xbest_peer[8];
+    Tagged* xbest;
     // io
     const float* h_in;
     float* h_out;
@@ -126,12 +137,12 @@ struct PhaseShape {
     int fmt;
 };
 
-__host__ __device__ inline PhaseShape phase_shape_of(int p, int dim, int kv_dim, int ffn, int vocab, int layer_fmt,
-                                                     int head_fmt) {
+__host__ __device__ inline PhaseShape phase_shape_of(int p, int dim, int q_dim, int kv_dim, int ffn, int vocab,
+                                                     int layer_fmt, int head_fmt) {
     PhaseShape s{};
     switch (p) {
-        case PH_QKV: s.items = (dim + 2 * kv_dim) / 2; s.rpi = 2; s.K = dim; s.fmt = layer_fmt; break;
-        case PH_WO: s.items = dim; s.rpi = 1; s.K = dim; s.fmt = layer_fmt; break;
+        case PH_QKV: s.items = (q_dim + 2 * kv_dim) / 2; s.rpi = 2; s.K = dim; s.fmt = layer_fmt; break;
+        case PH_WO: s.items = dim; s.rpi = 1; s.K = q_dim; s.fmt = layer_fmt; break;
         case PH_GU: s.items = ffn; s.rpi = 2; s.K = dim; s.fmt = layer_fmt; break;
         case PH_DOWN: s.items = dim; s.rpi = 1; s.K = ffn; s.fmt = layer_fmt; break;
         default: s.items = vocab; s.rpi = 1; s.K = dim; s.fmt = head_fmt; break;
@@ -242,6 +253,16 @@ __device__ __forceinline__ uint2 ld_poll8(const void* p) {
     unsigned long long a;
     asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
     return make_uint2((unsigned)a, (unsigned)(a >> 32));
+}
+// System-scope variants for words that another GPU writes or reads (tensor parallelism).
+__device__ __forceinline__ uint4 ld_poll16_sys(const void* p) {
+    unsigned long long a, b;
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+    return make_uint4((unsigned)a, (unsigned)(a >> 32), (unsigned)b, (unsigned)(b >> 32));
+}
+__device__ __forceinline__ void st_tagged_sys(Tagged* p, float v, unsigned int tag) {
+    const unsigned long long w = (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 __device__ __forceinline__ void st_tagged(Tagged* p, float v, unsigned int tag) {
     const unsigned long long w = (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
@@ -357,6 +378,33 @@ __device__ __forceinline__ float mk_poll1(MkCtx& c, const Tagged* p, unsigned in
         }
     }
     return __uint_as_float(r.x);
+}
+
+// Two adjacent values of a vector that arrives as one row per rank: the rows are added in rank
+// order (every rank forms the same bits).  p points into row 0, rows are `stride` words apart.
+__device__ __forceinline__ void mk_poll2_sum(MkCtx& c, const Tagged* p, int stride, int n, unsigned int tag, float& v0,
+                                             float& v1) {
+    v0 = 0.f; v1 = 0.f;
+    for (int r = 0; r < n; r++) {
+        const Tagged* q = p + (size_t)r * stride;
+        uint4 w = ld_poll16_sys(q);
+        if (w.y != tag || w.w != tag) {
+            if (!*c.abort_flag()) {
+                const long long t0 = global_ns();
+                for (unsigned int it = 1;; ++it) {
+                    w = ld_poll16_sys(q);
+                    if (w.y == tag && w.w == tag) break;
+                    if ((it & 63u) == 0u) {
+                        if (*c.abort_flag()) break;
+                        if (*(volatile int*)&c.status()->error) { *c.abort_flag() = 1; break; }
+                        if (global_ns() - t0 > MK_WAIT_CYCLES) { mk_fail(c, MK_ERR_POLL, (int)tag); break; }
+                    }
+                }
+            }
+        }
+        v0 += __uint_as_float(w.x);
+        v1 += __uint_as_float(w.z);
+    }
 }
 
 // ---------------------------------------------------------------------
@@ -527,12 +575,12 @@ __device__ __forceinline__ void mk_producer(MkCtx& c, const MegaArgs& a) {
     for (int step = 0; step < a.n_steps; step++) {
         for (int l = a.ls; l < a.le; l++)
             for (int p = 0; p < 4; p++) {
-                const PhaseShape s = phase_shape_of(p, a.dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
+                const PhaseShape s = phase_shape_of(p, a.dim, a.q_dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
                 const int nrows = c.phase_tab()[8 + p] * s.rpi;
                 mk_produce_phase(c, a, a.tape + off[l * 4 + p], p, nrows);
             }
         if (a.le >= a.n_layers && a.head) {
-            const PhaseShape s = phase_shape_of(PH_HEAD, a.dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
+            const PhaseShape s = phase_shape_of(PH_HEAD, a.dim, a.q_dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
             mk_produce_phase(c, a, a.tape + off[a.n_layers * 4], PH_HEAD, c.phase_tab()[8 + PH_HEAD]);
         }
     }
@@ -574,7 +622,7 @@ __device__ __forceinline__ void mk_epilogue(const MegaArgs& a, MkCtx& c, int p, 
                                             int row, bool has2, float v0, float v1, unsigned long long& best) {
     const int ib = c.phase_tab()[p];
     {   // self-check: every index an epilogue writes through must lie inside its vector
-        const int lim = p == PH_QKV ? (a.dim + 2 * a.kv_dim) / 2 : p == PH_GU ? a.ffn_dim : p == PH_HEAD ? a.vocab : a.dim;
+        const int lim = p == PH_QKV ? (a.q_dim + 2 * a.kv_dim) / 2 : p == PH_GU ? a.ffn_dim : p == PH_HEAD ? a.vocab : a.dim;
         const int idx = (p == PH_QKV || p == PH_GU) ? ib + (row >> 1) : ib + row + (has2 ? 1 : 0);
         if (row < 0 || idx >= lim) { mk_fail(c, MK_ERR_RANGE, 1000 * p + 100000 + row); return; }
     }
@@ -582,7 +630,7 @@ __device__ __forceinline__ void mk_epilogue(const MegaArgs& a, MkCtx& c, int p, 
         // same mapping as qkv_pair(), with the divisions by head_dim/2 done as shifts
         const int item = ib + (row >> 1);
         const int half = a.head_dim >> 1, hs1 = a.hd_shift - 1;
-        const int nq = a.dim >> 1, nk = a.kv_dim >> 1;
+        const int nq = a.q_dim >> 1, nk = a.kv_dim >> 1;
         int m = 0, i = item;
         if (i >= nq) { i -= nq; m = 1; }
         if (m == 1 && i >= nk) { i -= nk; m = 2; }
@@ -596,8 +644,8 @@ __device__ __forceinline__ void mk_epilogue(const MegaArgs& a, MkCtx& c, int p, 
             r1 = r0 + 1;
         }
         if (a.qkv_bias) {
-            const float* bias = a.qkv_bias + (size_t)layer * (a.dim + 2 * a.kv_dim) +
-                                (m == 0 ? 0 : m == 1 ? a.dim : a.dim + a.kv_dim);
+            const float* bias = a.qkv_bias + (size_t)layer * (a.q_dim + 2 * a.kv_dim) +
+                                (m == 0 ? 0 : m == 1 ? a.q_dim : a.q_dim + a.kv_dim);
             v0 += bias[r0];
             v1 += bias[r1];
         }
@@ -621,14 +669,27 @@ __device__ __forceinline__ void mk_epilogue(const MegaArgs& a, MkCtx& c, int p, 
     } else if (p == PH_HEAD) {
         const int r0 = ib + row;
         if (a.head == 2) { a.logits[r0] = v0; if (has2) a.logits[r0 + 1] = v1; }
-        unsigned long long key = pack_best(v0, (unsigned)r0);
+        unsigned long long key = pack_best(v0, (unsigned)(r0 + a.vocab_base));
         if (key > best) best = key;
-        if (has2) { key = pack_best(v1, (unsigned)(r0 + 1)); if (key > best) best = key; }
+        if (has2) { key = pack_best(v1, (unsigned)(r0 + 1 + a.vocab_base)); if (key > best) best = key; }
     } else {
-        Tagged* out = p == PH_WO ? a.xhm : a.xh;
         const int r0 = ib + row;
-        st_tagged(out + r0, c.hs()[r0] + v0, tag);
-        if (has2) st_tagged(out + r0 + 1, c.hs()[r0 + 1] + v1, tag);
+        if (a.tp_n == 1) {
+            Tagged* out = p == PH_WO ? a.xhm : a.xh;
+            st_tagged(out + r0, c.hs()[r0] + v0, tag);
+            if (has2) st_tagged(out + r0 + 1, c.hs()[r0 + 1] + v1, tag);
+        } else {
+            // partial sum over this rank's heads / FFN features: into row tp_rank of every rank's receive
+            // buffer; rank 0's row carries the residual
+            const float w0 = (a.tp_rank == 0 ? c.hs()[r0] : 0.f) + v0;
+            const float w1 = has2 ? (a.tp_rank == 0 ? c.hs()[r0 + 1] : 0.f) + v1 : 0.f;
+            Tagged* const* peers = p == PH_WO ? a.xhm_peer : a.xh_peer;
+            for (int q = 0; q < a.tp_n; q++) {
+                Tagged* out = peers[q] + (size_t)a.tp_rank * a.dim + r0;
+                st_tagged_sys(out, w0, tag);
+                if (has2) st_tagged_sys(out + 1, w1, tag);
+            }
+        }
     }
 }
 
@@ -695,7 +756,7 @@ __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int
                                          unsigned long long& best) {
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const PhaseGeom g = a.geom[p];
-    const int K = p == PH_DOWN ? a.ffn_dim : a.dim;
+    const int K = p == PH_DOWN ? a.ffn_dim : p == PH_WO ? a.q_dim : a.dim;
     const bool pairs = (p == PH_QKV || p == PH_GU);
     const int nrows = c.phase_tab()[8 + p] * (pairs ? 2 : 1);
     const int lpr = 1 << g.lpr_shift;
@@ -756,7 +817,8 @@ __device__ __forceinline__ float mk_stage_norm(const MegaArgs& a, MkCtx& c, int 
         if (ok) {
             nw = *reinterpret_cast<const float2*>(norm_w + i);   // issued before the poll
             if (src_kind == SRC_POLL) {
-                mk_poll2(c, xsrc + i, tag, v0, v1);
+                if (a.tp_n == 1) mk_poll2(c, xsrc + i, tag, v0, v1);
+                else mk_poll2_sum(c, xsrc + i, a.dim, a.tp_n, tag, v0, v1);
             } else if (src_kind == SRC_EMBED) {
                 v0 = embed_value(a.embed_w, a.head_fmt, a.dim, token, i);
                 v1 = embed_value(a.embed_w, a.head_fmt, a.dim, token, i + 1);
@@ -977,7 +1039,7 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
         // ---- token of this step (greedy feedback from the previous step) ----
         if (a.embed) {
             if (step > 0) token = (int)__float_as_uint(mk_poll1(c, a.xtok, ep - 8u + 1u));
-            token = min(max(token, 0), a.vocab - 1);
+            token = min(max(token, 0), a.vocab_total - 1);
         }
         // RoPE row of this position: staged once per step, published by the first stage barrier
         if (tid < 2 * half)
@@ -1012,8 +1074,8 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
                     mk_trace(a, step, l * 10 + 9);
                 }
                 const bool wo = p == PH_WO;
-                if (a.layer_fmt != FMT_F16) mk_gather_q(c, wo ? a.xattn : a.xmid, wo ? base + 2 : base + 4, wo ? a.dim : a.ffn_dim, a.layer_fmt == FMT_Q4_0);
-                else mk_gather(c, wo ? a.xattn : a.xmid, wo ? base + 2 : base + 4, c.xs(), wo ? a.dim : a.ffn_dim);
+                if (a.layer_fmt != FMT_F16) mk_gather_q(c, wo ? a.xattn : a.xmid, wo ? base + 2 : base + 4, wo ? a.q_dim : a.ffn_dim, a.layer_fmt == FMT_Q4_0);
+                else mk_gather(c, wo ? a.xattn : a.xmid, wo ? base + 2 : base + 4, c.xs(), wo ? a.q_dim : a.ffn_dim);
                 consumer_sync();
             }
             if (is_head && blockIdx.x == 0 && a.h_out && step == a.n_steps - 1)
@@ -1034,7 +1096,16 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
             // partial layer range: CTA 0 hands the hidden state back
             if (blockIdx.x == 0 && a.h_out && step == a.n_steps - 1 && a.le > a.ls) {
                 const unsigned int tag_final_h = ep + (unsigned)(a.le - 1) * MK_EPOCHS_PER_LAYER + 5;
-                mk_gather(c, a.xh, tag_final_h, c.hs(), a.dim);
+                if (a.tp_n == 1) {
+                    mk_gather(c, a.xh, tag_final_h, c.hs(), a.dim);
+                } else {
+                    for (int i = 2 * tid; i < a.dim; i += 2 * MK_CONSUMERS) {
+                        float u0, u1;
+                        mk_poll2_sum(c, a.xh + i, a.dim, a.tp_n, tag_final_h, u0, u1);
+                        c.hs()[i] = u0;
+                        c.hs()[i + 1] = u1;
+                    }
+                }
                 consumer_sync();
                 for (int i = tid; i < a.dim; i += MK_CONSUMERS) a.h_out[i] = c.hs()[i];
             }
@@ -1058,7 +1129,23 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
                 const unsigned int ticket = atomicAdd(&s->done, 1u);
                 if (ticket == gridDim.x - 1) {
                     __threadfence();
-                    const unsigned long long key = atomicMax(&s->best, 0ull);
+                    unsigned long long key = atomicMax(&s->best, 0ull);
+                    if (a.tp_n > 1) {
+                        // every rank publishes the key of its vocabulary slice to every rank; the largest
+                        // key (highest logit, lowest index) wins on all of them
+                        const unsigned int tagx = ep + (unsigned)(L * MK_EPOCHS_PER_LAYER) + 2u;
+                        for (int q = 0; q < a.tp_n; q++) {
+                            st_tagged_sys(a.xbest_peer[q] + 2 * a.tp_rank, __uint_as_float((unsigned)(key >> 32)), tagx);
+                            st_tagged_sys(a.xbest_peer[q] + 2 * a.tp_rank + 1, __uint_as_float((unsigned)key), tagx);
+                        }
+                        for (int r = 0; r < a.tp_n; r++) {
+                            float hi, lo;
+                            mk_poll2_sum(c, a.xbest + 2 * r, 0, 1, tagx, hi, lo);
+                            const unsigned long long k =
+                                ((unsigned long long)__float_as_uint(hi) << 32) | (unsigned long long)__float_as_uint(lo);
+                            key = k > key ? k : key;
+                        }
+                    }
                     const int tok = (int)(0xffffffffu - (unsigned int)(key & 0xffffffffull));
                     if (a.out_tokens && s->step < s->out_cap) a.out_tokens[s->step] = tok;
                     s->token = tok;
@@ -1089,7 +1176,7 @@ __global__ void __launch_bounds__(MK_THREADS, 1) mega_decode_kernel(const MegaAr
         }
         *c.abort_flag() = 0;
         for (int p = 0; p <= PH_HEAD; p++) {
-            const PhaseShape sh = phase_shape_of(p, a.dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
+            const PhaseShape sh = phase_shape_of(p, a.dim, a.q_dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
             const int ib = item_begin(sh.items, blockIdx.x, gridDim.x);
             c.phase_tab()[p] = ib;
             c.phase_tab()[8 + p] = item_begin(sh.items, blockIdx.x + 1, gridDim.x) - ib;

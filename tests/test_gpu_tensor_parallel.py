@@ -19,11 +19,12 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TOL = 1e-4   # relative to max|y|, the same bound as the single-GPU engine tests
 
 
-def run_ranks(world, cases, nccl_exchange=False):
+def run_ranks(world, cases, nccl_exchange=False, kernels_path=False):
     import torch
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs, {torch.cuda.device_count()} visible")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MG_TP_NCCL="1" if nccl_exchange else "0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MG_TP_NCCL="1" if nccl_exchange else "0",
+               MG_NO_MEGA="1" if kernels_path else "0")
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                           "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
                           os.path.join(ROOT, "tests", "tp_worker.py"), *cases],
@@ -36,9 +37,10 @@ def run_ranks(world, cases, nccl_exchange=False):
     return sorted(lines, key=lambda l: l["rank"])
 
 
-def check(lines, cases, n_new=24, nccl_exchange=False):
+def check(lines, cases, n_new=24, nccl_exchange=False, persistent=True):
     for name in cases:
         assert all(l["results"][name]["nccl_exchange"] == nccl_exchange for l in lines), "unexpected exchange path"
+        assert all(l["results"][name]["persistent"] == persistent for l in lines), "unexpected kernel path"
         toks = lines[0]["results"][name]["tokens"]
         for l in lines:
             r = l["results"][name]
@@ -49,15 +51,22 @@ def check(lines, cases, n_new=24, nccl_exchange=False):
 
 
 def test_two_ranks_match_the_oracle():
-    """Partial sums exchanged inside the kernels (peer stores into mapped receive buffers)."""
+    """The persistent kernel on every rank, partial sums and argmax keys exchanged inside it (peer
+    stores into mapped receive buffers)."""
     cases = ["tiny", "tiny-bias-ragged", "tiny-q4", "hd128-gqa", "tiny-kv1"]
     check(run_ranks(2, cases), cases)
+
+
+def test_two_ranks_on_the_phase_kernels_match_the_oracle():
+    """The graph of per-phase kernels with the exchange fused into their prologues / epilogues."""
+    cases = ["tiny", "tiny-bias-ragged", "tiny-q4", "hd128-gqa", "tiny-kv1"]
+    check(run_ranks(2, cases, kernels_path=True), cases, persistent=False)
 
 
 def test_two_ranks_with_nccl_exchange_match_the_oracle():
     """The same with ncclAllReduce between the kernels (MG_TP_NCCL=1)."""
     cases = ["tiny", "hd128-gqa"]
-    check(run_ranks(2, cases, nccl_exchange=True), cases, nccl_exchange=True)
+    check(run_ranks(2, cases, nccl_exchange=True), cases, nccl_exchange=True, persistent=False)
 
 
 def test_four_ranks_with_replicated_kv_heads_match_the_oracle():

@@ -48,6 +48,8 @@ def main():
         om = O.OracleModel(cfg)
         note = eng._lib.mg_last_error(eng._h).decode()      # says so when the exchange goes through NCCL
         fill_models(cfg, seed=3, jitter=0.1, engine=eng, oracle_model=om, raw_slots=True, bias=bias)
+        eng.BuildFusedDispatch()
+        persistent = "persistent kernel not used" not in eng._lib.mg_last_error(eng._h).decode()
         rng = np.random.default_rng(5)
         worst = 0.0
         logits = np.empty(cfg.vocab, np.float32)
@@ -82,7 +84,7 @@ def main():
         results[name] = {"logits_err": worst, "hidden_err": worst_hidden, "token_logits_err": tok_err,
                          "exact": exact, "ties": len(ties), "tokens": [int(x) for x in toks],
                          "launches": eng.LaunchCount(),
-                         "nccl_exchange": "ncclAllReduce" in note}
+                         "nccl_exchange": "ncclAllReduce" in note, "persistent": persistent}
         eng.close(); om.close()
         dist.barrier()
     # one writer: lines of several ranks on a shared pipe can interleave
