@@ -380,28 +380,36 @@ __device__ __forceinline__ float mk_poll1(MkCtx& c, const Tagged* p, unsigned in
     return __uint_as_float(r.x);
 }
 
+// Two adjacent exchange words that another GPU may have written, once both carry `tag` (raw
+// words: x, z = values, y, w = tags).  Bounded like every wait in this kernel.
+__device__ __forceinline__ uint4 mk_poll16_sys(MkCtx& c, const Tagged* q, unsigned int tag) {
+    uint4 w = ld_poll16_sys(q);
+    if (w.y != tag || w.w != tag) {
+        if (!*c.abort_flag()) {
+            const long long t0 = global_ns();
+            for (unsigned int it = 1;; ++it) {
+                w = ld_poll16_sys(q);
+                if (w.y == tag && w.w == tag) break;
+                if ((it & 63u) == 0u) {
+                    if (*c.abort_flag()) break;
+                    if (*(volatile int*)&c.status()->error) { *c.abort_flag() = 1; break; }
+                    if (global_ns() - t0 > MK_WAIT_CYCLES) { mk_fail(c, MK_ERR_POLL, (int)tag); break; }
+                }
+            }
+        }
+    }
+    return w;
+}
+
 // Two adjacent values of a vector that arrives as one row per rank: the rows are added in rank
 // order (every rank forms the same bits).  p points into row 0, rows are `stride` words apart.
 __device__ __forceinline__ void mk_poll2_sum(MkCtx& c, const Tagged* p, int stride, int n, unsigned int tag, float& v0,
                                              float& v1) {
-    v0 = 0.f; v1 = 0.f;
-    for (int r = 0; r < n; r++) {
-        const Tagged* q = p + (size_t)r * stride;
-        uint4 w = ld_poll16_sys(q);
-        if (w.y != tag || w.w != tag) {
-            if (!*c.abort_flag()) {
-                const long long t0 = global_ns();
-                for (unsigned int it = 1;; ++it) {
-                    w = ld_poll16_sys(q);
-                    if (w.y == tag && w.w == tag) break;
-                    if ((it & 63u) == 0u) {
-                        if (*c.abort_flag()) break;
-                        if (*(volatile int*)&c.status()->error) { *c.abort_flag() = 1; break; }
-                        if (global_ns() - t0 > MK_WAIT_CYCLES) { mk_fail(c, MK_ERR_POLL, (int)tag); break; }
-                    }
-                }
-            }
-        }
+    const uint4 first = mk_poll16_sys(c, p, tag);
+    v0 = __uint_as_float(first.x);
+    v1 = __uint_as_float(first.z);
+    for (int r = 1; r < n; r++) {
+        const uint4 w = mk_poll16_sys(c, p + (size_t)r * stride, tag);
         v0 += __uint_as_float(w.x);
         v1 += __uint_as_float(w.z);
     }
@@ -1139,10 +1147,9 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
                             st_tagged_sys(a.xbest_peer[q] + 2 * a.tp_rank + 1, __uint_as_float((unsigned)key), tagx);
                         }
                         for (int r = 0; r < a.tp_n; r++) {
-                            float hi, lo;
-                            mk_poll2_sum(c, a.xbest + 2 * r, 0, 1, tagx, hi, lo);
-                            const unsigned long long k =
-                                ((unsigned long long)__float_as_uint(hi) << 32) | (unsigned long long)__float_as_uint(lo);
+                            // raw words: the halves of a key are bit patterns, not numbers
+                            const uint4 w = mk_poll16_sys(c, a.xbest + 2 * r, tagx);
+                            const unsigned long long k = ((unsigned long long)w.x << 32) | (unsigned long long)w.z;
                             key = k > key ? k : key;
                         }
                     }

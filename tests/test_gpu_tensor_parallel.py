@@ -28,7 +28,7 @@ def run_ranks(world, cases, nccl_exchange=False, kernels_path=False):
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                           "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
                           os.path.join(ROOT, "tests", "tp_worker.py"), *cases],
-                         capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
+                         capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
     assert out.returncode == 0, (out.stdout[-1500:], out.stderr[-3000:])
     found = [l for l in out.stdout.splitlines() if l.startswith("TP_RESULTS ")]
     assert len(found) == 1, (out.stdout[-1500:], out.stderr[-3000:])

@@ -36,6 +36,12 @@ CASES = {
 }
 
 
+def progress(msg):
+    """Progress lines on stderr when TP_WORKER_VERBOSE=1 (which step a stuck run had reached)."""
+    if os.environ.get("TP_WORKER_VERBOSE") == "1":
+        print(f"[tp_worker rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
 def main():
     rank, world, local = multi.rank_env()
     dist.init_process_group("gloo")
@@ -48,7 +54,9 @@ def main():
         om = O.OracleModel(cfg)
         note = eng._lib.mg_last_error(eng._h).decode()      # says so when the exchange goes through NCCL
         fill_models(cfg, seed=3, jitter=0.1, engine=eng, oracle_model=om, raw_slots=True, bias=bias)
+        progress(f"{name}: weights set")
         eng.BuildFusedDispatch()
+        progress(f"{name}: built: {eng._lib.mg_last_error(eng._h).decode()!r}")
         persistent = "persistent kernel not used" not in eng._lib.mg_last_error(eng._h).decode()
         rng = np.random.default_rng(5)
         worst = 0.0
@@ -58,6 +66,7 @@ def main():
         for pos in range(5):
             h = rng.standard_normal(cfg.dim).astype(np.float32)
             eng.PartialStep(h, pos, 0, cfg.n_layers, None, logits)
+            progress(f"{name}: PartialStep pos {pos} done")
             _, want = om.step(h, pos, 0, cfg.n_layers)
             worst = max(worst, rel_err(logits, want))
         eng.ResetKV(); om.reset_kv()
@@ -65,6 +74,7 @@ def main():
         eng.PartialStep(h, 0, 0, 1, hid, None)
         want_h, _ = om.step(h, 0, 0, 1, want_logits=False)
         worst_hidden = rel_err(hid, want_h)
+        progress(f"{name}: layer-range step done, logits err {worst:.2e}, hidden err {worst_hidden:.2e}")
         # token input with logits
         eng.ResetKV(); om.reset_kv()
         tok_err = 0.0
@@ -75,11 +85,13 @@ def main():
             tok_err = max(tok_err, rel_err(logits, want))
             assert nxt == int(np.argmax(logits)), "argmax over ranks differs from the gathered logits"
             t = nxt
+        progress(f"{name}: StepToken loop done")
         # greedy generation
         eng.ResetKV()
         prompt = gen.prompt_ids(0, 6, cfg.vocab)
         n_new = 24
         toks = eng.Generate(prompt, n_new)
+        progress(f"{name}: Generate done")
         exact, ties, _ = greedy_parity(toks, om, prompt, n_new)
         results[name] = {"logits_err": worst, "hidden_err": worst_hidden, "token_logits_err": tok_err,
                          "exact": exact, "ties": len(ties), "tokens": [int(x) for x in toks],
