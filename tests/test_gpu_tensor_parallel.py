@@ -24,7 +24,7 @@ def run_ranks(world, cases, nccl_exchange=False, kernels_path=False):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs, {torch.cuda.device_count()} visible")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MG_TP_NCCL="1" if nccl_exchange else "0",
-               MG_NO_MEGA="1" if kernels_path else "0")
+               MG_TP_MEGA="0" if kernels_path else "1")
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                           "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
                           os.path.join(ROOT, "tests", "tp_worker.py"), *cases],
