@@ -702,9 +702,9 @@ bool mega_feasible(mg_engine* e, std::string* why) {
     const int G = e->num_sms;
     if (e->sh.size > 1 && !e->tp_fused) { *why = "tensor parallelism through NCCL uses the per-phase kernels"; return false; }
     if (e->sh.size > 1) {
-        // the persistent kernel across ranks is opt-in (MG_TP_MEGA=1); the per-phase kernels are the default there
+        // MG_TP_MEGA=0 keeps tensor-parallel ranks on the per-phase kernels
         const char* env = getenv("MG_TP_MEGA");
-        if (!(env && env[0] == '1')) { *why = "tensor parallelism defaults to the per-phase kernels (MG_TP_MEGA=1 selects it)"; return false; }
+        if (env && env[0] == '0') { *why = "MG_TP_MEGA=0: tensor parallelism on the per-phase kernels"; return false; }
     }
     if (e->sh.size > 1 && e->own_le - e->own_ls != c.n_layers) { *why = "layer ranges are not combined with tensor parallelism"; return false; }
     int coop = 0;
