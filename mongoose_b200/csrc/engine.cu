@@ -762,9 +762,9 @@ int build_mega(mg_engine* e) {
     bool ok = mega_feasible(e, &why);
     if (ok) {
         int per_sm = 0;
-        if (cudaFuncSetAttribute((const void*)mega_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)e->mk_smem) != cudaSuccess ||
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mega_decode_kernel, MK_THREADS, e->mk_smem) != cudaSuccess ||
+        const void* kern = e->sh.size > 1 ? (const void*)mega_decode_kernel<true> : (const void*)mega_decode_kernel<false>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->mk_smem) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MK_THREADS, e->mk_smem) != cudaSuccess ||
             per_sm < 1) {
             cudaGetLastError();
             ok = false;
@@ -949,7 +949,8 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
     a.trace = e->trace_next ? e->mk_trace : nullptr;
     e->trace_next = false;
     void* params[] = {&a};
-    MG_CUDA(e, cudaLaunchCooperativeKernel((const void*)mega_decode_kernel, dim3(e->num_sms), dim3(MK_THREADS), params,
+    const void* kern = e->sh.size > 1 ? (const void*)mega_decode_kernel<true> : (const void*)mega_decode_kernel<false>;
+    MG_CUDA(e, cudaLaunchCooperativeKernel(kern, dim3(e->num_sms), dim3(MK_THREADS), params,
                                            e->mk_smem, e->stream));
     e->launches += 1;
     return MG_OK;

@@ -626,6 +626,7 @@ __device__ __forceinline__ void mk_producer(MkCtx& c, const MegaArgs& a) {
 //   lm_head  : two consecutive vocab rows   -> logits (optional) + running argmax
 // xs holds the input vector (norm weights already folded in), `scale` is the RMSNorm factor.
 // ---------------------------------------------------------------------
+template <bool TP>
 __device__ __forceinline__ void mk_epilogue(const MegaArgs& a, MkCtx& c, int p, int layer, unsigned int tag,
                                             int row, bool has2, float v0, float v1, unsigned long long& best) {
     const int ib = c.phase_tab()[p];
@@ -682,7 +683,7 @@ __device__ __forceinline__ void mk_epilogue(const MegaArgs& a, MkCtx& c, int p, 
         if (has2) { key = pack_best(v1, (unsigned)(r0 + 1 + a.vocab_base)); if (key > best) best = key; }
     } else {
         const int r0 = ib + row;
-        if (a.tp_n == 1) {
+        if (!TP) {
             Tagged* out = p == PH_WO ? a.xhm : a.xh;
             st_tagged(out + r0, c.hs()[r0] + v0, tag);
             if (has2) st_tagged(out + r0 + 1, c.hs()[r0 + 1] + v1, tag);
@@ -759,7 +760,7 @@ __device__ __forceinline__ float tile_dot(MkCtx& c, const uint8_t* tile, int ni,
     return acc;
 }
 
-template <int FMT>
+template <int FMT, bool TP>
 __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int layer, unsigned int tag, float scale,
                                          unsigned long long& best) {
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -796,9 +797,9 @@ __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int
                 const int row = ((t + tl) << (5 - g.lpr_shift)) + rloc;       // row within this CTA's phase rows
                 if (pairs) {
                     const float v1 = __shfl_down_sync(MG_FULL_MASK, v, lpr);  // the partner row sits lpr lanes up
-                    if (part == 0 && (rloc & 1) == 0 && row < nrows) mk_epilogue(a, c, p, layer, tag, row, true, v, v1, best);
+                    if (part == 0 && (rloc & 1) == 0 && row < nrows) mk_epilogue<TP>(a, c, p, layer, tag, row, true, v, v1, best);
                 } else {
-                    if (part == 0 && row < nrows) mk_epilogue(a, c, p, layer, tag, row, false, v, 0.f, best);
+                    if (part == 0 && row < nrows) mk_epilogue<TP>(a, c, p, layer, tag, row, false, v, 0.f, best);
                 }
             }
             carry = tl - nt;
@@ -814,6 +815,7 @@ __device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int
 // values in hs (the residual), writes value * norm weight to xs and returns the RMSNorm factor
 // 1/sqrt(mean(h^2) + eps), which callers fold into the activation registers.  One barrier.
 enum : int { SRC_POLL = 0, SRC_EMBED = 1, SRC_PLAIN = 2 };
+template <bool TP>
 __device__ __forceinline__ float mk_stage_norm(const MegaArgs& a, MkCtx& c, int src_kind, const Tagged* xsrc,
                                                unsigned int tag, int token, const float* norm_w, bool quant, bool quant_sum) {
     float ss = 0.f;
@@ -825,7 +827,7 @@ __device__ __forceinline__ float mk_stage_norm(const MegaArgs& a, MkCtx& c, int 
         if (ok) {
             nw = *reinterpret_cast<const float2*>(norm_w + i);   // issued before the poll
             if (src_kind == SRC_POLL) {
-                if (a.tp_n == 1) mk_poll2(c, xsrc + i, tag, v0, v1);
+                if (!TP) mk_poll2(c, xsrc + i, tag, v0, v1);
                 else mk_poll2_sum(c, xsrc + i, a.dim, a.tp_n, tag, v0, v1);
             } else if (src_kind == SRC_EMBED) {
                 v0 = embed_value(a.embed_w, a.head_fmt, a.dim, token, i);
@@ -1031,6 +1033,7 @@ __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int la
 // Trace events per layer (mg_trace_step): 2p = input of phase p ready, 2p+1 = phase p done,
 // 8 = layer start, 9 = attention done (attention CTAs).
 // ---------------------------------------------------------------------
+template <bool TP>
 __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
     const int tid = threadIdx.x;
     const int L = a.n_layers;
@@ -1072,7 +1075,7 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
                 const float* nw = is_head ? a.final_norm : a.norms + (size_t)l * 2 * a.dim;
                 if (p == PH_GU) { src = a.xhm; tag = base + 3; nw += a.dim; }
                 else if (p == PH_QKV && l == a.ls) kind = a.embed ? SRC_EMBED : SRC_PLAIN;
-                scale = mk_stage_norm(a, c, kind, src, tag, token, nw, (is_head ? a.head_fmt : a.layer_fmt) != FMT_F16,
+                scale = mk_stage_norm<TP>(a, c, kind, src, tag, token, nw, (is_head ? a.head_fmt : a.layer_fmt) != FMT_F16,
                                       (is_head ? a.head_fmt : a.layer_fmt) == FMT_Q4_0);
             } else {
                 if (p == PH_WO && (int)blockIdx.x < a.n_heads) {
@@ -1093,9 +1096,9 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
             // ---- matvec + fused epilogue ----
             const unsigned int tag_out = base + (p == PH_QKV ? 1u : p == PH_WO ? 3u : p == PH_GU ? 4u : 5u);
             const int fmt = is_head ? a.head_fmt : a.layer_fmt;
-            if (fmt == FMT_Q8_0) mk_phase<FMT_Q8_0>(a, c, p, l, tag_out, scale, best);
-            else if (fmt == FMT_Q4_0) mk_phase<FMT_Q4_0>(a, c, p, l, tag_out, scale, best);
-            else mk_phase<FMT_F16>(a, c, p, l, tag_out, scale, best);
+            if (fmt == FMT_Q8_0) mk_phase<FMT_Q8_0, TP>(a, c, p, l, tag_out, scale, best);
+            else if (fmt == FMT_Q4_0) mk_phase<FMT_Q4_0, TP>(a, c, p, l, tag_out, scale, best);
+            else mk_phase<FMT_F16, TP>(a, c, p, l, tag_out, scale, best);
             consumer_sync();             // xs / hs / part are reused by the next phase
             mk_trace(a, step, l * 10 + 2 * (is_head ? 0 : p) + 1);
         }
@@ -1104,7 +1107,7 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
             // partial layer range: CTA 0 hands the hidden state back
             if (blockIdx.x == 0 && a.h_out && step == a.n_steps - 1 && a.le > a.ls) {
                 const unsigned int tag_final_h = ep + (unsigned)(a.le - 1) * MK_EPOCHS_PER_LAYER + 5;
-                if (a.tp_n == 1) {
+                if (!TP) {
                     mk_gather(c, a.xh, tag_final_h, c.hs(), a.dim);
                 } else {
                     for (int i = 2 * tid; i < a.dim; i += 2 * MK_CONSUMERS) {
@@ -1138,7 +1141,7 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
                 if (ticket == gridDim.x - 1) {
                     __threadfence();
                     unsigned long long key = atomicMax(&s->best, 0ull);
-                    if (a.tp_n > 1) {
+                    if (TP) {
                         // every rank publishes the key of its vocabulary slice to every rank; the largest
                         // key (highest logit, lowest index) wins on all of them
                         const unsigned int tagx = ep + (unsigned)(L * MK_EPOCHS_PER_LAYER) + 2u;
@@ -1174,6 +1177,8 @@ __host__ __device__ inline size_t mk_smem_bytes(int nslot, int slot_bytes, int x
            2 * MK_MAX_SLOTS * 8 + 16 + 144;
 }
 
+// TP = false: one GPU (no peer pointers are touched); TP = true: one rank of a tensor-parallel group.
+template <bool TP>
 __global__ void __launch_bounds__(MK_THREADS, 1) mega_decode_kernel(const MegaArgs a) {
     MkCtx c(a);
     if (threadIdx.x == 0) {
@@ -1193,7 +1198,7 @@ __global__ void __launch_bounds__(MK_THREADS, 1) mega_decode_kernel(const MegaAr
     }
     __syncthreads();
     if (threadIdx.x >= MK_CONSUMERS) mk_producer(c, a);
-    else mk_consumer(c, a);
+    else mk_consumer<TP>(c, a);
 }
 
 }  // namespace mg
