@@ -5,7 +5,7 @@
 
 Workload (default): Qwen2.5-0.5B architecture, random-init, Q8_0 (block 32, fp16 scales), fp16 KV,
 batch 1: a 32-token prompt fed one position at a time, then K greedy decode steps.  A "step" is one
-decode token.  Prints ONE JSON line (see README / DESIGN.md for the fields).
+decode token.  Prints ONE JSON line.
 
   value     tokens/s with everything resident in HBM: K greedy steps enqueued back to back
             (argmax fed back on the device), timed with CUDA events on the engine's stream.
