@@ -49,3 +49,21 @@ def test_engine_rejects_bad_config_without_gpu(mglib):
     assert mglib.mg_create(ctypes.byref(bad), ctypes.byref(h)) == -1 and not h.value
     assert mglib.mg_create(None, ctypes.byref(h)) == -1
     assert mglib.mg_last_error(None) == b"null engine"
+
+
+def test_plain_c_loader_resolves_every_symbol(mglib, tmp_path):
+    """dlopen + dlsym from C, as the reference's loader does (kernels.go:150-226); also proves the
+    public header compiles as C."""
+    import shutil
+    import subprocess
+    from mongoose_b200 import _lib
+    cc = shutil.which("gcc") or shutil.which("cc")
+    assert cc, "no C compiler"
+    exe = tmp_path / "abi_dlopen"
+    cuda_inc = "/usr/local/cuda/include"
+    subprocess.check_call([cc, "-std=c11", "-Wall", "-Werror", "-I", cuda_inc, "-o", str(exe),
+                           os.path.join(ROOT, "tests", "abi_dlopen.c"), "-ldl"])
+    out = subprocess.run([str(exe), _lib.LIB_PATH], capture_output=True, text=True, timeout=60)
+    assert out.returncode == 0, out.stderr
+    n = int(out.stdout.split()[0])
+    assert n == len(set(declared_symbols())), "abi_dlopen.c must list every symbol the header declares"
