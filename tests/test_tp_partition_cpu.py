@@ -115,3 +115,59 @@ def test_two_gloo_ranks_agree_on_the_partition_and_the_id(tmp_path):
     assert a["parts"] == b["parts"] and a["id"] == b["id"] and len(a["id"]) == 256
     assert a["parts"][0]["q_heads"] == [0, 14] and a["parts"][1]["q_heads"] == [14, 28]
     assert a["parts"][0]["kv_heads"] == [0, 2] and a["parts"][1]["ffn"] == [9472, 18944]
+
+
+# -- the split itself, restated with the CPU oracle ---------------------------------------------
+@pytest.mark.parametrize("fmt", [mc.FMT_Q8_0, mc.FMT_Q4_0], ids=["q8_0", "q4_0"])
+@pytest.mark.parametrize("size", [2, 4])
+def test_sharded_layer_equals_the_unsplit_layer_on_the_oracle(fmt, size):
+    """One transformer layer's matvecs computed shard by shard from slices of the UNSPLIT quantized
+    tensors (rows for q/k/v/gate/up, block-aligned columns for wo/down) and summed over ranks equal
+    the unsplit computation: the partition never cuts a quantization block and every Q head finds its
+    KV head on its rank."""
+    import numpy as np
+    from oracle import oracle as O
+    cfg = mc.TINY.with_(name="tp-oracle", dim=256, n_heads=8, n_kv_heads=2, head_dim=32, ffn_dim=352)
+    hd, dim, kvd, ffn = cfg.head_dim, cfg.dim, cfg.kv_dim, cfg.ffn_dim
+    rng = np.random.default_rng(11)
+    W = {n: (0.05 * rng.standard_normal(s)).astype(np.float32)
+         for n, s in (("q", (dim, dim)), ("k", (kvd, dim)), ("v", (kvd, dim)), ("o", (dim, dim)),
+                      ("g", (ffn, dim)), ("u", (ffn, dim)), ("d", (dim, ffn)))}
+    B = {n: O.quantize(fmt, w) for n, w in W.items()}
+    bb = {mc.FMT_Q8_0: 34, mc.FMT_Q4_0: 18}[fmt]
+
+    def cols(blocks, k0, k1):          # raw blocks of columns [k0, k1) of every row
+        assert k0 % 32 == 0 and k1 % 32 == 0
+        return np.ascontiguousarray(blocks[:, k0 // 32 * bb:k1 // 32 * bb])
+
+    x = rng.standard_normal(dim).astype(np.float32)
+    attn = rng.standard_normal(dim).astype(np.float32)          # stands in for the attention output
+    q_full = O.matvec(fmt, B["q"], x, dim, dim)
+    k_full = O.matvec(fmt, B["k"], x, kvd, dim)
+    o_full = O.matvec(fmt, B["o"], attn, dim, dim)
+    g_full = O.matvec(fmt, B["g"], x, ffn, dim)
+    u_full = O.matvec(fmt, B["u"], x, ffn, dim)
+    mid = O.silu_gate_mul(g_full, u_full)
+    d_full = O.matvec(fmt, B["d"], mid, dim, ffn)
+
+    q_parts, o_sum, d_sum = [], np.zeros(dim, np.float64), np.zeros(dim, np.float64)
+    group = cfg.n_heads // cfg.n_kv_heads
+    for r in range(size):
+        p = multi.tp_partition(cfg, r, size)
+        (q0, q1), (kv0, kv1), (f0, f1) = p["q_heads"], p["kv_heads"], p["ffn"]
+        # row splits reproduce the unsplit rows bit for bit
+        q_r = O.matvec(fmt, np.ascontiguousarray(B["q"][q0 * hd:q1 * hd]), x, (q1 - q0) * hd, dim)
+        k_r = O.matvec(fmt, np.ascontiguousarray(B["k"][kv0 * hd:kv1 * hd]), x, (kv1 - kv0) * hd, dim)
+        assert np.array_equal(q_r, q_full[q0 * hd:q1 * hd]) and np.array_equal(k_r, k_full[kv0 * hd:kv1 * hd])
+        assert all(kv0 <= h // group < kv1 for h in range(q0, q1))
+        q_parts.append(q_r)
+        # column splits give partial sums
+        o_sum += O.matvec(fmt, cols(B["o"], q0 * hd, q1 * hd), attn[q0 * hd:q1 * hd], dim, (q1 - q0) * hd)
+        g_r = O.matvec(fmt, np.ascontiguousarray(B["g"][f0:f1]), x, f1 - f0, dim)
+        u_r = O.matvec(fmt, np.ascontiguousarray(B["u"][f0:f1]), x, f1 - f0, dim)
+        mid_r = O.silu_gate_mul(g_r, u_r)
+        assert np.array_equal(mid_r, mid[f0:f1])
+        d_sum += O.matvec(fmt, cols(B["d"], f0, f1), mid_r, dim, f1 - f0)
+    assert np.array_equal(np.concatenate(q_parts), q_full)
+    for got, want in ((o_sum, o_full), (d_sum, d_full)):
+        assert np.abs(got - want).max() <= 2e-6 * np.abs(want).max()
