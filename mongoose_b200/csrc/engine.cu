@@ -122,7 +122,7 @@ struct mg_engine {
     // layer-range pipeline (mg_set_layer_range, mg_queue_hidden_to, L3 bridge)
     int own_ls = 0, own_le = 0;         // layers this engine holds weights for; [0, n_layers) by default
     cudaEvent_t sent_event = nullptr;   // recorded after this engine's hidden state has been copied to the next stage
-    mg_engine* mail_from = nullptr;     // stage whose hidden state was last queued to this engine
+    cudaEvent_t mail_event = nullptr;   // the sending stage's sent_event of the hidden state last queued to this engine
     unsigned int mail_queued = 0, mail_taken = 0;
     float* l3 = nullptr;                // pinned host copy of the hidden state (the reference's "L3 bridge")
     cudaStream_t copy_stream = nullptr;
@@ -1377,7 +1377,7 @@ int mg_queue_hidden_to(mg_engine* src, mg_engine* dst) {
     // the next stage's stream orders itself after the copy; its host thread may also ask with mg_wait_mailbox
     if ((rc = check_engine(dst))) return rc;
     MG_CUDA(dst, cudaStreamWaitEvent(dst->stream, src->sent_event, 0));
-    dst->mail_from = src;
+    dst->mail_event = src->sent_event;   // the event, not the engine: a destroyed sender yields an error, not a stale pointer
     dst->mail_queued++;
     return MG_OK;
 }
@@ -1390,8 +1390,8 @@ int mg_wait_mailbox(mg_engine* e, int timeout_ms) {
         return std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() >= timeout_ms;
     };
     for (;;) {
-        if (e->mail_queued != e->mail_taken && e->mail_from) {
-            const cudaError_t q = cudaEventQuery(e->mail_from->sent_event);
+        if (e->mail_queued != e->mail_taken && e->mail_event) {
+            const cudaError_t q = cudaEventQuery(e->mail_event);
             if (q == cudaSuccess) { e->mail_taken = e->mail_queued; return MG_OK; }
             if (q != cudaErrorNotReady) return fail(e, MG_ERR_CUDA, "mg_wait_mailbox: %s", cudaGetErrorString(q));
         }
