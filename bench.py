@@ -44,6 +44,9 @@ PROMPT_LEN = 32
 # DRAM bytes per decoded token (dram__bytes_read.sum + dram__bytes_write.sum of mega_decode_kernel from one
 # ncu capture of a 3-token launch, divided by 3; profiles/mega_decode_kernel_qwen05b_q8.md).
 NCU_TRAFFIC_PER_TOKEN = {"qwen2.5-0.5b-q8_0-b1": 592.4e6}
+# The one number the reference publishes for this metric: Qwen2.5-0.5B, batch 1, 200 tokens, "CUDA Q8
+# fused matvec" (per-row INT8 weights) on an RTX 5090: 234.0 tok/s (README.md:55-60 of the reference).
+PUBLISHED_TOK_S = {"qwen2.5-0.5b-q8_0-b1": 234.0}
 WORKLOADS = {
     "qwen2.5-0.5b-q8_0-b1": mc.QWEN25_05B,
     "qwen2.5-0.5b-q4_0-b1": mc.QWEN25_05B_Q4,
@@ -320,8 +323,12 @@ def run_b200_arm(args, cfg, rank, world, local_rank):
         line = {
             "metric": "decode_tokens_per_s", "value": tps, "unit": "tok/s", "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "strong" if tp else "weak",
-            "vs_baseline": None, "dtype": FMT_NAME[cfg.layer_fmt], "data": "synthetic",
+            "vs_baseline": (tps / PUBLISHED_TOK_S[args.workload] if args.workload in PUBLISHED_TOK_S else None),
+            "dtype": FMT_NAME[cfg.layer_fmt], "data": "synthetic",
             "config": {"workload": args.workload, "prompt_len": PROMPT_LEN, "batch": 1,
+                       "published_baseline": ("234.0 tok/s: the reference's README figure for this model and batch "
+                                              "on one RTX 5090 with per-row INT8 weights"
+                                              if args.workload in PUBLISHED_TOK_S else None),
                        "parallelism": (f"tensor parallel x{world} (partial sums exchanged " +
                                         ("by ncclAllReduce)" if os.environ.get("MG_TP_NCCL") == "1" else
                                          "inside the kernels over peer memory)") if tp else
