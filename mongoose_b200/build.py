@@ -29,7 +29,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-ffp-contract=off",
     "--expt-relaxed-constexpr",
     "-Xptxas", "-v",
-]
+] + (["-DMK_PROBE_P=" + os.environ["MK_PROBE_P"]] if os.environ.get("MK_PROBE_P") else [])
 
 
 def _nvcc() -> str:

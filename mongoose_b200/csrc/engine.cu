@@ -110,6 +110,7 @@ struct mg_engine {
     unsigned int epoch = 16;
     int mk_nslot = 0, mk_slot = MK_SLOT, mk_xs = 0, mk_sc = 0;
     int mk_prefetch = 0;                // L2 prefetch distance of the tape, bytes
+    long long mk_wait = MK_WAIT_CYCLES; // limit of every wait inside the persistent kernel, SM clocks
     PhaseGeom mk_geom[5] = {};
     size_t mk_smem = 0;
     size_t tape_bytes = 0;
@@ -712,38 +713,22 @@ bool mega_feasible(mg_engine* e, std::string* why) {
     if (!coop) { *why = "cooperative launch unsupported"; return false; }
     if (c.n_heads > G) { *why = "more query heads than SMs"; return false; }
     if (c.max_seq > 16384) { *why = "max_seq too large for the score buffer"; return false; }
-    // Ring slot: the default size, or, for matrices so wide that even a one-row tile exceeds it,
-    // the smallest multiple of 1 KiB that holds such a tile.
-    int slot = MK_SLOT;
-    for (int pass = 0; pass < 2; pass++) {
-        bool ok = true;
-        for (int p = 0; p <= PH_HEAD; p++) {
-            const PhaseShape s = phase_shape_of(p, c.dim, q_dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
-            int max_rows = 0;
-            for (int cta = 0; cta < G; cta++)
-                max_rows = std::max(max_rows, (item_begin(s.items, cta + 1, G) - item_begin(s.items, cta, G)) * s.rpi);
-            // MG_GEOM_SHIFT="q,w,g,d,h" pins log2(lanes per row) of the five phases (-1 = choose); tuning aid
-            int force = -1;
-            if (const char* gs = getenv("MG_GEOM_SHIFT")) {
-                int v[5] = {-1, -1, -1, -1, -1};
-                sscanf(gs, "%d,%d,%d,%d,%d", &v[0], &v[1], &v[2], &v[3], &v[4]);
-                force = v[p];
-            }
-            e->mk_geom[p] = choose_geom(s.fmt, s.K, max_rows, s.rpi == 2, MK_NW, slot, force);
-            if (e->mk_geom[p].ni == 0) {
-                ok = false;
-                const int lpr = s.rpi == 2 ? 16 : 32;
-                const int need = tile_bytes_of(s.fmt, (chunks_per_row(s.fmt, s.K) + lpr - 1) / lpr);
-                slot = std::max(slot, (need + 1023) & ~1023);
-            }
+    const int slot = MK_SLOT;
+    int xs_bytes = 3 * c.head_dim * 4;          // attention keeps q and the new k, v rows there
+    for (int p = 0; p <= PH_HEAD; p++) {
+        const PhaseShape s = phase_shape_of(p, c.dim, q_dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
+        // MG_GEOM="w:s,w:s,w:s,w:s,w:s" pins (wide, K-split) of the five phases (-1 = choose); tuning aid
+        int fw = -1, fs = -1;
+        if (const char* gs = getenv("MG_GEOM")) {
+            int v[10] = {-1, -1, -1, -1, -1, -1, -1, -1, -1, -1};
+            sscanf(gs, "%d:%d,%d:%d,%d:%d,%d:%d,%d:%d", &v[0], &v[1], &v[2], &v[3], &v[4], &v[5], &v[6], &v[7], &v[8], &v[9]);
+            fw = v[2 * p]; fs = v[2 * p + 1];
         }
-        if (ok) break;
-        if (pass == 1) { *why = "a weight tile does not fit a ring slot"; return false; }
+        e->mk_geom[p] = choose_geom(s.fmt, s.K, s.items, s.rpi, G, MK_NW, slot, p == PH_HEAD, fw, fs);
+        if (e->mk_geom[p].nkt == 0) { *why = "no tile layout for a phase"; return false; }
+        xs_bytes = std::max(xs_bytes, xs_bytes_of(s.fmt, s.K));
     }
-    int xs = c.dim > c.ffn_dim ? c.dim : c.ffn_dim;
-    if (xs < q_dim) xs = q_dim;
-    if (xs < 3 * c.head_dim) xs = 3 * c.head_dim;
-    xs = (xs + 3) & ~3;
+    const int xs = ((xs_bytes + 15) / 16) * 4;
     const int sc = (c.max_seq + 3) & ~3;
     int dev_max = 0;
     cudaDeviceGetAttribute(&dev_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, c.device);
@@ -794,14 +779,17 @@ int build_mega(mg_engine* e) {
     const int ncol = L * 4 + 2;
     std::vector<unsigned long long> off((size_t)G * ncol);
     unsigned long long total = 0;
-    auto phase_tiles = [&](int p, int cta) {
+    // row-groups of phase p on a CTA: [first, first + count)
+    auto phase_units = [&](int p, int cta, int* first) {
         const PhaseShape s = phase_shape_of(p, c.dim, q_dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
-        const int nrows = (item_begin(s.items, cta + 1, G) - item_begin(s.items, cta, G)) * s.rpi;
-        const int rpt = 32 >> e->mk_geom[p].lpr_shift;
-        return (nrows + rpt - 1) / rpt;
+        const int sh = e->mk_geom[p].ipg_shift;
+        const int units = (s.items + (1 << sh) - 1) >> sh;
+        const int ub = unit_begin(units, cta, G);
+        if (first) *first = ub;
+        return unit_begin(units, cta + 1, G) - ub;
     };
     auto phase_bytes = [&](int p, int cta) {
-        return (unsigned long long)phase_tiles(p, cta) * e->mk_geom[p].tile_bytes;
+        return (unsigned long long)phase_units(p, cta, nullptr) * e->mk_geom[p].nkt * e->mk_geom[p].tile_bytes;
     };
     // a pipeline stage streams only the layers it owns (and lm_head only with the last layer)
     auto owned = [&](int l) { return l < L ? (l >= e->own_ls && l < e->own_le) : e->own_le >= L; };
@@ -839,34 +827,67 @@ int build_mega(mg_engine* e) {
                 if (rd) MG_CUDA(e, cudaMemcpy(hd[m].data(), M.ds + (size_t)row0 * (s.K / 32), hd[m].size() * 2, cudaMemcpyDeviceToHost));
             }
             const PhaseGeom g = e->mk_geom[p];
-            const int lpr = 1 << g.lpr_shift, rpt = 32 >> g.lpr_shift;
+            const int ipg = 1 << g.ipg_shift;
             const int col = l < L ? l * 4 + p : L * 4;
             for (int cta = 0; cta < G; cta++) {
-                const int ib = item_begin(s.items, cta, G), ie = item_begin(s.items, cta + 1, G);
-                const int nrows = (ie - ib) * s.rpi;
-                const int ntiles = (nrows + rpt - 1) / rpt;
+                int ub = 0;
+                const int nrg = phase_units(p, cta, &ub);
                 uint8_t* dst = tape.data() + off[(size_t)cta * ncol + col];
-                // source row of every tape row of this CTA
-                std::vector<const uint8_t*> srcq(nrows);
-                std::vector<const unsigned short*> srcd(nrows);
-                for (int r = 0; r < nrows; r++) {
-                    int mm[2], rr[2];
-                    item_rows(c, q_dim, p, ib + r / s.rpi, mm, rr);
-                    const int k = r % s.rpi;
-                    srcq[r] = hq[mm[k]].data() + (size_t)rr[k] * rq;
-                    srcd[r] = rd ? hd[mm[k]].data() + (size_t)rr[k] * (s.K / 32) : nullptr;
-                }
-                for (int t = 0; t < ntiles; t++) {
-                    uint8_t* tile = dst + (size_t)t * g.tile_bytes;            // zero-initialised
-                    unsigned short* tds = reinterpret_cast<unsigned short*>(tile + (size_t)g.ni * 512);
-                    for (int i = 0; i < g.ni; i++)
-                        for (int lane = 0; lane < 32; lane++) {
-                            const int row = t * rpt + (lane >> g.lpr_shift);
-                            const int ch = (lane & (lpr - 1)) + i * lpr;
-                            if (row >= nrows || ch >= g.nchunks) continue;
-                            memcpy(tile + (size_t)(i * 32 + lane) * 16, srcq[row] + (size_t)ch * 16, 16);
-                            if (rd) tds[i * 32 + lane] = srcd[row][s.fmt == FMT_Q8_0 ? (ch >> 1) : ch];
-                        }
+                // tiles in the order the warps take them: pass, round, row-group of the pass, K-split
+                for (int rb = 0; rb * g.RS < nrg; rb++) {
+                    const int nrs = std::min(g.RS, nrg - rb * g.RS);
+                    for (int k0 = 0; k0 < g.nkt; k0 += g.S) {
+                        const int nkp = std::min(g.S, g.nkt - k0);
+                        for (int rs = 0; rs < nrs; rs++)
+                            for (int kp = 0; kp < nkp; kp++, dst += g.tile_bytes) {
+                                const int rgi = ub + rb * g.RS + rs, kt = k0 + kp;
+                                // source row and block of every row-slot (nullptr: the slot is empty)
+                                const uint8_t* sq[16];
+                                const unsigned short* sd[16];
+                                for (int sl = 0; sl < 16; sl++) {
+                                    int j, which, kpar;
+                                    slot_item(g.wide, s.rpi, sl, &j, &which, &kpar);
+                                    const int item = rgi * ipg + j;
+                                    const int kb = g.wide ? 2 * kt + kpar : kt;
+                                    sq[sl] = nullptr; sd[sl] = nullptr;
+                                    if (item >= s.items || kb >= g.kblocks) continue;
+                                    int mm[2], rr[2];
+                                    item_rows(c, q_dim, p, item, mm, rr);
+                                    const uint8_t* rowq = hq[mm[which]].data() + (size_t)rr[which] * rq;
+                                    sq[sl] = rowq + (size_t)kb * (s.fmt == FMT_Q8_0 ? 32 : s.fmt == FMT_Q4_0 ? 16 : 32);
+                                    if (rd) sd[sl] = hd[mm[which]].data() + (size_t)rr[which] * (s.K / 32) + kb;
+                                }
+                                for (int lane = 0; lane < 32; lane++) {
+                                    const int gq = lane >> 2, t = lane & 3;
+                                    if (s.fmt == FMT_Q8_0) {
+                                        // A registers a0..a3 = (slot g, cols 4t..), (slot g+8, cols 4t..), (slot g, cols 16+4t..), (slot g+8, 16+4t..)
+                                        for (int i = 0; i < 4; i++) {
+                                            const uint8_t* src = sq[gq + 8 * (i & 1)];
+                                            if (src) memcpy(dst + lane * 16 + i * 4, src + 16 * (i >> 1) + 4 * t, 4);
+                                        }
+                                    } else if (s.fmt == FMT_Q4_0) {
+                                        // nibble bytes 4t..4t+3 of slots g and g+8
+                                        for (int i = 0; i < 2; i++) {
+                                            const uint8_t* src = sq[gq + 8 * i];
+                                            if (src) memcpy(dst + lane * 8 + i * 4, src + 4 * t, 4);
+                                        }
+                                    } else {
+                                        // halves 4t..4t+3 of slots g and g+8
+                                        for (int i = 0; i < 2; i++) {
+                                            const uint8_t* src = sq[gq + 8 * i];
+                                            if (src) memcpy(dst + lane * 16 + i * 8, src + 8 * t, 8);
+                                        }
+                                    }
+                                }
+                                if (rd) {
+                                    unsigned short* tds = reinterpret_cast<unsigned short*>(dst + (s.fmt == FMT_Q8_0 ? 512 : 256));
+                                    for (int gq = 0; gq < 8; gq++) {
+                                        if (sd[gq]) tds[2 * gq] = *sd[gq];
+                                        if (sd[gq + 8]) tds[2 * gq + 1] = *sd[gq + 8];
+                                    }
+                                }
+                            }
+                    }
                 }
             }
         }
@@ -917,13 +938,14 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
     MegaArgs a{};
     a.dim = c.dim; a.kv_dim = c.kv_dim; a.head_dim = c.head_dim; a.n_heads = c.n_heads; a.n_kv_heads = c.n_kv_heads;
     a.ffn_dim = c.ffn_dim; a.vocab = c.vocab; a.n_layers = L; a.max_seq = c.max_seq;
-    a.layer_fmt = c.layer_fmt; a.head_fmt = c.head_fmt; a.eps = c.rms_eps;
+    a.layer_fmt = c.layer_fmt; a.head_fmt = c.head_fmt; a.eps = c.rms_eps; a.inv_dim = 1.0f / (float)c.dim;
     a.ls = ls; a.le = le; a.head = (le >= L) ? head : 0; a.embed = (mode == MODE_EMBED); a.n_steps = n_steps;
     a.epoch = e->epoch;
     e->epoch += (unsigned)n_steps * (unsigned)(L * MK_EPOCHS_PER_LAYER + 8);
     a.hd_shift = c.head_dim == 32 ? 5 : c.head_dim == 64 ? 6 : 7;
     for (int p = 0; p < 5; p++) a.geom[p] = e->mk_geom[p];
     a.nslot = e->mk_nslot; a.slot_bytes = e->mk_slot; a.prefetch_bytes = e->mk_prefetch; a.xs_floats = e->mk_xs; a.sc_floats = e->mk_sc;
+    a.wait_cycles = e->mk_wait;
     a.tape = e->tape; a.tape_off = e->tape_off; a.tape_bytes = e->tape_bytes;
     a.norms = e->mk_norms; a.qkv_bias = e->mk_bias;
     a.final_norm = e->vecs[L * 12];

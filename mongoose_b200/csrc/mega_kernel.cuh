@@ -8,30 +8,38 @@
 //
 //  * Weight tape.  At build time every CTA's share of every matrix is copied
 //    into one contiguous per-CTA byte stream in exactly the order the CTA
-//    consumes it: tiles of 32 >> s rows in which 1 << s adjacent lanes share a
-//    row, stored as [iteration][lane] 16-byte chunks followed by the fp16 block
-//    scales in the same order, so a warp reads 512 contiguous, conflict-free
-//    bytes per iteration.  A dedicated producer warp walks the tape with bulk
-//    asynchronous copies (cp.async.bulk, mbarrier completion) into a ring of
-//    shared-memory slots, running up to a ring ahead of the consumers - weights
-//    never depend on activations, so HBM streaming is off the dependency chain.
+//    consumes it.  The unit is a TILE: 16 row-slots x one block of 32 input
+//    columns ("tall"), or 8 rows x two consecutive blocks ("wide", for phases
+//    that have only a handful of rows per CTA), stored in the register order of
+//    the m16n8k32 integer MMA's A operand (one 16-byte shared-memory load per
+//    lane) followed by the tile's 16 fp16 block scales.  A dedicated producer
+//    warp walks the tape with bulk asynchronous copies (cp.async.bulk, mbarrier
+//    completion) into a ring of shared-memory slots, running up to a ring ahead
+//    of the consumers - weights never depend on activations, so HBM streaming
+//    is off the dependency chain.
 //  * Tagged exchange.  A phase's output vector is written to global memory as
 //    8-byte {fp32 value, 32-bit epoch} words.  Consumers poll the words they
 //    need until the epoch is the one they expect: data and flag arrive in one
 //    atomic 8-byte access, so no fence, no counter and no reset is needed, and
 //    a stale buffer can never be mistaken for fresh data.
-//  * 15 consumer warps per CTA.  The input vector is staged in shared memory
-//    (for int8/4-bit weights as 24-bit fixed point in three byte planes, so
-//    the dot products are integer dp4a); every lane accumulates its share of
-//    one row, lanes of a row combine with log2(lanes per row) shuffles, and all
-//    rows of a tile run their fused epilogue in parallel lanes.  The lanes-per-
-//    row split is chosen per phase on the host so that even a phase with eight
-//    rows per CTA spreads over several warps.
+//  * 15 consumer warps per CTA, all of them busy in every phase.  The input
+//    vector is staged in shared memory as 24-bit fixed point in three signed
+//    byte planes with one scale per block of 32; the planes are three columns
+//    of the MMA's B operand, so ONE mma.sync multiplies a 512-byte weight tile
+//    with the whole 24-bit activation block, exactly, in int32.  Per tile a
+//    lane then does two int->float conversions and two FMAs with
+//    (block scale x activation scale).  A phase's tiles are dealt to the warps
+//    as (row-group, K-split) pairs chosen per phase on the host, so that a
+//    phase with eight rows per CTA still gives every warp one tile; the K-split
+//    partial sums meet in shared memory and one thread per output row runs the
+//    fused epilogue (bias + RoPE + fp16 rounding, residual add, SiLU * up,
+//    argmax).  fp16 weights use the same tiles with fp32 FMAs.
 //
-// Every wait (mbarrier, exchange poll) is bounded by a deadline in SM clocks (about 1 s);
-// on expiry the kernel records an error code, stops waiting everywhere and
-// runs to completion on whatever data it has, so a logic error cannot hang
-// the GPU.  The host checks the status word after each launch.
+// Every wait (mbarrier, exchange poll) is bounded by a deadline in SM clocks
+// (MegaArgs::wait_cycles, about 1 s by default); on expiry the kernel records
+// an error code, stops waiting everywhere and runs to completion on whatever
+// data it has, so a logic error cannot hang the GPU.  The host checks the
+// status word after each launch.
 #pragma once
 
 #include "decode_kernels.cuh"
@@ -41,11 +49,11 @@ namespace mg {
 constexpr int MK_NW = 15;                       // consumer warps
 constexpr int MK_CONSUMERS = MK_NW * 32;        // 480
 constexpr int MK_THREADS = MK_CONSUMERS + 32;   // + producer warp = 512 threads, 128 registers each
-constexpr int MK_SLOT = 16384;                  // default ring slot bytes (MegaArgs::slot_bytes holds the size in use)
+constexpr int MK_SLOT = 16384;                  // ring slot bytes
 constexpr int MK_MAX_SLOTS = 14;
 constexpr int MK_PART_FLOATS = 2048;
 constexpr int MK_EPOCHS_PER_LAYER = 8;
-constexpr long long MK_WAIT_CYCLES = 2000000000ll;         // per wait: about one second of SM clocks
+constexpr long long MK_WAIT_CYCLES = 2000000000ll;         // default per-wait limit: about one second of SM clocks
 
 enum : int { PH_QKV = 0, PH_WO = 1, PH_GU = 2, PH_DOWN = 3, PH_HEAD = 4 };
 enum : int { MK_OK = 0, MK_ERR_POLL = 1, MK_ERR_FULL = 2, MK_ERR_EMPTY = 3, MK_ERR_RANGE = 4 };
@@ -62,22 +70,33 @@ struct Tagged {         // one exchanged activation
     unsigned int tag;
 };
 
-// How a phase's rows are laid over lanes (the same on every CTA).  A warp works on a TILE of
-// 32 >> lpr_shift rows; a row is shared by 1 << lpr_shift adjacent lanes, lane `part` of a row taking
-// the 16-byte chunks part, part + lpr, part + 2 lpr, ...  The tape stores a tile exactly in the order
-// the lanes read it: ni iterations x 32 lanes x 16 bytes, then ni x 32 fp16 block scales.
+// How a phase's rows are laid over the warps (the same on every CTA).
+//   A ROW-GROUP is the set of weight rows one tile column covers: 16 row-slots ("tall") or 8
+//   ("wide").  Phases whose work items are row PAIRS (the two rows of a RoPE pair, gate row j and up
+//   row j) put the first rows of `ipg` items in the lower half of the slots and the second rows in
+//   the upper half.  A tile is one row-group x one k-tile: one block of 32 columns (tall) or two
+//   consecutive blocks (wide; MMA rows 8..15 then hold the same 8 rows for the odd block).
+//   S warps share a row-group and split its k-tiles (warp kp takes k-tiles kp, kp + S, ...);
+//   RS row-groups are in flight at a time, RS * S <= MK_NW.  The tape stores the tiles in the order
+//   the warps take them: pass (RS row-groups), round (S k-tiles), row-group, k-split.
 struct PhaseGeom {
-    int lpr_shift;      // log2(lanes per row)
-    int ni;             // chunks per lane = ceil(chunks per row / lanes per row)
+    int wide;
+    int S;
+    int RS;
+    int nkt;            // k-tiles per row-group
+    int ipg_shift;      // log2(work items per row-group)
     int tile_bytes;
     int tpe;            // tiles per ring entry
-    int nchunks;        // 16-byte chunks per weight row
+    int kblocks;        // blocks of 32 (fp16 weights: 16) input columns per row
+    int K;              // input width
+    int nfull;          // nkt / S: rounds in which every K-split has a tile
 };
 
 struct MegaArgs {
     int dim, kv_dim, head_dim, n_heads, n_kv_heads, ffn_dim, vocab, n_layers, max_seq;
     int layer_fmt, head_fmt;
     float eps;
+    float inv_dim;          // 1 / dim
     int ls, le;             // layer range
     int head;               // HEAD_NONE / HEAD_ARGMAX / HEAD_LOGITS (0/1/2)
     int embed;              // 1: hidden state from the embedding row of st->token, 0: from h_in
@@ -85,9 +104,10 @@ struct MegaArgs {
     unsigned int epoch;     // first epoch of this launch
     int hd_shift;           // log2(head_dim)
     int nslot;
-    int slot_bytes;       // ring slot size: MK_SLOT, or larger when one tile of the widest matrix needs it
-    int prefetch_bytes;   // how far ahead of the ring the producer asks L2 for this CTA's tape (0 = off)
+    int slot_bytes;         // ring slot size
+    int prefetch_bytes;     // how far ahead of the ring the producer asks L2 for this CTA's tape (0 = off)
     int xs_floats;          // size of the staged-activation buffer (multiple of 4)
+    long long wait_cycles;  // limit of every wait inside the kernel, in SM clocks
     PhaseGeom geom[5];
     int sc_floats;          // attention score buffer: max_seq rounded up to a multiple of 4
     // weight tape
@@ -124,11 +144,12 @@ struct MegaArgs {
     StepState* st;
     int* out_tokens;
     MegaStatus* status;
-    long long* trace;       // optional [grid][n_layers*10 + 2] SM-clock stamps of CTA thread 0 (first step)
+    long long* trace;       // optional [grid][(n_layers + 1) * MK_EV] SM-clock stamps of CTA thread 0 (first step)
+    int trace_step;         // always 0: the step whose stamps are kept
 };
 
 // ---------------------------------------------------------------------
-// Row partition shared by the host tape builder and the kernel.
+// Work partition shared by the host tape builder and the kernel.
 // ---------------------------------------------------------------------
 struct PhaseShape {
     int items;      // work items over the whole grid
@@ -150,37 +171,61 @@ __host__ __device__ inline PhaseShape phase_shape_of(int p, int dim, int q_dim, 
     return s;
 }
 
-__host__ __device__ inline int item_begin(int items, int cta, int grid) {
-    return (int)(((long long)cta * items) / grid);
+// Row-groups are dealt to the CTAs in contiguous, balanced runs (a CTA may get none).
+__host__ __device__ inline int unit_begin(int units, int cta, int grid) {
+    return (int)(((long long)cta * units) / grid);
 }
 __host__ __device__ inline int row_q_bytes(int fmt, int K) { return plane_row_bytes(fmt, K); }
 __host__ __device__ inline int row_d_bytes(int fmt, int K) { return fmt == FMT_F16 ? 0 : (K / 32) * 2; }
-__host__ __device__ inline int chunks_per_row(int fmt, int K) {
-    return fmt == FMT_Q8_0 ? K / 16 : fmt == FMT_Q4_0 ? K / 32 : K / 8;
+__host__ __device__ inline int tile_bytes_of(int fmt) { return fmt == FMT_Q8_0 ? 544 : fmt == FMT_Q4_0 ? 288 : 512; }
+__host__ __device__ inline int kblock_of(int fmt) { return fmt == FMT_F16 ? 16 : 32; }
+
+// Row-slot s (0..15) of a row-group -> which item of the group (j), which of its rows, and, for
+// wide tiles, which of the tile's two blocks.
+__host__ __device__ inline void slot_item(int wide, int rpi, int s, int* j, int* which, int* kpar) {
+    if (!wide) {
+        *kpar = 0;
+        if (rpi == 2) { *j = s & 7; *which = s >> 3; } else { *j = s; *which = 0; }
+    } else {
+        *kpar = s >> 3;
+        s &= 7;
+        if (rpi == 2) { *j = s & 3; *which = s >> 2; } else { *j = s; *which = 0; }
+    }
 }
-__host__ __device__ inline int tile_bytes_of(int fmt, int ni) { return ni * 32 * (fmt == FMT_F16 ? 16 : 18); }
-// Lanes per row for a phase whose busiest CTA has max_rows rows: the choice that minimises the
-// chunks a warp walks through (tiles per warp x chunks per lane) among those whose tile fits a ring
-// slot; row pairs must stay inside a tile, so pair phases use at most 16 lanes per row.
-__host__ inline PhaseGeom choose_geom(int fmt, int K, int max_rows, bool pairs, int n_warps, int slot_bytes,
-                                      int force_shift = -1) {
+
+// Layout of a phase: tall or wide tiles and the K-split that minimise the tiles the busiest warp
+// walks through (plus a charge per pass and for the shared-memory reduction of a K-split).
+__host__ inline PhaseGeom choose_geom(int fmt, int K, int items, int rpi, int grid, int n_warps, int slot_bytes,
+                                      bool head, int force_wide = -1, int force_s = -1) {
     PhaseGeom best{};
     long long best_cost = -1;
-    const int nch = chunks_per_row(fmt, K);
-    for (int sh = 0; sh <= (pairs ? 4 : 5); sh++) {
-        if (force_shift >= 0 && sh != force_shift) continue;
-        const int lpr = 1 << sh, rpt = 32 >> sh;
-        const int ni = (nch + lpr - 1) / lpr;
-        const int tb = tile_bytes_of(fmt, ni);
-        if (tb > slot_bytes) continue;
-        const int tiles = (max_rows + rpt - 1) / rpt;
-        const long long cost = (long long)((tiles + n_warps - 1) / n_warps) * (ni + 6);   // + per-tile overhead
-        if (best_cost < 0 || cost < best_cost) {
-            best_cost = cost;
-            best.lpr_shift = sh; best.ni = ni; best.tile_bytes = tb; best.tpe = slot_bytes / tb; best.nchunks = nch;
+    const int kblk = kblock_of(fmt), nkb = K / kblk;
+    for (int wide = 0; wide <= 1; wide++) {
+        if (force_wide >= 0 && wide != force_wide) continue;
+        const int ipg = (wide ? 8 : 16) / rpi;
+        const int units = (items + ipg - 1) / ipg;
+        const int max_units = (units + grid - 1) / grid;
+        const int nkt = wide ? (nkb + 1) / 2 : nkb;
+        for (int S = 1; S <= n_warps; S++) {
+            if (force_s >= 0 && S != force_s) continue;
+            if (head && S != 1) continue;                  // lm_head: many rows, epilogue inside the warp
+            const int RS = n_warps / S;
+            if (!head && max_units * 16 > n_warps * 32) continue;       // one epilogue thread per row-slot
+            const int passes = (max_units + RS - 1) / RS;
+            if (max_units * 16 * (S == 1 ? 1 : ((S + 3) & ~3)) > MK_PART_FLOATS) continue;     // room for the partial sums
+            const long long cost = (long long)passes * ((nkt + S - 1) / S) + passes + (S > 1 ? 3 : 0);
+            if (best_cost < 0 || cost < best_cost) {
+                best_cost = cost;
+                best.wide = wide; best.S = S; best.RS = RS; best.nkt = nkt;
+                best.ipg_shift = ipg == 16 ? 4 : ipg == 8 ? 3 : 2;
+                best.tile_bytes = tile_bytes_of(fmt);
+                best.tpe = slot_bytes / best.tile_bytes;
+                best.kblocks = nkb;
+                best.K = K; best.nfull = nkt / S;
+            }
         }
     }
-    if (best_cost < 0) best.ni = 0;     // no feasible layout
+    if (best_cost < 0) best.nkt = 0;     // no feasible layout
     return best;
 }
 
@@ -283,28 +328,37 @@ struct MkCtx {
     int slot;                     // ring slot of the next entry
     unsigned int par;             // phase parity of that slot
     unsigned long long pf;        // producer: tape offset up to which L2 prefetches have been issued
-    __device__ __forceinline__ MkCtx(const MegaArgs& args) : a(args), entry(0), slot(0), par(0), pf(0) {}
+    // byte offsets of the regions inside mk_smem, fixed for the launch
+    uint32_t xs_off, hs_off, part_off, bar_off;
+    int redsel;                   // which half of the RMS partial-sum buffer the current phase uses (0 / 16)
+    __device__ __forceinline__ MkCtx(const MegaArgs& args) : a(args), entry(0), slot(0), par(0), pf(0), redsel(0) {
+        xs_off = (uint32_t)a.nslot * (uint32_t)a.slot_bytes;
+        hs_off = xs_off + 4u * (uint32_t)a.xs_floats;
+        part_off = hs_off + 4u * (uint32_t)a.dim;
+        bar_off = part_off + 4u * (uint32_t)(MK_PART_FLOATS + 64 + MK_ROPE_FLOATS + a.sc_floats);
+    }
     __device__ __forceinline__ void advance() {
         entry++;
         if (++slot == a.nslot) { slot = 0; par ^= 1u; }
     }
     __device__ __forceinline__ uint8_t* ring() const { return mk_smem; }
-    __device__ __forceinline__ float* xs() const { return reinterpret_cast<float*>(mk_smem + (size_t)a.nslot * a.slot_bytes); }
-    __device__ __forceinline__ float* hs() const { return xs() + a.xs_floats; }
-    __device__ __forceinline__ float* part() const { return hs() + a.dim; }
+    __device__ __forceinline__ float* xs() const { return reinterpret_cast<float*>(mk_smem + xs_off); }
+    __device__ __forceinline__ float* hs() const { return reinterpret_cast<float*>(mk_smem + hs_off); }
+    __device__ __forceinline__ float* part() const { return reinterpret_cast<float*>(mk_smem + part_off); }
     __device__ __forceinline__ float* red() const { return part() + MK_PART_FLOATS; }
     __device__ __forceinline__ float* rope() const { return red() + 64; }
     __device__ __forceinline__ float* sc() const { return rope() + MK_ROPE_FLOATS; }
     __device__ __forceinline__ unsigned long long* full() const {
-        return reinterpret_cast<unsigned long long*>(sc() + a.sc_floats);
+        return reinterpret_cast<unsigned long long*>(mk_smem + bar_off);
     }
     __device__ __forceinline__ unsigned long long* empty() const { return full() + MK_MAX_SLOTS; }
     __device__ __forceinline__ volatile int* abort_flag() const {
         return reinterpret_cast<volatile int*>(empty() + MK_MAX_SLOTS);
     }
-    // per phase p: [p] first work item on this CTA, [8+p] item count, [16+p] rows per ring entry,
-    // [24+p] consumer warps per K segment
+    // per phase p: [p] first row-group of this CTA, [8+p] its number of row-groups;
+    // then per phase and consumer warp (MK_WARP_TAB): row-group slot | K-split index << 8
     __device__ __forceinline__ int* phase_tab() const { return const_cast<int*>(reinterpret_cast<volatile int*>(abort_flag())) + 4; }
+    __device__ __forceinline__ unsigned short* warp_tab() const { return reinterpret_cast<unsigned short*>(phase_tab() + 16); }
     __device__ __forceinline__ MegaStatus* status() const { return a.status; }
     __device__ __forceinline__ int nslot() const { return a.nslot; }
 };
@@ -320,85 +374,92 @@ __device__ __forceinline__ void mk_fail(MkCtx& c, int code, int where) {
     mk_fail_impl(c.abort_flag(), c.status(), code, where);
 }
 
-#define MK_TRACE_EVENTS(L) ((L) * 10 + 2)
+constexpr int MK_EV = 32;             // trace events per layer
+#define MK_TRACE_EVENTS(L) (((L) + 1) * MK_EV)
 __device__ __forceinline__ void mk_trace(const MegaArgs& a, int step, int ev) {
     if (a.trace && step == 0 && threadIdx.x == 0)
         a.trace[(size_t)blockIdx.x * MK_TRACE_EVENTS(a.n_layers) + ev] = clock64();
 }
 
-// Bounded wait on an mbarrier phase.
-__device__ __forceinline__ void mk_wait_bar(MkCtx& c, unsigned long long* bar, uint32_t parity, int code) {
-    if (*c.abort_flag()) return;
-    if (mbar_try(bar, parity)) return;
+// Waits.  The fast path (the awaited thing is already there) is inlined; everything else lives
+// in ONE out-of-line copy per kind of wait, so that the many places that wait add a handful of
+// instructions each to the code a phase runs through (the kernel's speed is bounded by the length
+// of the instruction stream of a phase as much as by its data).  All waits are bounded.
+__device__ __noinline__ void mk_wait_bar_slow(volatile int* abort_flag, MegaStatus* status, long long limit,
+                                              uint32_t bar_s, uint32_t parity, int code, int where) {
+    if (*abort_flag) return;
     const long long t0 = global_ns();
     for (unsigned int it = 1;; ++it) {
-        if (mbar_try(bar, parity)) return;
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar_s), "r"(parity) : "memory");
+        if (ok) return;
+        // a spinning try_wait occupies the shared-memory pipe that the working warps' loads and shuffles
+        // go through: back off between attempts (longer for the producer, which runs a ring ahead)
+        __nanosleep(code == MK_ERR_EMPTY ? 400u : 40u);
         if ((it & 63u) == 0u) {
-            if (*c.abort_flag()) return;
-            if (*(volatile int*)&c.status()->error) { *c.abort_flag() = 1; return; }
-            if (global_ns() - t0 > MK_WAIT_CYCLES) { mk_fail(c, code, (int)c.entry); return; }
+            if (*abort_flag) return;
+            if (*(volatile int*)&status->error) { *abort_flag = 1; return; }
+            if (global_ns() - t0 > limit) { mk_fail_impl(abort_flag, status, code, where); return; }
         }
     }
 }
+__device__ __forceinline__ void mk_wait_bar(MkCtx& c, unsigned long long* bar, uint32_t parity, int code) {
+    if (mbar_try(bar, parity)) return;
+    mk_wait_bar_slow(c.abort_flag(), c.status(), c.a.wait_cycles, smem_u32(bar), parity, code, (int)c.entry);
+}
 
-// Poll two adjacent tagged values (16-byte aligned pair).
-__device__ __forceinline__ void mk_poll2(MkCtx& c, const Tagged* p, unsigned int tag, float& v0, float& v1) {
-    uint4 r = ld_poll16(p);
-    if (r.y != tag || r.w != tag) {
-        if (!*c.abort_flag()) {
-            const long long t0 = global_ns();
-            for (unsigned int it = 1;; ++it) {
-                r = ld_poll16(p);
-                if (r.y == tag && r.w == tag) break;
-                if ((it & 63u) == 0u) {
-                    if (*c.abort_flag()) break;
-                    if (*(volatile int*)&c.status()->error) { *c.abort_flag() = 1; break; }
-                    if (global_ns() - t0 > MK_WAIT_CYCLES) { mk_fail(c, MK_ERR_POLL, (int)tag); break; }
-                }
-            }
+// Re-read a pair of exchange words (16-byte aligned) until both carry `tag`; sys = the words may be
+// written by another GPU.  Returns the raw words: x, z = values, y, w = tags.
+__device__ __noinline__ uint4 mk_poll16_slow(volatile int* abort_flag, MegaStatus* status, long long limit,
+                                             const Tagged* p, unsigned int tag, int sys) {
+    uint4 r = make_uint4(0u, tag, 0u, tag);
+    if (*abort_flag) return r;
+    const long long t0 = global_ns();
+    for (unsigned int it = 1;; ++it) {
+        r = sys ? ld_poll16_sys(p) : ld_poll16(p);
+        if (r.y == tag && r.w == tag) return r;
+        if ((it & 63u) == 0u) {
+            if (*abort_flag) return r;
+            if (*(volatile int*)&status->error) { *abort_flag = 1; return r; }
+            if (global_ns() - t0 > limit) { mk_fail_impl(abort_flag, status, MK_ERR_POLL, (int)tag); return r; }
         }
     }
+}
+// r holds a first attempt; poll on if it is stale.
+__device__ __forceinline__ void mk_poll2_finish(MkCtx& c, const Tagged* p, unsigned int tag, uint4& r) {
+    if (r.y != tag || r.w != tag) r = mk_poll16_slow(c.abort_flag(), c.status(), c.a.wait_cycles, p, tag, 0);
+}
+__device__ __forceinline__ void mk_poll2(MkCtx& c, const Tagged* p, unsigned int tag, float& v0, float& v1) {
+    uint4 r = ld_poll16(p);
+    mk_poll2_finish(c, p, tag, r);
     v0 = __uint_as_float(r.x);
     v1 = __uint_as_float(r.z);
 }
+__device__ __forceinline__ uint4 mk_poll16_sys(MkCtx& c, const Tagged* q, unsigned int tag) {
+    uint4 w = ld_poll16_sys(q);
+    if (w.y != tag || w.w != tag) w = mk_poll16_slow(c.abort_flag(), c.status(), c.a.wait_cycles, q, tag, 1);
+    return w;
+}
+// One exchange word (the token of the previous step).
 __device__ __forceinline__ float mk_poll1(MkCtx& c, const Tagged* p, unsigned int tag) {
     uint2 r = ld_poll8(p);
-    if (r.y != tag) {
-        if (!*c.abort_flag()) {
-            const long long t0 = global_ns();
-            for (unsigned int it = 1;; ++it) {
-                r = ld_poll8(p);
-                if (r.y == tag) break;
-                if ((it & 63u) == 0u) {
-                    if (*c.abort_flag()) break;
-                    if (*(volatile int*)&c.status()->error) { *c.abort_flag() = 1; break; }
-                    if (global_ns() - t0 > MK_WAIT_CYCLES) { mk_fail(c, MK_ERR_POLL, (int)tag); break; }
-                }
+    if (r.y != tag && !*c.abort_flag()) {
+        const long long t0 = global_ns();
+        for (unsigned int it = 1;; ++it) {
+            r = ld_poll8(p);
+            if (r.y == tag) break;
+            if ((it & 63u) == 0u) {
+                if (*c.abort_flag()) break;
+                if (*(volatile int*)&c.status()->error) { *c.abort_flag() = 1; break; }
+                if (global_ns() - t0 > c.a.wait_cycles) { mk_fail(c, MK_ERR_POLL, (int)tag); break; }
             }
         }
     }
     return __uint_as_float(r.x);
-}
-
-// Two adjacent exchange words that another GPU may have written, once both carry `tag` (raw
-// words: x, z = values, y, w = tags).  Bounded like every wait in this kernel.
-__device__ __forceinline__ uint4 mk_poll16_sys(MkCtx& c, const Tagged* q, unsigned int tag) {
-    uint4 w = ld_poll16_sys(q);
-    if (w.y != tag || w.w != tag) {
-        if (!*c.abort_flag()) {
-            const long long t0 = global_ns();
-            for (unsigned int it = 1;; ++it) {
-                w = ld_poll16_sys(q);
-                if (w.y == tag && w.w == tag) break;
-                if ((it & 63u) == 0u) {
-                    if (*c.abort_flag()) break;
-                    if (*(volatile int*)&c.status()->error) { *c.abort_flag() = 1; break; }
-                    if (global_ns() - t0 > MK_WAIT_CYCLES) { mk_fail(c, MK_ERR_POLL, (int)tag); break; }
-                }
-            }
-        }
-    }
-    return w;
 }
 
 // Two adjacent values of a vector that arrives as one row per rank: the rows are added in rank
@@ -417,52 +478,73 @@ __device__ __forceinline__ void mk_poll2_sum(MkCtx& c, const Tagged* p, int stri
 
 // ---------------------------------------------------------------------
 // Fixed-point activations.  For int8 / 4-bit weights the dot products run on
-// the integer pipe (dp4a) without giving up fp32-class accuracy: every group
-// of 16 consecutive activations is scaled by its own s = max|x| / (2^23 - 1)
-// and rounded to a 24-bit integer t = a2*65536 + a1*256 + a0 (a2 signed byte,
-// a1 and a0 unsigned bytes).  sum q_i x_i over the group is then
-// s * (65536 * dp(q, a2) + 256 * dp(q, a1) + dp(q, a0)) with exact integer
-// dot products; the representation error is at most 2^-24 of the group's
-// largest element per term.  Shared-memory layout for a vector of K values
-// (at xs): byte planes P0 | P1 | P2 (K bytes each, element order), then one
-// float2 {s, s * sum(t)} per group of 16.
+// the integer tensor-core path without giving up fp32-class accuracy: every
+// block of 32 consecutive activations is scaled by its own s = max|x| / 8355709
+// and rounded to a 24-bit integer T = a2*65536 + a1*256 + a0 with three SIGNED
+// byte digits (8355711 = 127*65536 + 127*256 + 127 is the largest such T).
+// sum q_i x_i over the block is then s * (65536 dp(q,a2) + 256 dp(q,a1) + dp(q,a0))
+// with exact integer dot products; the representation error is at most 2^-23
+// of the block's largest element per term.
+//
+// Shared-memory layout (at xs), chosen so that the B operand of the MMA is one
+// 8-byte load per lane: blocks are kept in pairs of 192 bytes,
+//   pair j: plane 0 of block 2j | plane 0 of block 2j+1 | plane 1 of 2j | plane 1 of 2j+1 | plane 2 ...
+// and inside a 32-byte plane element e = 16h + 4t + b sits at byte 8t + 4h + b
+// (lane t of an MMA quad reads its two k-quads, columns 4t.. and 16+4t.., as
+// one 8-byte word).  After the planes: one float2 {s, -8 s sum(T)} per block
+// (the second half only for 4-bit weights: their stored nibbles carry a +8 offset).
 // ---------------------------------------------------------------------
-__device__ __forceinline__ uint8_t* xq_plane(MkCtx& c, int K, int k) {
-    return reinterpret_cast<uint8_t*>(c.xs()) + (size_t)k * K;
-}
+__device__ __forceinline__ uint8_t* xq_base(MkCtx& c) { return reinterpret_cast<uint8_t*>(c.xs()); }
+__host__ __device__ inline int xq_plane_bytes(int K) { return ((K + 63) >> 6) * 192; }
 __device__ __forceinline__ float2* xq_scales(MkCtx& c, int K) {
-    return reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(c.xs()) + (size_t)3 * K);
+    return reinterpret_cast<float2*>(xq_base(c) + xq_plane_bytes(K));
+}
+// Bytes of the staged-activation buffer a phase with input width K needs.
+__host__ __device__ inline int xs_bytes_of(int fmt, int K) {
+    return fmt == FMT_F16 ? K * 4 : xq_plane_bytes(K) + ((K >> 5) + 2) * 8;
 }
 
-// All 32 lanes call; lanes 8j..8j+7 hold the 16 values of one group (u0,u1 each).
-// `want_sum`: the group's sum(t) is only needed by 4-bit weights (their -8 offset).
+// All 32 lanes call; lanes 16j..16j+15 hold the 32 values of one block (u0, u1 = elements i, i+1).
+// `want_sum`: the block's sum(T) is only needed by 4-bit weights.
 __device__ __forceinline__ void xq_store_pair(MkCtx& c, int K, int i, bool ok, float u0, float u1, bool want_sum) {
     float m = fmaxf(fabsf(u0), fabsf(u1));
     m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 1));
     m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 2));
     m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 4));
-    // an approximate reciprocal is enough: t is clamped, and the value represented is t * (m / 8388607)
-    const float inv = m > 0.f ? 8388607.0f * __frcp_rn(m) : 0.f;
-    // the group maximum may round to 2^23, which would not fit the signed top byte: clamp
-    const int t0 = max(-8388607, min(8388607, __float2int_rn(u0 * inv)));
-    const int t1 = max(-8388607, min(8388607, __float2int_rn(u1 * inv)));
+    m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 8));
+    // an approximate reciprocal is enough: the value represented is T * (m / 8355709); the factor is two
+    // below the largest three-digit T so that neither the reciprocal's nor the product's rounding can
+    // carry |T| past 8355711
+    const float inv = m > 0.f ? 8355709.0f * __frcp_rn(m) : 0.f;
+    const int t0 = __float2int_rn(u0 * inv);
+    const int t1 = __float2int_rn(u1 * inv);
     int ts = 0;
     if (want_sum) {
         ts = t0 + t1;
         ts += __shfl_xor_sync(MG_FULL_MASK, ts, 1);
         ts += __shfl_xor_sync(MG_FULL_MASK, ts, 2);
         ts += __shfl_xor_sync(MG_FULL_MASK, ts, 4);
+        ts += __shfl_xor_sync(MG_FULL_MASK, ts, 8);
     }
     if (ok) {
-        const unsigned int a = (unsigned)t0, b = (unsigned)t1;
-        *reinterpret_cast<unsigned short*>(xq_plane(c, K, 0) + i) = (unsigned short)((a & 0xffu) | ((b & 0xffu) << 8));
-        *reinterpret_cast<unsigned short*>(xq_plane(c, K, 1) + i) = (unsigned short)(((a >> 8) & 0xffu) | (b & 0xff00u));
-        *reinterpret_cast<unsigned short*>(xq_plane(c, K, 2) + i) = (unsigned short)(((a >> 16) & 0xffu) | ((b >> 8) & 0xff00u));
-        if ((threadIdx.x & 7) == 0) {
-            const float sc = m * (1.0f / 8388607.0f);
-            xq_scales(c, K)[i >> 4] = make_float2(sc, sc * (float)ts);
+        // signed digits: a0 = sext(T & 255), a1 = sext(((T + 128) >> 8) & 255), a2 = ((T + 128) >> 8) + 128 >> 8
+        const int p1a = (t0 + 128) >> 8, p1b = (t1 + 128) >> 8;
+        const int p2a = (p1a + 128) >> 8, p2b = (p1b + 128) >> 8;
+        const int kb = i >> 5, j = i & 31;
+        uint8_t* dst = xq_base(c) + (kb >> 1) * 192 + (kb & 1) * 32 + ((j & 15) >> 2) * 8 + (j >> 4) * 4 + (j & 3);
+        *reinterpret_cast<unsigned short*>(dst) = (unsigned short)((t0 & 0xff) | ((t1 & 0xff) << 8));
+        *reinterpret_cast<unsigned short*>(dst + 64) = (unsigned short)((p1a & 0xff) | ((p1b & 0xff) << 8));
+        *reinterpret_cast<unsigned short*>(dst + 128) = (unsigned short)((p2a & 0xff) | ((p2b & 0xff) << 8));
+        if ((threadIdx.x & 15) == 0) {
+            const float sc = m * (1.0f / 8355709.0f);
+            xq_scales(c, K)[kb] = make_float2(sc, -8.0f * sc * (float)ts);
         }
     }
+}
+// An odd number of blocks leaves the second half of the last pair unwritten: wide tiles read its
+// scale (against all-zero weights), so it must be a finite number.
+__device__ __forceinline__ void xq_pad(MkCtx& c, int K) {
+    if (((K >> 5) & 1) && threadIdx.x == 0) xq_scales(c, K)[K >> 5] = make_float2(0.f, 0.f);
 }
 
 // Poll n tagged values into shared memory dst[0..n) (n even).  All consumer threads call.
@@ -474,106 +556,71 @@ __device__ __forceinline__ void mk_gather(MkCtx& c, const Tagged* src, unsigned 
         dst[i + 1] = b;
     }
 }
-// Re-poll one pair until both tags match (bounded); r holds the first attempt.
-__device__ __forceinline__ void mk_poll2_finish(MkCtx& c, const Tagged* p, unsigned int tag, uint4& r) {
-    if (r.y == tag && r.w == tag) return;
-    if (*c.abort_flag()) return;
-    const long long t0 = global_ns();
-    for (unsigned int it = 1;; ++it) {
-        r = ld_poll16(p);
-        if (r.y == tag && r.w == tag) return;
-        if ((it & 63u) == 0u) {
-            if (*c.abort_flag()) return;
-            if (*(volatile int*)&c.status()->error) { *c.abort_flag() = 1; return; }
-            if (global_ns() - t0 > MK_WAIT_CYCLES) { mk_fail(c, MK_ERR_POLL, (int)tag); return; }
-        }
-    }
-}
-
-// Same, but the values land in xs as fixed-point planes (n a multiple of 32).  A thread's loads
-// for up to four strides are issued together so that their L2 latencies overlap; only then are the
-// tags checked (and stale words polled again).
-__device__ __forceinline__ void mk_gather_q(MkCtx& c, const Tagged* src, unsigned int tag, int n, bool want_sum) {
-    constexpr int STRIDE = 2 * MK_CONSUMERS;
-    for (int i0 = 0; i0 < n; i0 += 4 * STRIDE) {
-        const int ia = i0 + 2 * (int)threadIdx.x, ib = ia + STRIDE, ic = ib + STRIDE, id = ic + STRIDE;
-        const uint4 z = make_uint4(0u, tag, 0u, tag);
-        uint4 ra = z, rb = z, rc = z, rd = z;
-        if (ia < n) ra = ld_poll16(src + ia);
-        if (ib < n) rb = ld_poll16(src + ib);
-        if (ic < n) rc = ld_poll16(src + ic);
-        if (id < n) rd = ld_poll16(src + id);
-        if (ia < n) mk_poll2_finish(c, src + ia, tag, ra);
-        if (ib < n) mk_poll2_finish(c, src + ib, tag, rb);
-        if (ic < n) mk_poll2_finish(c, src + ic, tag, rc);
-        if (id < n) mk_poll2_finish(c, src + id, tag, rd);
-        xq_store_pair(c, n, ia, ia < n, __uint_as_float(ra.x), __uint_as_float(ra.z), want_sum);
-        if (i0 + STRIDE < n) xq_store_pair(c, n, ib, ib < n, __uint_as_float(rb.x), __uint_as_float(rb.z), want_sum);
-        if (i0 + 2 * STRIDE < n) xq_store_pair(c, n, ic, ic < n, __uint_as_float(rc.x), __uint_as_float(rc.z), want_sum);
-        if (i0 + 3 * STRIDE < n) xq_store_pair(c, n, id, id < n, __uint_as_float(rd.x), __uint_as_float(rd.z), want_sum);
-    }
-}
-
 // Sum over the consumer threads (deterministic order); includes one consumer barrier.
 __device__ __forceinline__ float mk_block_sum(MkCtx& c, float v) {
     v = warp_sum(v);
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    if (lane == 0) c.red()[w] = v;
+    if (lane == 0) c.red()[48 + w] = v;
     consumer_sync();
     float t = 0.f;
 #pragma unroll
-    for (int i = 0; i < MK_NW; i++) t += c.red()[i];
+    for (int i = 0; i < MK_NW; i++) t += c.red()[48 + i];
     return t;
-}
-
-__device__ __forceinline__ float dot8_f16(uint4 w, float4 xa, float4 xb) {
-    const __half2* h = reinterpret_cast<const __half2*>(&w);
-    const float2 a0 = __half22float2(h[0]), a1 = __half22float2(h[1]);
-    const float2 a2 = __half22float2(h[2]), a3 = __half22float2(h[3]);
-    float a = a0.x * xa.x;
-    a = fmaf(a0.y, xa.y, a); a = fmaf(a1.x, xa.z, a); a = fmaf(a1.y, xa.w, a);
-    a = fmaf(a2.x, xb.x, a); a = fmaf(a2.y, xb.y, a); a = fmaf(a3.x, xb.z, a); a = fmaf(a3.y, xb.w, a);
-    return a;
 }
 
 // ---------------------------------------------------------------------
 // Producer warp: stream this CTA's tape through the ring.
 // ---------------------------------------------------------------------
-__device__ __forceinline__ void mk_produce_phase(MkCtx& c, const MegaArgs& a, const uint8_t* src, int p, int nrows) {
+// Whole rounds of `step` tiles that fit a ring entry of tpe tiles (at least one).  Used by the
+// producer and the consumers alike.
+__device__ __forceinline__ int rounds_per_entry(int tpe, int step) {
+    return max(1, __float2int_rz(__fdividef((float)tpe + 0.5f, (float)step)));
+}
+
+__device__ __forceinline__ void mk_produce_entry(MkCtx& c, const MegaArgs& a, const uint8_t*& src, uint32_t bytes, int p) {
+    const int slot = c.slot;
+    const uint32_t par = c.par;
+    mk_wait_bar(c, &c.empty()[slot], par ^ 1u, MK_ERR_EMPTY);
+    if ((unsigned long long)(src - a.tape) + bytes > a.tape_bytes || bytes == 0 || bytes > (uint32_t)a.slot_bytes || (bytes & 15u) ||
+        ((unsigned long long)(src - a.tape) & 15ull)) {
+        mk_fail(c, MK_ERR_RANGE, 300000 + p);
+        return;
+    }
+    mbar_expect_tx(&c.full()[slot], bytes);
+    bulk_g2s(c.ring() + (size_t)slot * a.slot_bytes, src, bytes, &c.full()[slot]);
+    src += bytes;
+    c.advance();
+    if (a.prefetch_bytes > 0) {
+        // The ring alone keeps nslot * slot_bytes in flight per SM, too little to saturate HBM when
+        // the activations crowd the ring (wide models).  The tape of a CTA is one contiguous run
+        // through all phases and layers, so the producer also asks L2 for the bytes a fixed distance
+        // ahead; the ring then fills from L2 and DRAM runs ahead of it.
+        const unsigned long long pos = (unsigned long long)(src - a.tape);
+        unsigned long long want = pos + (unsigned long long)a.prefetch_bytes;
+        if (want > a.tape_bytes) want = a.tape_bytes;
+        if (c.pf < pos) c.pf = pos;
+        while (c.pf + 16 <= want) {
+            unsigned long long n = want - c.pf;
+            if (n > 8192ull) n = 8192ull;
+            n &= ~15ull;
+            bulk_prefetch_l2(a.tape + c.pf, (uint32_t)n);
+            c.pf += n;
+        }
+    }
+}
+
+// The entries of one phase, in the consumers' order (see mk_run_phase).
+__device__ __forceinline__ void mk_produce_phase(MkCtx& c, const MegaArgs& a, const uint8_t* src, int p, int nrg) {
     const PhaseGeom g = a.geom[p];
-    const int rpt = 32 >> g.lpr_shift;
-    const int ntiles = (nrows + rpt - 1) >> (5 - g.lpr_shift);
-    for (int t = 0; t < ntiles; t += g.tpe) {
-        const uint32_t bytes = (uint32_t)(min(g.tpe, ntiles - t) * g.tile_bytes);
-        const int slot = c.slot;
-        const uint32_t par = c.par;
-        mk_wait_bar(c, &c.empty()[slot], par ^ 1u, MK_ERR_EMPTY);
-        if ((unsigned long long)(src - a.tape) + bytes > a.tape_bytes || bytes == 0 || bytes > (uint32_t)a.slot_bytes || (bytes & 15u) ||
-            ((unsigned long long)(src - a.tape) & 15ull)) {
-            mk_fail(c, MK_ERR_RANGE, 300000 + p);
-            return;
-        }
-        mbar_expect_tx(&c.full()[slot], bytes);
-        bulk_g2s(c.ring() + (size_t)slot * a.slot_bytes, src, bytes, &c.full()[slot]);
-        src += bytes;
-        c.advance();
-        if (a.prefetch_bytes > 0) {
-            // The ring alone keeps nslot * slot_bytes in flight per SM, too little to saturate HBM when
-            // the activations crowd the ring (wide models).  The tape of a CTA is one contiguous run
-            // through all phases and layers, so the producer also asks L2 for the bytes a fixed distance
-            // ahead; the ring then fills from L2 and DRAM runs ahead of it.
-            const unsigned long long pos = (unsigned long long)(src - a.tape);
-            unsigned long long want = pos + (unsigned long long)a.prefetch_bytes;
-            if (want > a.tape_bytes) want = a.tape_bytes;
-            if (c.pf < pos) c.pf = pos;
-            while (c.pf + 16 <= want) {
-                unsigned long long n = want - c.pf;
-                if (n > 8192ull) n = 8192ull;
-                n &= ~15ull;
-                bulk_prefetch_l2(a.tape + c.pf, (uint32_t)n);
-                c.pf += n;
-            }
-        }
+    const int rem = g.nkt - g.nfull * g.S;
+    for (int rg0 = 0; rg0 < nrg; rg0 += g.RS) {
+        const int nrs = min(g.RS, nrg - rg0);
+        const int step = nrs * g.S;
+        const int R = rounds_per_entry(g.tpe, step);
+        for (int r0 = 0; r0 < g.nfull; r0 += R)
+            mk_produce_entry(c, a, src, (uint32_t)(min(R, g.nfull - r0) * step * g.tile_bytes), p);
+        if (rem) mk_produce_entry(c, a, src, (uint32_t)(nrs * rem * g.tile_bytes), p);
+        if (*c.abort_flag()) return;
     }
 }
 
@@ -582,15 +629,9 @@ __device__ __forceinline__ void mk_producer(MkCtx& c, const MegaArgs& a) {
     const unsigned long long* off = a.tape_off + (size_t)blockIdx.x * (a.n_layers * 4 + 2);
     for (int step = 0; step < a.n_steps; step++) {
         for (int l = a.ls; l < a.le; l++)
-            for (int p = 0; p < 4; p++) {
-                const PhaseShape s = phase_shape_of(p, a.dim, a.q_dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
-                const int nrows = c.phase_tab()[8 + p] * s.rpi;
-                mk_produce_phase(c, a, a.tape + off[l * 4 + p], p, nrows);
-            }
-        if (a.le >= a.n_layers && a.head) {
-            const PhaseShape s = phase_shape_of(PH_HEAD, a.dim, a.q_dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
+            for (int p = 0; p < 4; p++) mk_produce_phase(c, a, a.tape + off[l * 4 + p], p, c.phase_tab()[8 + p]);
+        if (a.le >= a.n_layers && a.head)
             mk_produce_phase(c, a, a.tape + off[a.n_layers * 4], PH_HEAD, c.phase_tab()[8 + PH_HEAD]);
-        }
     }
     // every issued copy has been waited for by the consumers unless the kernel is aborting:
     // then give the copies in flight a bounded time to land before the CTA retires.
@@ -607,37 +648,22 @@ __device__ __forceinline__ void mk_producer(MkCtx& c, const MegaArgs& a) {
 }
 
 // ---------------------------------------------------------------------
-// Consumer side of one matvec phase.
-//   EPI_QKV   : pairs -> bias, RoPE -> tagged q / fp16-rounded tagged k,v
-//   EPI_RESID : out[r] = hs[r] + dot -> tagged
-//   EPI_SWIGLU: pairs (gate, up) -> silu(g) * u -> tagged
-//   EPI_LOGITS: logits[r] (plain store if requested) + running argmax
-// xs holds the (un-normalised) input vector, `scale` the RMSNorm factor
-// (1 for plain inputs; norm weights are already folded into xs).
-// ---------------------------------------------------------------------
-// ---------------------------------------------------------------------
-// One matvec phase on the consumer warps.  ONE code path serves every phase
-// (QKV, wo, gate/up, down, lm_head) so that the instructions stay resident in
-// the instruction caches across the ~120 phases of a token; only the epilogue
-// switches on the phase.  Rows are always processed two at a time:
+// Fused epilogue of one work item.
 //   QKV      : the two rows of a RoPE pair  -> bias, rotate -> tagged q / fp16-rounded tagged k,v
 //   gate/up  : gate row j and up row j      -> silu(g) * u -> tagged
-//   wo, down : two consecutive output rows  -> hs[r] + dot -> tagged
-//   lm_head  : two consecutive vocab rows   -> logits (optional) + running argmax
-// xs holds the input vector (norm weights already folded in), `scale` is the RMSNorm factor.
+//   wo, down : one output row               -> hs[r] + dot -> tagged
+//   lm_head  : one vocab row                -> logits (optional) + running argmax
+// `item` is the index among this rank's items of the phase.
 // ---------------------------------------------------------------------
 template <bool TP>
-__device__ __forceinline__ void mk_epilogue(const MegaArgs& a, MkCtx& c, int p, int layer, unsigned int tag,
-                                            int row, bool has2, float v0, float v1, unsigned long long& best) {
-    const int ib = c.phase_tab()[p];
+__device__ __forceinline__ void mk_epilogue(const MegaArgs& a, MkCtx& c, int p, int layer, unsigned int tag, int item,
+                                            float v0, float v1, unsigned long long& best) {
     {   // self-check: every index an epilogue writes through must lie inside its vector
         const int lim = p == PH_QKV ? (a.q_dim + 2 * a.kv_dim) / 2 : p == PH_GU ? a.ffn_dim : p == PH_HEAD ? a.vocab : a.dim;
-        const int idx = (p == PH_QKV || p == PH_GU) ? ib + (row >> 1) : ib + row + (has2 ? 1 : 0);
-        if (row < 0 || idx >= lim) { mk_fail(c, MK_ERR_RANGE, 1000 * p + 100000 + row); return; }
+        if (item < 0 || item >= lim) { mk_fail(c, MK_ERR_RANGE, 1000 * p + 100000); return; }
     }
     if (p == PH_QKV) {
         // same mapping as qkv_pair(), with the divisions by head_dim/2 done as shifts
-        const int item = ib + (row >> 1);
         const int half = a.head_dim >> 1, hs1 = a.hd_shift - 1;
         const int nq = a.q_dim >> 1, nk = a.kv_dim >> 1;
         int m = 0, i = item;
@@ -674,182 +700,508 @@ __device__ __forceinline__ void mk_epilogue(const MegaArgs& a, MkCtx& c, int p, 
             st_tagged(dst + r1, __half2float(__float2half_rn(v1)), tag);
         }
     } else if (p == PH_GU) {
-        st_tagged(a.xmid + ib + (row >> 1), v0 * (1.0f / (1.0f + expf(-v0))) * v1, tag);
+        st_tagged(a.xmid + item, v0 * (1.0f / (1.0f + expf(-v0))) * v1, tag);
     } else if (p == PH_HEAD) {
-        const int r0 = ib + row;
-        if (a.head == 2) { a.logits[r0] = v0; if (has2) a.logits[r0 + 1] = v1; }
-        unsigned long long key = pack_best(v0, (unsigned)(r0 + a.vocab_base));
+        if (a.head == 2) a.logits[item] = v0;
+        const unsigned long long key = pack_best(v0, (unsigned)(item + a.vocab_base));
         if (key > best) best = key;
-        if (has2) { key = pack_best(v1, (unsigned)(r0 + 1 + a.vocab_base)); if (key > best) best = key; }
     } else {
-        const int r0 = ib + row;
+        // the residual is read before the result is published: the next phase's staging overwrites
+        // hs[item] only after it has seen this very word
+        const float res = c.hs()[item];
         if (!TP) {
-            Tagged* out = p == PH_WO ? a.xhm : a.xh;
-            st_tagged(out + r0, c.hs()[r0] + v0, tag);
-            if (has2) st_tagged(out + r0 + 1, c.hs()[r0 + 1] + v1, tag);
+            st_tagged((p == PH_WO ? a.xhm : a.xh) + item, res + v0, tag);
         } else {
             // partial sum over this rank's heads / FFN features: into row tp_rank of every rank's receive
             // buffer; rank 0's row carries the residual
-            const float w0 = (a.tp_rank == 0 ? c.hs()[r0] : 0.f) + v0;
-            const float w1 = has2 ? (a.tp_rank == 0 ? c.hs()[r0 + 1] : 0.f) + v1 : 0.f;
+            const float w0 = (a.tp_rank == 0 ? res : 0.f) + v0;
             Tagged* const* peers = p == PH_WO ? a.xhm_peer : a.xh_peer;
-            for (int q = 0; q < a.tp_n; q++) {
-                Tagged* out = peers[q] + (size_t)a.tp_rank * a.dim + r0;
-                st_tagged_sys(out, w0, tag);
-                if (has2) st_tagged_sys(out + 1, w1, tag);
-            }
+            for (int q = 0; q < a.tp_n; q++) st_tagged_sys(peers[q] + (size_t)a.tp_rank * a.dim + item, w0, tag);
         }
     }
 }
 
-// Dot product of this lane's share of a tile row with the staged activations.
-// tile: [ni][32] x 16-byte weight chunks, then [ni][32] fp16 block scales (lane order).
-// Lane `part` of a row takes chunks part, part + lpr, ...; chunks beyond the row are zero in the
-// tape (weights and scale), their activation index is clamped so that the loads stay in range.
+// ---------------------------------------------------------------------
+// Tile arithmetic.  Lane (g = lane >> 2, t = lane & 3) of a warp ends up with the partial sums of
+// row-slots g (acc0) and g + 8 (acc1).  Shared memory is addressed with 32-bit shared-space
+// addresses throughout, so that the address arithmetic of the inner loop stays in 32 bits.
+// ---------------------------------------------------------------------
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float2 lds64f(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+
+// D (16x8, int32) = A (16x32 signed bytes, row) x B (32x8 signed bytes, col)
+__device__ __forceinline__ void mma_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint2 b) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y), "r"(0));
+}
+// same with unsigned A bytes (4-bit weights unpacked to 0..15)
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint2 b) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y), "r"(0));
+}
+
+// Per-lane constants of a phase (shared-space addresses).
+//   B columns: tall tiles put digit plane n/2 in column n (even n < 6); wide tiles put plane n/2 of
+//   the even block in even columns and of the odd block in odd columns.  Lane (g, t) supplies column
+//   g and receives columns 2t and 2t + 1, i.e. digit plane t.
+struct LaneGeom {
+    uint32_t a_off;     // this lane's offset inside a tile's A bytes
+    uint32_t d_off;     // offset of its pair of block scales inside the tile
+    uint32_t b_addr;    // its B word in block pair 0 (fp16 weights: its float4 of x in block 0)
+    uint32_t s_addr;    // float2 {s, -8 s sum T} of block 0
+    bool bvalid;        // lane supplies a plane column (others supply zeros)
+    int t;
+};
+
 template <int FMT>
-__device__ __forceinline__ float tile_dot(MkCtx& c, const uint8_t* tile, int ni, int lane, int part, int lpr_shift,
-                                          int K) {
-    float acc = 0.f;
+__device__ __forceinline__ LaneGeom lane_geom(const MkCtx& c, int lane, int wide, int K) {
+    LaneGeom L;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t xs = smem_u32(mk_smem) + c.xs_off;
+    L.t = t;
     if (FMT == FMT_F16) {
-        const int last = (K >> 3) - 1;
-        const float* xs = c.xs();
-#pragma unroll 4
-        for (int i = 0; i < ni; i++) {
-            const uint4 w = lds16(tile + (size_t)(i * 32 + lane) * 16);
-            const int ch = min(part + (i << lpr_shift), last);
-            const float4 xa = *reinterpret_cast<const float4*>(xs + ch * 8);
-            const float4 xb = *reinterpret_cast<const float4*>(xs + ch * 8 + 4);
-            acc += dot8_f16(w, xa, xb);
-        }
-        return acc;
-    }
-    const unsigned short* ds = reinterpret_cast<const unsigned short*>(tile + (size_t)ni * 512);
-    const uint8_t* p0 = xq_plane(c, K, 0);
-    const uint8_t* p1 = xq_plane(c, K, 1);
-    const uint8_t* p2 = xq_plane(c, K, 2);
-    const float2* sc = xq_scales(c, K);
-    if (FMT == FMT_Q8_0) {
-        const int last = (K >> 4) - 1;
-#pragma unroll 4
-        for (int i = 0; i < ni; i++) {
-            const uint4 w = lds16(tile + (size_t)(i * 32 + lane) * 16);
-            const float d = half_bits_to_float(ds[i * 32 + lane]);
-            const int g = min(part + (i << lpr_shift), last);          // chunk = activation group
-            const float f = group_dot_s8(w, lds16(p0 + g * 16), lds16(p1 + g * 16), lds16(p2 + g * 16));
-            acc = fmaf(d * sc[g].x, f, acc);
-        }
+        L.a_off = lane * 16; L.d_off = 0; L.b_addr = xs + t * 16; L.s_addr = 0; L.bvalid = true;
     } else {
-        const int last = (K >> 5) - 1;
-#pragma unroll 4
-        for (int i = 0; i < ni; i++) {
-            const uint4 w = lds16(tile + (size_t)(i * 32 + lane) * 16);
-            const float d = half_bits_to_float(ds[i * 32 + lane]);
-            const int b = min(part + (i << lpr_shift), last);          // chunk = block = groups 2b, 2b+1
-            const int ga = 2 * b, gb = 2 * b + 1;
-            // word i holds bytes 4i..4i+3: low nibbles = elements 4i..4i+3 (group A), high = 16+4i.. (group B)
-            const float fa = group_dot_u4(w.x & 0x0f0f0f0fu, w.y & 0x0f0f0f0fu, w.z & 0x0f0f0f0fu, w.w & 0x0f0f0f0fu,
-                                          lds16(p0 + ga * 16), lds16(p1 + ga * 16), lds16(p2 + ga * 16));
-            const float fb = group_dot_u4((w.x >> 4) & 0x0f0f0f0fu, (w.y >> 4) & 0x0f0f0f0fu,
-                                          (w.z >> 4) & 0x0f0f0f0fu, (w.w >> 4) & 0x0f0f0f0fu,
-                                          lds16(p0 + gb * 16), lds16(p1 + gb * 16), lds16(p2 + gb * 16));
-            const float2 sa = sc[ga], sb = sc[gb];
-            // sum (nib - 8) x = sum nib x - 8 sum x
-            acc = fmaf(d, fmaf(sa.x, fa, sb.x * fb) - 8.0f * (sa.y + sb.y), acc);
-        }
+        L.a_off = FMT == FMT_Q8_0 ? lane * 16 : lane * 8;
+        L.d_off = (FMT == FMT_Q8_0 ? 512 : 256) + g * 4;
+        L.bvalid = g < 6 && (wide || (g & 1) == 0);
+        L.b_addr = xs + (g >> 1) * 64 + (wide ? (g & 1) * 32 : 0) + t * 8;
+        L.s_addr = xs + xq_plane_bytes(K);
     }
-    return acc;
+    return L;
 }
 
-template <int FMT, bool TP>
-__device__ __forceinline__ void mk_phase(const MegaArgs& a, MkCtx& c, int p, int layer, unsigned int tag, float scale,
-                                         unsigned long long& best) {
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const PhaseGeom g = a.geom[p];
-    const int K = p == PH_DOWN ? a.ffn_dim : p == PH_WO ? a.q_dim : a.dim;
-    const bool pairs = (p == PH_QKV || p == PH_GU);
-    const int nrows = c.phase_tab()[8 + p] * (pairs ? 2 : 1);
-    const int lpr = 1 << g.lpr_shift;
-    const int part = lane & (lpr - 1), rloc = lane >> g.lpr_shift;
-    const int ntiles = (nrows + (32 >> g.lpr_shift) - 1) >> (5 - g.lpr_shift);
-    int carry = w;                                   // this warp's next tile, relative to the entry's first tile
+template <int FMT>
+__device__ __forceinline__ void tile_mac(uint32_t tile, int kt, int wide, const LaneGeom& L, float& acc0, float& acc1) {
+    if (FMT == FMT_F16) {
+        // 16 row-slots x 16 columns of halves: lane (g, t) holds columns 4t..4t+3 of slots g and g + 8
+        const uint4 A = lds128(tile + L.a_off);
+        const uint32_t xa = L.b_addr + (wide ? 2 * kt : kt) * 64;
+        const float4 xe = lds128f(xa);
+        const float4 xo = wide ? lds128f(xa + 64) : xe;
+        const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&A.x));
+        const float2 a1 = __half22float2(*reinterpret_cast<const __half2*>(&A.y));
+        const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&A.z));
+        const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(&A.w));
+        acc0 = fmaf(a0.x, xe.x, acc0); acc0 = fmaf(a0.y, xe.y, acc0);
+        acc0 = fmaf(a1.x, xe.z, acc0); acc0 = fmaf(a1.y, xe.w, acc0);
+        acc1 = fmaf(b0.x, xo.x, acc1); acc1 = fmaf(b0.y, xo.y, acc1);
+        acc1 = fmaf(b1.x, xo.z, acc1); acc1 = fmaf(b1.y, xo.w, acc1);
+        return;
+    }
+    const int kb = wide ? 2 * kt : kt;                      // (even) block of the tile
+    uint2 B = make_uint2(0u, 0u);
+    if (L.bvalid) B = lds64(L.b_addr + (kb >> 1) * 192 + (wide ? 0 : (kb & 1) * 32));
+    const float2 se = lds64f(L.s_addr + kb * 8);
+    const float2 so = wide ? lds64f(L.s_addr + kb * 8 + 8) : se;
+    const uint32_t dd = lds32(tile + L.d_off);
+    int d[4];
+    if (FMT == FMT_Q8_0) {
+        const uint4 A = lds128(tile + L.a_off);
+        mma_s8s8(d, A.x, A.y, A.z, A.w, B);
+    } else {
+        // 16 nibble bytes per block: byte 4t+b = element 4t+b (low) and 16+4t+b (high)
+        const uint2 A = lds64(tile + L.a_off);
+        mma_u8s8(d, A.x & 0x0f0f0f0fu, A.y & 0x0f0f0f0fu, (A.x >> 4) & 0x0f0f0f0fu, (A.y >> 4) & 0x0f0f0f0fu, B);
+    }
+    const float2 df = __half22float2(*reinterpret_cast<const __half2*>(&dd));    // scales of slots g, g + 8
+    const float c0 = (float)d[0];
+    const float c1 = (float)(wide ? d[3] : d[2]);
+    if (FMT == FMT_Q8_0) {
+        acc0 = fmaf(df.x * se.x, c0, acc0);
+        acc1 = fmaf(df.y * so.x, c1, acc1);
+    } else {
+        // sum (nib - 8) x = sum nib x - 8 sum x; the correction rides in the lanes of plane 0
+        const float oe = L.t == 0 ? se.y : 0.f, oo = L.t == 0 ? so.y : 0.f;
+        acc0 = fmaf(df.x, fmaf(se.x, c0, oe), acc0);
+        acc1 = fmaf(df.y, fmaf(so.x, c1, oo), acc1);
+    }
+}
 
-    for (int t = 0; t < ntiles; t += g.tpe) {
-        const int nt = min(g.tpe, ntiles - t);
-        const int slot = c.slot;
-        int tl = carry;
-        carry -= nt;
-        // Every warp observes every entry's arrival, also of entries it owns no tile of: a warp that
-        // skipped ahead could otherwise meet a slot whose barrier is a whole ring revolution behind,
-        // take the stale phase for its own (parity waits cannot tell them apart) and release the slot
-        // early.  Waiting on a completed phase costs a few cycles.
-        mk_wait_bar(c, &c.full()[slot], c.par, MK_ERR_FULL);
-        if (tl < nt) {
-            // tiles are dealt to the warps round-robin over the whole phase
-            const uint8_t* base = c.ring() + (size_t)slot * a.slot_bytes;
-            if (slot < 0 || slot >= a.nslot || nt * g.tile_bytes > a.slot_bytes || g.ni <= 0) {
-                mk_fail(c, MK_ERR_RANGE, 200000 + p);
-                tl = nt + ((tl - nt) % MK_NW + MK_NW) % MK_NW;      // skip this entry's tiles
+// ---------------------------------------------------------------------
+// Staging of one pair of activations as fixed point (see "Fixed-point activations" above), with
+// every address worked out by the caller: dst = plane-0 halfword of the pair, sc_addr = the
+// block's float2.  All 32 lanes call; lanes 16j..16j+15 hold one block.  `lead`: first lane of a block.
+// ---------------------------------------------------------------------
+__device__ __forceinline__ void sts16(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)v));
+}
+__device__ __forceinline__ void xq_store_fast(uint32_t dst, uint32_t sc_addr, bool ok, bool lead, float u0, float u1,
+                                              bool want_sum) {
+    float m = fmaxf(fabsf(u0), fabsf(u1));
+    m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 2));
+    m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 4));
+    m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 8));
+    // an approximate reciprocal is enough: the value represented is T * (m / 8355709); the factor is two
+    // below the largest three-digit T so that neither the reciprocal's nor the product's rounding can
+    // carry |T| past 8355711
+    float inv;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(m));
+    inv = m > 1e-30f ? inv * 8355709.0f : 0.f;
+    const int t0 = __float2int_rn(u0 * inv), t1 = __float2int_rn(u1 * inv);
+    int ts = 0;
+    if (want_sum) {
+        ts = t0 + t1;
+        ts += __shfl_xor_sync(MG_FULL_MASK, ts, 1);
+        ts += __shfl_xor_sync(MG_FULL_MASK, ts, 2);
+        ts += __shfl_xor_sync(MG_FULL_MASK, ts, 4);
+        ts += __shfl_xor_sync(MG_FULL_MASK, ts, 8);
+    }
+    if (ok) {
+        // signed digits a0 = byte 0 of T, a1 = byte 1 of T + 128, a2 = byte 2 of T + 128 + 32768
+        sts16(dst, __byte_perm((unsigned)t0, (unsigned)t1, 0x0040));
+        sts16(dst + 64, __byte_perm((unsigned)(t0 + 128), (unsigned)(t1 + 128), 0x0051));
+        sts16(dst + 128, __byte_perm((unsigned)(t0 + 32896), (unsigned)(t1 + 32896), 0x0062));
+        if (lead) {
+            const float sc = m > 1e-30f ? m * (1.0f / 8355709.0f) : 0.f;
+            asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(sc_addr), "f"(sc), "f"(-8.0f * sc * (float)ts));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------
+// Input staging.  A thread's share of the phase's input vector is the pairs of elements
+// 2 tid + 960 k (k = 0, 1, ...: "strides").  NS strides are handled at a time, all of their loads
+// in flight together, with straight-line code (NS is a compile-time constant chosen from the
+// vector's length: the shuffles and conversions of the strides then overlap instead of queueing
+// behind branches).
+// ---------------------------------------------------------------------
+enum : int { SRC_POLL = 0, SRC_EMBED = 1, SRC_PLAIN = 2 };
+constexpr int MK_STRIDE = 2 * MK_CONSUMERS;
+
+struct StageSrc {
+    int kind;
+    const Tagged* src;
+    unsigned int tag;
+    int n;
+    const float* norm_w;
+    int token;
+};
+
+// Profiling build only (-DMK_PROBE_P=<phase>): extra clock stamps of thread 0 inside that phase.
+#ifdef MK_PROBE_P
+#define MK_STAMP(EV) do { if (P == MK_PROBE_P && a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * MK_TRACE_EVENTS(a.n_layers) + trace_base + (EV)] = clock64(); } while (0)
+#else
+#define MK_STAMP(EV) do { } while (0)
+#endif
+
+// The first token's hidden state does not come through an exchange buffer: embedding row or plain vector.
+__device__ __noinline__ float2 mk_direct_pair(const MegaArgs& a, int kind, int token, int i) {
+    if (kind == SRC_EMBED)
+        return make_float2(embed_value(a.embed_w, a.head_fmt, a.dim, token, i), embed_value(a.embed_w, a.head_fmt, a.dim, token, i + 1));
+    return make_float2(a.h_in[i], a.h_in[i + 1]);
+}
+
+template <int NS, bool NORMED, bool TP>
+__device__ __forceinline__ void stage_issue(const MegaArgs& a, const StageSrc& s, int i0, uint4 (&r)[NS], float2 (&nw)[NS]) {
+    const int tid = threadIdx.x;
+#pragma unroll
+    for (int k = 0; k < NS; k++) {
+        const int i = i0 + k * MK_STRIDE + 2 * tid;
+        r[k] = make_uint4(0u, s.tag, 0u, s.tag);
+        nw[k] = make_float2(1.f, 1.f);
+        if (i < s.n) {
+            if (NORMED) nw[k] = *reinterpret_cast<const float2*>(s.norm_w + i);
+            if (s.kind == SRC_POLL) {
+                if (!TP || !NORMED) r[k] = ld_poll16(s.src + i);
+            } else {
+                const float2 v = mk_direct_pair(a, s.kind, s.token, i);
+                r[k].x = __float_as_uint(v.x); r[k].z = __float_as_uint(v.y);
             }
-            for (; tl < nt; tl += MK_NW) {
-                float v = tile_dot<FMT>(c, base + (size_t)tl * g.tile_bytes, g.ni, lane, part, g.lpr_shift, K);
-                for (int o = lpr >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(MG_FULL_MASK, v, o);
-                v *= scale;
-                const int row = ((t + tl) << (5 - g.lpr_shift)) + rloc;       // row within this CTA's phase rows
-                if (pairs) {
-                    const float v1 = __shfl_down_sync(MG_FULL_MASK, v, lpr);  // the partner row sits lpr lanes up
-                    if (part == 0 && (rloc & 1) == 0 && row < nrows) mk_epilogue<TP>(a, c, p, layer, tag, row, true, v, v1, best);
-                } else {
-                    if (part == 0 && row < nrows) mk_epilogue<TP>(a, c, p, layer, tag, row, false, v, 0.f, best);
+        }
+    }
+}
+
+// Completes the loads of NS strides, stages them; ss accumulates the squares of a hidden state.
+// st_dst / st_sc: staging addresses of this thread's stride-0 pair; stride number kk0 + k.
+template <int NS, int FMT, bool NORMED, bool TP>
+__device__ __forceinline__ void stage_finish(const MegaArgs& a, MkCtx& c, const StageSrc& s, int i0, int kk0, uint4 (&r)[NS],
+                                             float2 (&nw)[NS], uint32_t st_dst, uint32_t st_sc, float& ss) {
+    const int tid = threadIdx.x;
+#pragma unroll
+    for (int k = 0; k < NS; k++) {
+        const int i = i0 + k * MK_STRIDE + 2 * tid;
+        const bool ok = i < s.n;
+        float v0 = 0.f, v1 = 0.f;
+        if (ok) {
+            if (TP && NORMED && s.kind == SRC_POLL) mk_poll2_sum(c, s.src + i, a.dim, a.tp_n, s.tag, v0, v1);
+            else { mk_poll2_finish(c, s.src + i, s.tag, r[k]); v0 = __uint_as_float(r[k].x); v1 = __uint_as_float(r[k].z); }
+            if (NORMED) {
+                *reinterpret_cast<float2*>(c.hs() + i) = make_float2(v0, v1);
+                ss = fmaf(v0, v0, ss);
+                ss = fmaf(v1, v1, ss);
+                v0 *= nw[k].x; v1 *= nw[k].y;
+            }
+        }
+        if (FMT != FMT_F16) {
+            if (NS == 1 || i0 + k * MK_STRIDE < s.n)         // (uniform) strides wholly beyond the vector need no shuffles
+                xq_store_fast(st_dst + 2880u * (kk0 + k), st_sc + 240u * (kk0 + k), ok, (tid & 15) == 0, v0, v1, FMT == FMT_Q4_0);
+        } else if (ok) *reinterpret_cast<float2*>(c.xs() + i) = make_float2(v0, v1);
+    }
+}
+
+// ---------------------------------------------------------------------
+// One phase of a layer (or lm_head) on the consumer warps, P and the weight format fixed at
+// compile time.  What bounds a phase is the chain of dependent instructions between "the input
+// has arrived" and "the output is on its way", so the order of the work is:
+//   1. everything that does not depend on the input: the warp's tiles and addresses, the epilogue
+//      thread's row indices, residuals, biases and output pointers (this runs while the exchange
+//      words of the previous phase are still on their way);
+//   2. the input vector is polled and staged in xs; barrier;
+//   3. every warp multiplies its tiles and leaves the sums of its 16 row-slots in part[]:
+//      [row-group][slot][K-split], the splits of a slot padded with zeros to a multiple of four; barrier;
+//   4. one thread per row-slot adds the slot's splits (float4 loads, fixed order), meets the other
+//      block's sum (wide tiles) and its partner row (row pairs) by shuffle, and runs the fused epilogue:
+//        QKV      : the two rows of a RoPE pair  -> bias, rotate -> tagged q / fp16-rounded tagged k,v
+//        gate/up  : gate row j and up row j      -> silu(g) * u -> tagged
+//        wo, down : one output row               -> residual + dot -> tagged
+//        lm_head  : one vocab row                -> logits (optional) + running argmax
+// With a hidden state as input (QKV, gate/up, lm_head) the raw values are kept in hs (the residual),
+// the staged values are value * norm weight, and the RMSNorm factor 1/sqrt(mean(h^2) + eps) is
+// applied in the epilogue; the warps' sums of squares travel through red[] (alternating halves).
+//
+// Ring entries of a phase (producer and consumers agree): a PASS is RS row-groups at a time; within
+// a pass the tiles come in ROUNDS of (row-groups of the pass) x S tiles, one per working warp;
+// an entry holds as many whole rounds as fit a slot, and the last, incomplete round of a pass
+// (nkt not a multiple of S) travels in an entry of its own.  So a warp's tiles sit at fixed
+// offsets in every entry and the inner loop has no address arithmetic beyond an increment.
+// ---------------------------------------------------------------------
+template <int P, int FMT, bool TP>
+__device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const StageSrc& s, int layer, unsigned int tag_out,
+                                             int trace_base, unsigned long long& best) {
+    constexpr bool kNormed = (P == PH_QKV || P == PH_GU || P == PH_HEAD);
+    constexpr bool kPairs = (P == PH_QKV || P == PH_GU);
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const uint32_t sm0 = smem_u32(mk_smem);
+
+    // ---- 1. set-up that does not depend on the input ----
+    const PhaseGeom& g = a.geom[P];
+    const int ub = c.phase_tab()[P], nrg = c.phase_tab()[8 + P];
+    const int S = g.S, RS = g.RS, nkt = g.nkt, wide = g.wide, tile_bytes = g.tile_bytes;
+    const unsigned int rk = c.warp_tab()[P * 16 + w];
+    const int rs = rk & 0xff, kp = rk >> 8;                  // rs = 255: this warp has no tiles in the phase
+    const LaneGeom L = lane_geom<FMT>(c, lane, wide, g.K);
+    const float wt = FMT == FMT_F16 ? 1.0f : L.t == 0 ? 1.0f : L.t == 1 ? 256.0f : L.t == 2 ? 65536.0f : 0.0f;
+    const int sp = S == 1 ? 1 : (S + 3) & ~3;                // splits per slot as stored
+    const uint32_t part_s = sm0 + c.part_off;
+    const int lim = P == PH_QKV ? (a.q_dim + 2 * a.kv_dim) / 2 : P == PH_GU ? a.ffn_dim : P == PH_HEAD ? a.vocab : a.dim;
+    // staging addresses of this thread's first pair (element 2 tid); stride k adds 15 block pairs
+    const uint32_t st_dst = sm0 + c.xs_off + (uint32_t)((tid >> 5) * 192 + ((tid >> 4) & 1) * 32 + ((tid & 7) >> 1) * 8 +
+                                                        ((tid >> 3) & 1) * 4 + (tid & 1) * 2);
+    const uint32_t st_sc = sm0 + c.xs_off + (uint32_t)xq_plane_bytes(s.n) + (uint32_t)(tid >> 4) * 8u;
+    // epilogue of the (single) row-slot this thread finishes, for the phases that fit one round
+    const int nslots = nrg * 16;
+    const int e_s = tid & 15;
+    const int e_item = ((ub + (tid >> 4)) << g.ipg_shift) + e_s;
+    const bool e_act = tid < nslots && e_s < (1 << g.ipg_shift) && e_item < lim;
+    const uint32_t e_pr = part_s + (uint32_t)tid * (uint32_t)sp * 4u;
+    float e_res = 0.f, e_b0 = 0.f, e_b1 = 0.f;
+    int e_m = 0, e_r0 = 0, e_r1 = 0;
+    if (P == PH_QKV && e_act) {
+        // same mapping as qkv_pair(), with the divisions by head_dim/2 done as shifts
+        const int half = a.head_dim >> 1, hs1 = a.hd_shift - 1;
+        const int nq = a.q_dim >> 1, nk = a.kv_dim >> 1;
+        int i = e_item;
+        if (i >= nq) { i -= nq; e_m = 1; }
+        if (e_m == 1 && i >= nk) { i -= nk; e_m = 2; }
+        if (e_m < 2) {
+            const int head = i >> hs1, j = i - (head << hs1);
+            e_r0 = (head << a.hd_shift) + j;
+            e_r1 = e_r0 + half;
+        } else {
+            e_r0 = 2 * i;
+            e_r1 = e_r0 + 1;
+        }
+        if (a.qkv_bias) {
+            const float* bias = a.qkv_bias + (size_t)layer * (a.q_dim + 2 * a.kv_dim) +
+                                (e_m == 0 ? 0 : e_m == 1 ? a.q_dim : a.q_dim + a.kv_dim);
+            e_b0 = bias[e_r0];
+            e_b1 = bias[e_r1];
+        }
+    }
+    // the residual: hs was staged by this layer's QKV (for wo) / gate-up (for down) phase
+    if ((P == PH_WO || P == PH_DOWN) && e_act) e_res = (!TP || a.tp_rank == 0) ? c.hs()[e_item] : 0.f;
+    MK_STAMP(23);
+
+    // ---- 2. poll and stage the input, barrier ----
+    float ss = 0.f;
+    if (FMT != FMT_F16 && ((s.n >> 5) & 1) && tid == 0)    // odd number of blocks: the unused half pair's scale must be finite
+        *reinterpret_cast<float2*>(mk_smem + c.xs_off + xq_plane_bytes(s.n) + (s.n >> 5) * 8) = make_float2(0.f, 0.f);
+    if (s.n <= MK_STRIDE) {
+        uint4 r[1]; float2 nw[1];
+        stage_issue<1, kNormed, TP>(a, s, 0, r, nw);
+        stage_finish<1, FMT, kNormed, TP>(a, c, s, 0, 0, r, nw, st_dst, st_sc, ss);
+    } else if (s.n <= 3 * MK_STRIDE) {
+        uint4 r[3]; float2 nw[3];
+        stage_issue<3, kNormed, TP>(a, s, 0, r, nw);
+        stage_finish<3, FMT, kNormed, TP>(a, c, s, 0, 0, r, nw, st_dst, st_sc, ss);
+    } else {
+        uint4 r[6]; float2 nw[6];
+        for (int i0 = 0, kk = 0; i0 < s.n; i0 += 6 * MK_STRIDE, kk += 6) {
+            stage_issue<6, kNormed, TP>(a, s, i0, r, nw);
+            stage_finish<6, FMT, kNormed, TP>(a, c, s, i0, kk, r, nw, st_dst, st_sc, ss);
+        }
+    }
+    float e_cs = 1.f, e_sn = 0.f;
+    if (kNormed) {
+        ss = warp_sum(ss);
+        c.redsel ^= 16;
+        if (lane == 0) c.red()[c.redsel + w] = ss;
+    }
+    MK_STAMP(25);
+    consumer_sync();                           // xs, hs and the sums of squares are published
+    mk_trace(a, 0, trace_base + 2 * (P == PH_HEAD ? 0 : P));
+    if (P == PH_HEAD && blockIdx.x == 0 && a.h_out)          // the hidden state that entered lm_head (ExportHidden)
+        for (int i = tid; i < a.dim; i += MK_CONSUMERS) a.h_out[i] = c.hs()[i];
+    if (P == PH_QKV && e_act && e_m < 2) {                   // (the step's RoPE row is published by this phase's barrier)
+        const int j = e_r0 & (a.head_dim - 1);
+        e_cs = c.rope()[j]; e_sn = c.rope()[(a.head_dim >> 1) + j];
+    }
+    MK_STAMP(26);
+
+    // ---- 3. tiles ----
+    for (int rg0 = 0; rg0 < nrg; rg0 += RS) {
+        const int nrs = min(RS, nrg - rg0);
+        const int step = nrs * S;
+        const int R = rounds_per_entry(g.tpe, step);
+        const bool act = rs < nrs;
+        const uint32_t rstride = (uint32_t)(step * tile_bytes);
+        const uint32_t woff = (uint32_t)((rs * S + kp) * tile_bytes);
+        float acc0 = 0.f, acc1 = 0.f;
+        int kt = kp;
+        for (int r0 = 0; r0 < g.nfull; r0 += R) {
+            const int rounds = min(R, g.nfull - r0);
+            mk_wait_bar(c, &c.full()[c.slot], c.par, MK_ERR_FULL);
+            if (act) {
+                uint32_t tile = sm0 + (uint32_t)c.slot * (uint32_t)a.slot_bytes + woff;
+                for (int rr = 0; rr < rounds; rr++, tile += rstride, kt += S) tile_mac<FMT>(tile, kt, wide, L, acc0, acc1);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&c.empty()[c.slot]);
+            c.advance();
+        }
+        const int rem = nkt - g.nfull * S;
+        if (rem) {                                           // the incomplete last round: an entry of its own
+            mk_wait_bar(c, &c.full()[c.slot], c.par, MK_ERR_FULL);
+            if (act && kp < rem)
+                tile_mac<FMT>(sm0 + (uint32_t)c.slot * (uint32_t)a.slot_bytes + (uint32_t)((rs * rem + kp) * tile_bytes), kt, wide, L, acc0, acc1);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&c.empty()[c.slot]);
+            c.advance();
+        }
+        MK_STAMP(27);
+        if (act) {
+            // quad sum: lanes t = 0..2 hold the three digit planes (fp16 weights: four column quarters)
+            acc0 *= wt; acc1 *= wt;
+            acc0 += __shfl_xor_sync(MG_FULL_MASK, acc0, 1); acc1 += __shfl_xor_sync(MG_FULL_MASK, acc1, 1);
+            acc0 += __shfl_xor_sync(MG_FULL_MASK, acc0, 2); acc1 += __shfl_xor_sync(MG_FULL_MASK, acc1, 2);
+            // lane t of a quad stores split kp + t: t = 0 the sum, the others the zero padding
+            const int col = kp + L.t;
+            if (L.t == 0 || (kp == S - 1 && col < sp)) {
+                float* part = c.part() + ((rg0 + rs) * 16 + (lane >> 2)) * sp + col;
+                part[0] = L.t == 0 ? acc0 : 0.f;
+                part[8 * sp] = L.t == 0 ? acc1 : 0.f;        // slot g + 8
+            }
+        }
+    }
+    mk_trace(a, 0, trace_base + 11 + 3 * (P == PH_HEAD ? 0 : P));
+    consumer_sync();                     // every warp is done with xs; the partial sums are published
+    mk_trace(a, 0, trace_base + 12 + 3 * (P == PH_HEAD ? 0 : P));
+
+    // ---- 4. epilogue: whole warps (the shuffles need every lane) ----
+    if ((tid & ~31) < nslots) {
+        float scale = 1.0f;
+        if (kNormed) {
+            // RMSNorm factor of the staged vector (16th entry of a half of red[]: always 0)
+            const uint32_t rr = part_s + (uint32_t)(MK_PART_FLOATS + c.redsel) * 4u;
+            const float4 r0 = lds128f(rr), r1 = lds128f(rr + 16), r2 = lds128f(rr + 32), r3 = lds128f(rr + 48);
+            const float t = ((r0.x + r0.y) + (r0.z + r0.w)) + ((r1.x + r1.y) + (r1.z + r1.w)) +
+                            (((r2.x + r2.y) + (r2.z + r2.w)) + ((r3.x + r3.y) + (r3.z + r3.w)));
+            scale = rsqrtf(fmaf(t, a.inv_dim, a.eps));
+        }
+        MK_STAMP(29);
+        const int nq = sp >> 2;
+        for (int sl = tid; sl < ((nslots + 31) & ~31); sl += MK_CONSUMERS) {
+            float v = 0.f;
+            if (sl < nslots) {
+                const uint32_t pr = e_pr + (uint32_t)(sl - tid) * (uint32_t)sp * 4u;
+                if (S == 1) v = __uint_as_float(lds32(pr));
+                else {
+                    // up to 16 splits, zero-padded to a multiple of four: all loads at once, the unused quads dropped
+                    const float4 f0 = lds128f(pr), f1 = lds128f(pr + 16), f2 = lds128f(pr + 32), f3 = lds128f(pr + 48);
+                    const float s0 = (f0.x + f0.y) + (f0.z + f0.w), s1 = (f1.x + f1.y) + (f1.z + f1.w);
+                    const float s2 = (f2.x + f2.y) + (f2.z + f2.w), s3 = (f3.x + f3.y) + (f3.z + f3.w);
+                    v = (s0 + (nq > 1 ? s1 : 0.f)) + ((nq > 2 ? s2 : 0.f) + (nq > 3 ? s3 : 0.f));
                 }
             }
-            carry = tl - nt;
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&c.empty()[slot]);
-        c.advance();
-    }
-}
-
-// Hidden-state staging fused with RMSNorm.  Each thread fetches a pair of elements of the
-// hidden state (from an exchange buffer, the embedding row, or a plain vector), keeps the raw
-// values in hs (the residual), writes value * norm weight to xs and returns the RMSNorm factor
-// 1/sqrt(mean(h^2) + eps), which callers fold into the activation registers.  One barrier.
-enum : int { SRC_POLL = 0, SRC_EMBED = 1, SRC_PLAIN = 2 };
-template <bool TP>
-__device__ __forceinline__ float mk_stage_norm(const MegaArgs& a, MkCtx& c, int src_kind, const Tagged* xsrc,
-                                               unsigned int tag, int token, const float* norm_w, bool quant, bool quant_sum) {
-    float ss = 0.f;
-    for (int i0 = 0; i0 < a.dim; i0 += 2 * MK_CONSUMERS) {
-        const int i = i0 + 2 * (int)threadIdx.x;
-        const bool ok = i < a.dim;
-        float v0 = 0.f, v1 = 0.f;
-        float2 nw = make_float2(0.f, 0.f);
-        if (ok) {
-            nw = *reinterpret_cast<const float2*>(norm_w + i);   // issued before the poll
-            if (src_kind == SRC_POLL) {
-                if (!TP) mk_poll2(c, xsrc + i, tag, v0, v1);
-                else mk_poll2_sum(c, xsrc + i, a.dim, a.tp_n, tag, v0, v1);
-            } else if (src_kind == SRC_EMBED) {
-                v0 = embed_value(a.embed_w, a.head_fmt, a.dim, token, i);
-                v1 = embed_value(a.embed_w, a.head_fmt, a.dim, token, i + 1);
-            } else {
-                v0 = a.h_in[i];
-                v1 = a.h_in[i + 1];
+            if (wide) v += __shfl_xor_sync(MG_FULL_MASK, v, 8);               // the odd blocks' sum of the same row
+            float v1 = 0.f;
+            if (kPairs) v1 = __shfl_xor_sync(MG_FULL_MASK, v, wide ? 4 : 8) * scale;   // second row of a pair
+            v *= scale;
+            MK_STAMP(30);
+            if (P == PH_HEAD) {
+                const int item = ((ub + (sl >> 4)) << g.ipg_shift) + e_s;
+                if (sl < nslots && e_s < (1 << g.ipg_shift) && item < lim) {
+                    if (a.head == 2) a.logits[item] = v;
+                    const unsigned long long key = pack_best(v, (unsigned)(item + a.vocab_base));
+                    if (key > best) best = key;
+                }
+            } else if (e_act) {
+                if (P == PH_QKV) {
+                    float v0 = v + e_b0;
+                    v1 += e_b1;
+                    const float t0 = v0 * e_cs - v1 * e_sn, t1 = v0 * e_sn + v1 * e_cs;   // K, Q: rotate (V: cs = 1, sn = 0)
+                    if (e_m == 0) {
+                        st_tagged(a.xq + e_r0, t0, tag_out);
+                        st_tagged(a.xq + e_r1, t1, tag_out);
+                    } else {
+                        // K (after RoPE) and V are stored in the cache as fp16: exchange the rounded values
+                        Tagged* dst = a.xkv + (e_m == 1 ? 0 : a.kv_dim);
+                        st_tagged(dst + e_r0, __half2float(__float2half_rn(t0)), tag_out);
+                        st_tagged(dst + e_r1, __half2float(__float2half_rn(t1)), tag_out);
+                    }
+                } else if (P == PH_GU) {
+                    st_tagged(a.xmid + e_item, v * __fdividef(1.0f, 1.0f + __expf(-v)) * v1, tag_out);
+                } else if (!TP) {
+                    st_tagged((P == PH_WO ? a.xhm : a.xh) + e_item, e_res + v, tag_out);
+                } else {
+                    // partial sum over this rank's heads / FFN features: into row tp_rank of every rank's receive
+                    // buffer; rank 0's row carries the residual
+                    Tagged* const* peers = P == PH_WO ? a.xhm_peer : a.xh_peer;
+                    for (int q = 0; q < a.tp_n; q++) st_tagged_sys(peers[q] + (size_t)a.tp_rank * a.dim + e_item, e_res + v, tag_out);
+                }
             }
-            c.hs()[i] = v0;
-            c.hs()[i + 1] = v1;
-            ss = fmaf(v0, v0, ss);
-            ss = fmaf(v1, v1, ss);
-        }
-        if (quant) {
-            xq_store_pair(c, a.dim, i, ok, v0 * nw.x, v1 * nw.y, quant_sum);
-        } else if (ok) {
-            c.xs()[i] = v0 * nw.x;
-            c.xs()[i + 1] = v1 * nw.y;
         }
     }
-    const float tot = mk_block_sum(c, ss);     // barrier: xs and hs are published
-    return rsqrtf(tot / (float)a.dim + a.eps);
+    mk_trace(a, 0, trace_base + 2 * (P == PH_HEAD ? 0 : P) + 1);
 }
 
 // ---------------------------------------------------------------------
@@ -1041,8 +1393,6 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
     const int pos0 = a.st->pos;
     int token = a.st->token;
     const bool do_head = a.le >= L && a.head;
-    const int ph_begin = a.ls * 4;
-    const int ph_end = a.le * 4 + (do_head ? 1 : 0);
 
     for (int step = 0; step < a.n_steps; step++) {
         const unsigned int ep = a.epoch + (unsigned)step * (unsigned)(L * MK_EPOCHS_PER_LAYER + 8);
@@ -1057,50 +1407,40 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
             c.rope()[tid] = tid < half ? a.cos_tab[(size_t)pos * half + tid] : a.sin_tab[(size_t)pos * half + tid - half];
         unsigned long long best = 0ull;
 
-        for (int ph = ph_begin; ph < ph_end; ph++) {
-            const bool is_head = ph >= L * 4;
-            const int l = is_head ? L : (ph >> 2);
-            const int p = is_head ? PH_HEAD : (ph & 3);
-            // tags of layer l: +1 q/kv, +2 attn, +3 h after wo, +4 ffn mid, +5 h after down
+        // tags of layer l: +1 q/kv, +2 attn, +3 h after wo, +4 ffn mid, +5 h after down
+#define MK_LAYER(FMT)                                                                                              \
+        {                                                                                                          \
+            StageSrc s0{SRC_POLL, a.xh, tag_prev_h, a.dim, a.norms + (size_t)l * 2 * a.dim, token};                \
+            if (l == a.ls) s0.kind = a.embed ? SRC_EMBED : SRC_PLAIN;                                              \
+            mk_run_phase<PH_QKV, FMT, TP>(a, c, s0, l, base + 1, l * MK_EV, best);                                 \
+            if ((int)blockIdx.x < a.n_heads) {                                                                     \
+                if (a.head_dim == 64) mk_attention<64>(a, c, l, pos, base + 1, base + 2);                          \
+                else if (a.head_dim == 128) mk_attention<128>(a, c, l, pos, base + 1, base + 2);                   \
+                else mk_attention<32>(a, c, l, pos, base + 1, base + 2);                                           \
+                mk_trace(a, step, l * MK_EV + 9);                                                                  \
+            }                                                                                                      \
+            const StageSrc s1{SRC_POLL, a.xattn, base + 2, a.q_dim, nullptr, token};                               \
+            mk_run_phase<PH_WO, FMT, TP>(a, c, s1, l, base + 3, l * MK_EV, best);                                  \
+            const StageSrc s2{SRC_POLL, a.xhm, base + 3, a.dim, a.norms + (size_t)l * 2 * a.dim + a.dim, token};   \
+            mk_run_phase<PH_GU, FMT, TP>(a, c, s2, l, base + 4, l * MK_EV, best);                                  \
+            const StageSrc s3{SRC_POLL, a.xmid, base + 4, a.ffn_dim, nullptr, token};                              \
+            mk_run_phase<PH_DOWN, FMT, TP>(a, c, s3, l, base + 5, l * MK_EV, best);                                \
+        }
+        for (int l = a.ls; l < a.le; l++) {
             const unsigned int base = ep + (unsigned)l * MK_EPOCHS_PER_LAYER;
             const unsigned int tag_prev_h = base - MK_EPOCHS_PER_LAYER + 5;
-            if (p == PH_QKV) mk_trace(a, step, l * 10 + 8);
-
-            // ---- input staging ----
-            float scale = 1.0f;
-            if (p == PH_QKV || p == PH_GU || p == PH_HEAD) {
-                int kind = SRC_POLL;
-                const Tagged* src = a.xh;
-                unsigned int tag = tag_prev_h;
-                const float* nw = is_head ? a.final_norm : a.norms + (size_t)l * 2 * a.dim;
-                if (p == PH_GU) { src = a.xhm; tag = base + 3; nw += a.dim; }
-                else if (p == PH_QKV && l == a.ls) kind = a.embed ? SRC_EMBED : SRC_PLAIN;
-                scale = mk_stage_norm<TP>(a, c, kind, src, tag, token, nw, (is_head ? a.head_fmt : a.layer_fmt) != FMT_F16,
-                                      (is_head ? a.head_fmt : a.layer_fmt) == FMT_Q4_0);
-            } else {
-                if (p == PH_WO && (int)blockIdx.x < a.n_heads) {
-                    if (a.head_dim == 64) mk_attention<64>(a, c, l, pos, base + 1, base + 2);
-                    else if (a.head_dim == 128) mk_attention<128>(a, c, l, pos, base + 1, base + 2);
-                    else mk_attention<32>(a, c, l, pos, base + 1, base + 2);
-                    mk_trace(a, step, l * 10 + 9);
-                }
-                const bool wo = p == PH_WO;
-                if (a.layer_fmt != FMT_F16) mk_gather_q(c, wo ? a.xattn : a.xmid, wo ? base + 2 : base + 4, wo ? a.q_dim : a.ffn_dim, a.layer_fmt == FMT_Q4_0);
-                else mk_gather(c, wo ? a.xattn : a.xmid, wo ? base + 2 : base + 4, c.xs(), wo ? a.q_dim : a.ffn_dim);
-                consumer_sync();
-            }
-            if (is_head && blockIdx.x == 0 && a.h_out && step == a.n_steps - 1)
-                for (int i = tid; i < a.dim; i += MK_CONSUMERS) a.h_out[i] = c.hs()[i];
-            mk_trace(a, step, l * 10 + 2 * (is_head ? 0 : p));
-
-            // ---- matvec + fused epilogue ----
-            const unsigned int tag_out = base + (p == PH_QKV ? 1u : p == PH_WO ? 3u : p == PH_GU ? 4u : 5u);
-            const int fmt = is_head ? a.head_fmt : a.layer_fmt;
-            if (fmt == FMT_Q8_0) mk_phase<FMT_Q8_0, TP>(a, c, p, l, tag_out, scale, best);
-            else if (fmt == FMT_Q4_0) mk_phase<FMT_Q4_0, TP>(a, c, p, l, tag_out, scale, best);
-            else mk_phase<FMT_F16, TP>(a, c, p, l, tag_out, scale, best);
-            consumer_sync();             // xs / hs / part are reused by the next phase
-            mk_trace(a, step, l * 10 + 2 * (is_head ? 0 : p) + 1);
+            mk_trace(a, step, l * MK_EV + 8);
+            if (a.layer_fmt == FMT_Q8_0) MK_LAYER(FMT_Q8_0)
+            else if (a.layer_fmt == FMT_Q4_0) MK_LAYER(FMT_Q4_0)
+            else MK_LAYER(FMT_F16)
+        }
+#undef MK_LAYER
+        if (do_head) {
+            const unsigned int base = ep + (unsigned)L * MK_EPOCHS_PER_LAYER;
+            const StageSrc sh{SRC_POLL, a.xh, base - MK_EPOCHS_PER_LAYER + 5, a.dim, a.final_norm, token};
+            if (a.head_fmt == FMT_Q8_0) mk_run_phase<PH_HEAD, FMT_Q8_0, TP>(a, c, sh, L, base + 5, L * MK_EV, best);
+            else if (a.head_fmt == FMT_Q4_0) mk_run_phase<PH_HEAD, FMT_Q4_0, TP>(a, c, sh, L, base + 5, L * MK_EV, best);
+            else mk_run_phase<PH_HEAD, FMT_F16, TP>(a, c, sh, L, base + 5, L * MK_EV, best);
         }
 
         if (!do_head) {
@@ -1122,7 +1462,8 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
             }
         } else {
             // CTA argmax -> one atomic per CTA -> the last CTA publishes the token
-            unsigned long long* sb = reinterpret_cast<unsigned long long*>(c.part());
+            // (not in part[]: the threads that run lm_head's epilogue may still be reading it)
+            unsigned long long* sb = reinterpret_cast<unsigned long long*>(c.red() + 32);
             unsigned long long wb = best;         // candidates may sit in any lane (cross-segment path)
 #pragma unroll
             for (int sh = 16; sh > 0; sh >>= 1) {
@@ -1174,12 +1515,12 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
 
 __host__ __device__ inline size_t mk_smem_bytes(int nslot, int slot_bytes, int xs_floats, int dim, int sc_floats) {
     return (size_t)nslot * slot_bytes + ((size_t)xs_floats + dim + MK_PART_FLOATS + 64 + MK_ROPE_FLOATS + sc_floats) * 4 +
-           2 * MK_MAX_SLOTS * 8 + 16 + 144;
+           2 * MK_MAX_SLOTS * 8 + 16 + 64 + 5 * 16 * 2 + 16;
 }
 
 // TP = false: one GPU (no peer pointers are touched); TP = true: one rank of a tensor-parallel group.
 template <bool TP>
-__global__ void __launch_bounds__(MK_THREADS, 1) mega_decode_kernel(const MegaArgs a) {
+__global__ void __launch_bounds__(MK_THREADS, 1) mega_decode_kernel(const __grid_constant__ MegaArgs a) {
     MkCtx c(a);
     if (threadIdx.x == 0) {
         for (int i = 0; i < a.nslot; i++) {
@@ -1187,11 +1528,18 @@ __global__ void __launch_bounds__(MK_THREADS, 1) mega_decode_kernel(const MegaAr
             mbar_init(&c.empty()[i], MK_NW);
         }
         *c.abort_flag() = 0;
+        c.red()[15] = 0.f; c.red()[31] = 0.f;      // 16th entry of the two halves of the RMS partial sums
         for (int p = 0; p <= PH_HEAD; p++) {
             const PhaseShape sh = phase_shape_of(p, a.dim, a.q_dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
-            const int ib = item_begin(sh.items, blockIdx.x, gridDim.x);
-            c.phase_tab()[p] = ib;
-            c.phase_tab()[8 + p] = item_begin(sh.items, blockIdx.x + 1, gridDim.x) - ib;
+            const int ipg = 1 << a.geom[p].ipg_shift;
+            const int units = (sh.items + ipg - 1) >> a.geom[p].ipg_shift;
+            const int ub = unit_begin(units, blockIdx.x, gridDim.x);
+            c.phase_tab()[p] = ub;
+            c.phase_tab()[8 + p] = unit_begin(units, blockIdx.x + 1, gridDim.x) - ub;
+            for (int w = 0; w < 16; w++) {
+                const int S = a.geom[p].S, rs = w / S;
+                c.warp_tab()[p * 16 + w] = (unsigned short)(rs < a.geom[p].RS ? (rs | ((w - rs * S) << 8)) : 255);
+            }
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1202,3 +1550,4 @@ __global__ void __launch_bounds__(MK_THREADS, 1) mega_decode_kernel(const MegaAr
 }
 
 }  // namespace mg
+
