@@ -228,11 +228,17 @@ MG_API int mg_dequant_rows(mg_engine* e, int idx, int row0, int nrows, float* ou
 MG_API int mg_read_kv(mg_engine* e, int layer, int pos0, int npos, uint16_t* k_out, uint16_t* v_out);
 /* Per-phase timeline of ONE greedy step from the current cursor (the counterpart of the reference's
  * per-op [PROFILE] timing at pos 1, cuda_fused_infer_q4.go:147-242).  stamps receives
- * [n_ctas][n_events] SM clock values of each CTA's first thread, n_events = n_layers*10 + 2: per layer,
- * event 2p = input of phase p staged, 2p+1 = phase p done (p: 0 QKV, 1 wo, 2 gate/up, 3 down),
- * 8 = layer start, 9 = attention done (CTAs that run a head); then lm_head input staged / done.
+ * [n_ctas][n_events] SM clock values of each CTA's first thread, n_events = (n_layers + 1) * 32: per
+ * layer (lm_head counts as layer n_layers, phase 0), event 2p = input of phase p staged, 2p+1 = phase p
+ * done (p: 0 QKV, 1 wo, 2 gate/up, 3 down), 8 = layer start, 9 = attention done (CTAs that run a head),
+ * 11+3p = the CTA's tiles of phase p multiplied, 12+3p = all warps past them; other slots unused.
  * Needs the persistent kernel; capacity is in stamps. */
 MG_API int mg_trace_step(mg_engine* e, long long* stamps, int capacity, int* n_ctas, int* n_events);
+/* Limit of every wait inside the persistent kernel (ring barriers, exchange polls), in milliseconds
+ * of SM clock at 2 GHz; the default is about a second.  A wait that runs out makes the step return
+ * MG_ERR_TIMEOUT; the context stays usable.  The reference's device-side waits (WaitMailbox,
+ * cuda_fused_infer.go:575-590) have no limit at all. */
+MG_API int mg_set_wait_limit_ms(mg_engine* e, int ms);
 /* ---- replay API (CaptureGraph / Launch / UpdateAndLaunch / ValidateGraphCapture, cuda_graph.go:313-739) ----
  * The reference captures a layer range into a CUDA graph and replays it with the position patched
  * in a device-side parameter block.  Here every step already replays a cached graph (or runs the

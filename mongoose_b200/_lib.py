@@ -80,6 +80,7 @@ SIGNATURES = {
     "mg_dequant_rows": (ci, [vp, ci, ci, ci, vp]),
     "mg_read_kv": (ci, [vp, ci, ci, ci, vp, vp]),
     "mg_trace_step": (ci, [vp, vp, ci, vp, vp]),
+    "mg_set_wait_limit_ms": (ci, [vp, ci]),
     "mg_set_layer_range": (ci, [vp, ci, ci]),
     "mg_partial_step_continue": (ci, [vp, ci, ci, ci, vp, vp]),
     "mg_queue_hidden_to": (ci, [vp, vp]),

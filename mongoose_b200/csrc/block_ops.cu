@@ -195,7 +195,9 @@ void mongoose_q4_0_matvec_dp4a(const float* act, const void* w_blocks, float* ou
 //
 // The array's name is only a host-side handle; the device address is looked up once per device with
 // cudaGetSymbolAddress while that device is current.  That lookup happens on the FIRST call on a
-// device, so make the first call outside any stream capture.  Every call overwrites the whole
+// device, so make the first call outside any stream capture.  The address is remembered per device
+// for the life of the process: after cudaDeviceReset() the library must not be used on that device
+// again (the remembered address belongs to the destroyed context).  Every call overwrites the whole
 // region it uses before reading it, so nothing needs clearing between calls, but all calls share
 // the one array: two calls that overlap on the GPU (different streams, different threads) race.
 // Returns MG_OK, MG_ERR_ARG (NULL pointer, K not a multiple of 32, or K > 32768) or MG_ERR_CUDA;
@@ -223,10 +225,16 @@ int mongoose_q4_0_matvec_dp4a_static(const float* act, const void* w_blocks, flo
         }
         scratch = g_static_ptr[dev];
     }
+    // Each launch's own status is checked: an error that an earlier, unrelated call left behind is
+    // cleared first so that it is not taken for one of ours (a sticky error - a faulted context -
+    // comes back from the next check all the same, and is reported as what it is).
+    (void)cudaGetLastError();
     quantize_act_kernel<<<cdiv(K / 32, 8), 256, 0, stream>>>(act, (ActBlock*)scratch, K / 32);
+    if ((ce = cudaGetLastError()) != cudaSuccess)
+        return static_fail(MG_ERR_CUDA, "launch of the activation quantizer failed on device %d (CUDA error %d)", dev, (int)ce);
     q4_0_dp4a_kernel<<<cdiv(N, 8), 256, 0, stream>>>((const uint8_t*)w_blocks, (const ActBlock*)scratch, out, N, K, 1);
-    ce = cudaPeekAtLastError();
-    if (ce != cudaSuccess) return static_fail(MG_ERR_CUDA, "kernel launch failed on device %d (error %d)", dev, (int)ce);
+    if ((ce = cudaGetLastError()) != cudaSuccess)
+        return static_fail(MG_ERR_CUDA, "launch of the matvec failed on device %d (CUDA error %d)", dev, (int)ce);
     return MG_OK;
 }
 

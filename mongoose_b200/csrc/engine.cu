@@ -123,7 +123,7 @@ struct mg_engine {
     // layer-range pipeline (mg_set_layer_range, mg_queue_hidden_to, L3 bridge)
     int own_ls = 0, own_le = 0;         // layers this engine holds weights for; [0, n_layers) by default
     cudaEvent_t sent_event = nullptr;   // recorded after this engine's hidden state has been copied to the next stage
-    cudaEvent_t mail_event = nullptr;   // the sending stage's sent_event of the hidden state last queued to this engine
+    cudaEvent_t mail_event = nullptr;   // this engine's own event: recorded behind the arrival of the hidden state last queued to it
     unsigned int mail_queued = 0, mail_taken = 0;
     float* l3 = nullptr;                // pinned host copy of the hidden state (the reference's "L3 bridge")
     cudaStream_t copy_stream = nullptr;
@@ -938,7 +938,7 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
     MegaArgs a{};
     a.dim = c.dim; a.kv_dim = c.kv_dim; a.head_dim = c.head_dim; a.n_heads = c.n_heads; a.n_kv_heads = c.n_kv_heads;
     a.ffn_dim = c.ffn_dim; a.vocab = c.vocab; a.n_layers = L; a.max_seq = c.max_seq;
-    a.layer_fmt = c.layer_fmt; a.head_fmt = c.head_fmt; a.eps = c.rms_eps; a.inv_dim = 1.0f / (float)c.dim;
+    a.layer_fmt = c.layer_fmt; a.head_fmt = c.head_fmt; a.eps = c.rms_eps; a.inv_dim = 1.0f / (float)c.dim; a.dbg = getenv("MG_DBG") ? atoi(getenv("MG_DBG")) : 0;
     a.ls = ls; a.le = le; a.head = (le >= L) ? head : 0; a.embed = (mode == MODE_EMBED); a.n_steps = n_steps;
     a.epoch = e->epoch;
     e->epoch += (unsigned)n_steps * (unsigned)(L * MK_EPOCHS_PER_LAYER + 8);
@@ -1108,6 +1108,7 @@ int mg_create(const mg_config* cfg, mg_engine** out) {
     }
     e->own_ls = 0; e->own_le = c.n_layers;
     if (cudaEventCreateWithFlags(&e->sent_event, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&e->mail_event, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&e->compute_done, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&e->l3_done, cudaEventDisableTiming) != cudaSuccess ||
         cudaStreamCreateWithFlags(&e->copy_stream, cudaStreamNonBlocking) != cudaSuccess ||
@@ -1204,6 +1205,7 @@ void mg_destroy(mg_engine* e) {
     if (e->copy_stream) { cudaStreamSynchronize(e->copy_stream); cudaStreamDestroy(e->copy_stream); }
     if (e->l3) cudaFreeHost(e->l3);
     if (e->sent_event) cudaEventDestroy(e->sent_event);
+    if (e->mail_event) cudaEventDestroy(e->mail_event);
     if (e->compute_done) cudaEventDestroy(e->compute_done);
     if (e->l3_done) cudaEventDestroy(e->l3_done);
     if (e->stream) cudaStreamDestroy(e->stream);
@@ -1399,7 +1401,9 @@ int mg_queue_hidden_to(mg_engine* src, mg_engine* dst) {
     // the next stage's stream orders itself after the copy; its host thread may also ask with mg_wait_mailbox
     if ((rc = check_engine(dst))) return rc;
     MG_CUDA(dst, cudaStreamWaitEvent(dst->stream, src->sent_event, 0));
-    dst->mail_event = src->sent_event;   // the event, not the engine: a destroyed sender yields an error, not a stale pointer
+    // the receiver asks its OWN event (recorded on its stream behind the wait for the copy): the sender
+    // may be destroyed before mg_wait_mailbox is called
+    MG_CUDA(dst, cudaEventRecord(dst->mail_event, dst->stream));
     dst->mail_queued++;
     return MG_OK;
 }
@@ -1412,7 +1416,7 @@ int mg_wait_mailbox(mg_engine* e, int timeout_ms) {
         return std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() >= timeout_ms;
     };
     for (;;) {
-        if (e->mail_queued != e->mail_taken && e->mail_event) {
+        if (e->mail_queued != e->mail_taken) {
             const cudaError_t q = cudaEventQuery(e->mail_event);
             if (q == cudaSuccess) { e->mail_taken = e->mail_queued; return MG_OK; }
             if (q != cudaErrorNotReady) return fail(e, MG_ERR_CUDA, "mg_wait_mailbox: %s", cudaGetErrorString(q));
@@ -1650,6 +1654,12 @@ int mg_trace_step(mg_engine* e, long long* stamps, int capacity, int* n_ctas, in
     return check_mega_status(e);
 }
 
+int mg_set_wait_limit_ms(mg_engine* e, int ms) {
+    if (!e || ms <= 0) return MG_ERR_ARG;
+    e->mk_wait = (long long)ms * 2000000ll;
+    return MG_OK;
+}
+
 int mg_tp_partition(const mg_config* cfg, int rank, int size, mg_tp_shard* out) {
     if (!cfg || !out) return MG_ERR_ARG;
     if (cfg->n_heads <= 0 || cfg->n_kv_heads <= 0 || cfg->n_heads % cfg->n_kv_heads || cfg->ffn_dim % 32 || cfg->vocab <= 0)
@@ -1741,13 +1751,12 @@ int mg_tp_init(mg_engine* e, int rank, int size, const void* id, size_t bytes) {
         MG_CUDA(e, cudaMemcpy(&opened, d_flag, sizeof(int), cudaMemcpyDeviceToHost));
         cudaFree(d_all);
         e->tp_fused = opened != 0;
-        if (e->tp_fused) {   // only this library's kernels sit between the phases: early launch is safe again
-            const char* nopdl = getenv("MG_NO_PDL");
-            e->use_pdl = !(nopdl && nopdl[0] == '1');
-        }
         if (!e->tp_fused) e->err = "tensor-parallel exchange through ncclAllReduce (peer mapping unavailable or MG_TP_NCCL=1)";
     }
-    e->use_pdl = false;    // launches alternate with library collectives; keep plain stream order
+    // Programmatic dependent launch stays off under tensor parallelism, on both exchange paths: the
+    // per-phase kernels alternate with library collectives (NCCL path), and with the in-kernel exchange
+    // an early-launched consumer would spin on words that a peer's not-yet-running kernel must write.
+    e->use_pdl = false;
     e->built = false;
     return MG_OK;
 }

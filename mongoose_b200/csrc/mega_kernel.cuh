@@ -97,6 +97,7 @@ struct MegaArgs {
     int layer_fmt, head_fmt;
     float eps;
     float inv_dim;          // 1 / dim
+    int dbg;                // experiment switches
     int ls, le;             // layer range
     int head;               // HEAD_NONE / HEAD_ARGMAX / HEAD_LOGITS (0/1/2)
     int embed;              // 1: hidden state from the embedding row of st->token, 0: from h_in
@@ -1095,14 +1096,19 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
         const bool act = rs < nrs;
         const uint32_t rstride = (uint32_t)(step * tile_bytes);
         const uint32_t woff = (uint32_t)((rs * S + kp) * tile_bytes);
-        float acc0 = 0.f, acc1 = 0.f;
+        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
         int kt = kp;
         for (int r0 = 0; r0 < g.nfull; r0 += R) {
             const int rounds = min(R, g.nfull - r0);
             mk_wait_bar(c, &c.full()[c.slot], c.par, MK_ERR_FULL);
             if (act) {
                 uint32_t tile = sm0 + (uint32_t)c.slot * (uint32_t)a.slot_bytes + woff;
-                for (int rr = 0; rr < rounds; rr++, tile += rstride, kt += S) tile_mac<FMT>(tile, kt, wide, L, acc0, acc1);
+                int rr = 0;
+                for (; rr + 2 <= rounds; rr += 2, tile += 2 * rstride, kt += 2 * S) {     // two independent tiles in flight
+                    tile_mac<FMT>(tile, kt, wide, L, acc0, acc1);
+                    tile_mac<FMT>(tile + rstride, kt + S, wide, L, acc2, acc3);
+                }
+                if (rr < rounds) { tile_mac<FMT>(tile, kt, wide, L, acc0, acc1); kt += S; }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&c.empty()[c.slot]);
@@ -1120,7 +1126,7 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
         MK_STAMP(27);
         if (act) {
             // quad sum: lanes t = 0..2 hold the three digit planes (fp16 weights: four column quarters)
-            acc0 *= wt; acc1 *= wt;
+            acc0 = (acc0 + acc2) * wt; acc1 = (acc1 + acc3) * wt;
             acc0 += __shfl_xor_sync(MG_FULL_MASK, acc0, 1); acc1 += __shfl_xor_sync(MG_FULL_MASK, acc1, 1);
             acc0 += __shfl_xor_sync(MG_FULL_MASK, acc0, 2); acc1 += __shfl_xor_sync(MG_FULL_MASK, acc1, 2);
             // lane t of a quad stores split kp + t: t = 0 the sum, the others the zero padding
@@ -1145,7 +1151,7 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
             const float4 r0 = lds128f(rr), r1 = lds128f(rr + 16), r2 = lds128f(rr + 32), r3 = lds128f(rr + 48);
             const float t = ((r0.x + r0.y) + (r0.z + r0.w)) + ((r1.x + r1.y) + (r1.z + r1.w)) +
                             (((r2.x + r2.y) + (r2.z + r2.w)) + ((r3.x + r3.y) + (r3.z + r3.w)));
-            scale = rsqrtf(fmaf(t, a.inv_dim, a.eps));
+            scale = (a.dbg & 4) ? 1.0f / sqrtf(t / (float)a.dim + a.eps) : rsqrtf(fmaf(t, a.inv_dim, a.eps));
         }
         MK_STAMP(29);
         const int nq = sp >> 2;
@@ -1189,7 +1195,7 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
                         st_tagged(dst + e_r1, __half2float(__float2half_rn(t1)), tag_out);
                     }
                 } else if (P == PH_GU) {
-                    st_tagged(a.xmid + e_item, v * __fdividef(1.0f, 1.0f + __expf(-v)) * v1, tag_out);
+                    st_tagged(a.xmid + e_item, (a.dbg & 1) ? v * (1.0f / (1.0f + expf(-v))) * v1 : v * __fdividef(1.0f, 1.0f + __expf(-v)) * v1, tag_out);
                 } else if (!TP) {
                     st_tagged((P == PH_WO ? a.xhm : a.xh) + e_item, e_res + v, tag_out);
                 } else {
@@ -1205,18 +1211,38 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
 }
 
 // ---------------------------------------------------------------------
-// Attention for one query head on this CTA (fp16 KV cache).
-// Cached K/V rows do not depend on this token, so each thread loads the rows it
-// will need into registers BEFORE it waits for q: thread t holds the K row of
-// position t, thread (group g, dim pair dp) holds V[g + j*Gp][2dp..2dp+1] for
-// j < MK_VPF.  Longer contexts take the remainder from L2 in unrolled batches.
+// Attention for one query head on this CTA (fp16 KV cache), three barriers.
+// Cached K/V rows do not depend on this token, so they are loaded into registers BEFORE q is
+// waited for.
+//   scores : four adjacent lanes share a position (a quarter of the head's dims each); unit
+//            u = tid / 4 takes positions u, u + 120, ...; the first NPRE of them come from registers;
+//   softmax: one maximum over the CTA; exp(s - max) is formed where it is used;
+//   P . V  : warp w takes positions w, w + 15, ... (the first NV from registers), a lane HD / 32
+//            adjacent dims; the warps' partial outputs and partial sums of exp meet in shared memory.
 // ---------------------------------------------------------------------
-constexpr int MK_VPF = 16;
-
-__device__ __forceinline__ float dot8_kq(uint4 kk, const float* q) {
+template <int VPL>
+__device__ __forceinline__ uint2 ldcg_v(const __half* p) {
+    if (VPL == 1) return make_uint2(__ldcg(reinterpret_cast<const unsigned short*>(p)), 0u);
+    if (VPL == 2) return make_uint2(__ldcg(reinterpret_cast<const unsigned int*>(p)), 0u);
+    return __ldcg(reinterpret_cast<const uint2*>(p));
+}
+template <int VPL>
+__device__ __forceinline__ void fma_v(float (&acc)[VPL], float p, uint2 v) {
+    if (VPL == 1) {
+        acc[0] = fmaf(p, __half2float(__ushort_as_half((unsigned short)v.x)), acc[0]);
+    } else {
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+        acc[0] = fmaf(p, f0.x, acc[0]); acc[1] = fmaf(p, f0.y, acc[1]);
+        if (VPL == 4) {
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+            acc[2] = fmaf(p, f1.x, acc[2]); acc[3] = fmaf(p, f1.y, acc[3]);
+        }
+    }
+}
+// dot of 8 fp16 K values with 8 floats of q in shared memory
+__device__ __forceinline__ float dot8_kq(uint4 kk, uint32_t q_s) {
     const __half2* h = reinterpret_cast<const __half2*>(&kk);
-    const float4 qa = reinterpret_cast<const float4*>(q)[0];
-    const float4 qb = reinterpret_cast<const float4*>(q)[1];
+    const float4 qa = lds128f(q_s), qb = lds128f(q_s + 16);
     const float2 k0 = __half22float2(h[0]), k1 = __half22float2(h[1]);
     const float2 k2 = __half22float2(h[2]), k3 = __half22float2(h[3]);
     float d0 = qa.x * k0.x, d1 = qa.y * k0.y;
@@ -1229,35 +1255,40 @@ __device__ __forceinline__ float dot8_kq(uint4 kk, const float* q) {
 template <int HD>
 __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int layer, int pos, unsigned int tag_in,
                                              unsigned int tag_out) {
-    constexpr int KV = HD / 8;                 // 16-byte pieces of one K row
-    constexpr int DP = HD / 2;                 // dim pairs
-    constexpr int Gp = MK_CONSUMERS / DP;      // whole position groups: 15 for hd 64, 7 for hd 128, 30 for hd 32
+    constexpr int DPL = HD / 4;                // dims per lane in the score phase
+    constexpr int KV4 = DPL / 8;               // 16-byte pieces of K per lane and position
+    constexpr int NPRE = HD == 128 ? 2 : 4;    // positions per unit held in registers
+    constexpr int UNITS = MK_CONSUMERS / 4;    // 120
+    constexpr int VPL = HD / 32;               // dims per lane in P . V
+    constexpr int NV = 16;                     // positions per warp held in registers
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int head = blockIdx.x;
     const int kvh = head / (a.n_heads / a.n_kv_heads);
-    const int tid = threadIdx.x;
     const size_t lbase = (size_t)layer * a.max_seq * a.kv_dim;
     __half* kc = a.kc + lbase + kvh * HD;
     __half* vc = a.vc + lbase + kvh * HD;
-    float* qs = c.xs();                 // HD
-    float* kn = c.xs() + HD;            // new K row
-    float* vn = c.xs() + 2 * HD;        // new V row
-    const int g = tid / DP, dp = tid - g * DP;
+    const uint32_t xs_s = smem_u32(mk_smem) + c.xs_off;        // q | new k | new v, HD floats each
+    const int u = tid >> 2, qp = tid & 3;
 
-    // ---- prefetch cached rows (positions < pos) ----
-    uint4 kreg[KV];
+    // ---- cached rows (positions < pos) into registers ----
+    uint4 kreg[NPRE][KV4];
 #pragma unroll
-    for (int i = 0; i < KV; i++) kreg[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (tid < pos) {
-        const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)tid * a.kv_dim);
+    for (int i = 0; i < NPRE; i++) {
+        const int t = u + i * UNITS;
 #pragma unroll
-        for (int i = 0; i < KV; i++) kreg[i] = __ldcg(kp + i);
+        for (int j = 0; j < KV4; j++) kreg[i][j] = make_uint4(0u, 0u, 0u, 0u);
+        if (t < pos) {
+            const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)t * a.kv_dim + qp * DPL);
+#pragma unroll
+            for (int j = 0; j < KV4; j++) kreg[i][j] = __ldcg(kp + j);
+        }
     }
-    __half2 vreg[MK_VPF];
+    uint2 vreg[NV];
 #pragma unroll
-    for (int j = 0; j < MK_VPF; j++) {
-        const int t = g + j * Gp;
-        vreg[j] = __floats2half2_rn(0.f, 0.f);
-        if (g < Gp && t < pos) vreg[j] = __ldcg(reinterpret_cast<const __half2*>(vc + (size_t)t * a.kv_dim) + dp);
+    for (int j = 0; j < NV; j++) {
+        const int t = w + j * MK_NW;
+        vreg[j] = make_uint2(0u, 0u);
+        if (t < pos) vreg[j] = ldcg_v<VPL>(vc + (size_t)t * a.kv_dim + lane * VPL);
     }
 
     // ---- gather q, new k, new v (HD values each); append the new row to the cache ----
@@ -1268,8 +1299,7 @@ __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int la
                                        : a.xkv + a.kv_dim + kvh * HD + d;
         float v0, v1;
         mk_poll2(c, src, tag_in, v0, v1);
-        c.xs()[i] = v0;
-        c.xs()[i + 1] = v1;
+        *reinterpret_cast<float2*>(c.xs() + i) = make_float2(v0, v1);
         // every CTA of the KV group appends the (identical) new row; each CTA later reads back
         // only addresses it has written itself
         if (which == 1) *reinterpret_cast<__half2*>(kc + (size_t)pos * a.kv_dim + d) = __floats2half2_rn(v0, v1);
@@ -1277,106 +1307,112 @@ __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int la
     }
     consumer_sync();
 
-    // ---- scores: thread t owns position t; the new position's K row comes from shared memory ----
-    const int len = pos + 1;
+    // ---- scores ----
     const float scale = rsqrtf((float)HD);
+    const uint32_t q_s = xs_s + (uint32_t)(qp * DPL) * 4u;
     float mx = -INFINITY;
-    if (tid == pos) {
 #pragma unroll
-        for (int i = 0; i < KV; i++) {
-            const float4 ka = reinterpret_cast<const float4*>(kn)[2 * i], kb = reinterpret_cast<const float4*>(kn)[2 * i + 1];
-            __half2 h[4] = {__floats2half2_rn(ka.x, ka.y), __floats2half2_rn(ka.z, ka.w), __floats2half2_rn(kb.x, kb.y),
-                            __floats2half2_rn(kb.z, kb.w)};      // exact: kn already holds fp16-rounded values
-            kreg[i] = *reinterpret_cast<const uint4*>(h);
+    for (int i = 0; i < NPRE; i++) {
+        const int t = u + i * UNITS;
+        if (i * UNITS <= pos) {                 // uniform
+            float dot = 0.f;
+            if (t == pos) {                     // the new position's K row sits in shared memory (already fp16-rounded values)
+                const float* kn = c.xs() + HD + qp * DPL;
+                const float* qq = c.xs() + qp * DPL;
+#pragma unroll
+                for (int d = 0; d < DPL; d++) dot = fmaf(qq[d], kn[d], dot);
+            } else {
+#pragma unroll
+                for (int j = 0; j < KV4; j++) dot += dot8_kq(kreg[i][j], q_s + j * 32);
+            }
+            dot += __shfl_xor_sync(MG_FULL_MASK, dot, 1);
+            dot += __shfl_xor_sync(MG_FULL_MASK, dot, 2);
+            dot *= scale;
+            if (t <= pos) { if (qp == 0) c.sc()[t] = dot; mx = fmaxf(mx, dot); }
         }
     }
-    if (tid <= pos) {
-        float dot = 0.f;
-#pragma unroll
-        for (int i = 0; i < KV; i++) dot += dot8_kq(kreg[i], qs + 8 * i);
-        dot *= scale;
-        c.sc()[tid] = dot;
-        mx = dot;
-    }
-    for (int t = tid + MK_CONSUMERS; t <= pos; t += MK_CONSUMERS) {     // contexts beyond one row per thread
+    for (int t0 = NPRE * UNITS; t0 <= pos; t0 += UNITS) {      // contexts beyond the registers: rows from L2
+        const int t = t0 + u;
         float dot = 0.f;
         if (t == pos) {
-            for (int d = 0; d < HD; d++) dot = fmaf(qs[d], kn[d], dot);
-        } else {
-            const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)t * a.kv_dim);
-            uint4 kk[KV];
+            const float* kn = c.xs() + HD + qp * DPL;
+            const float* qq = c.xs() + qp * DPL;
 #pragma unroll
-            for (int i = 0; i < KV; i++) kk[i] = __ldcg(kp + i);
+            for (int d = 0; d < DPL; d++) dot = fmaf(qq[d], kn[d], dot);
+        } else if (t < pos) {
+            const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)t * a.kv_dim + qp * DPL);
+            uint4 kk[KV4];
 #pragma unroll
-            for (int i = 0; i < KV; i++) dot += dot8_kq(kk[i], qs + 8 * i);
+            for (int j = 0; j < KV4; j++) kk[j] = __ldcg(kp + j);
+#pragma unroll
+            for (int j = 0; j < KV4; j++) dot += dot8_kq(kk[j], q_s + j * 32);
         }
+        dot += __shfl_xor_sync(MG_FULL_MASK, dot, 1);
+        dot += __shfl_xor_sync(MG_FULL_MASK, dot, 2);
         dot *= scale;
-        c.sc()[t] = dot;
-        mx = fmaxf(mx, dot);
+        if (t <= pos) { if (qp == 0) c.sc()[t] = dot; mx = fmaxf(mx, dot); }
     }
     mx = warp_max(mx);
-    const int lane = tid & 31, w = tid >> 5;
     if (lane == 0) c.red()[32 + w] = mx;
     consumer_sync();
-    mx = c.red()[32];
-#pragma unroll
-    for (int i = 1; i < MK_NW; i++) mx = fmaxf(mx, c.red()[32 + i]);
-    float sum = 0.f;
-    for (int t = tid; t < len; t += MK_CONSUMERS) {
-        const float pv = expf(c.sc()[t] - mx);
-        c.sc()[t] = pv;
-        sum += pv;
+    {
+        const uint32_t rr = smem_u32(mk_smem) + c.part_off + (uint32_t)(MK_PART_FLOATS + 32) * 4u;
+        const float4 m0 = lds128f(rr), m1 = lds128f(rr + 16), m2 = lds128f(rr + 32), m3 = lds128f(rr + 48);
+        mx = fmaxf(fmaxf(fmaxf(m0.x, m0.y), fmaxf(m0.z, m0.w)), fmaxf(fmaxf(m1.x, m1.y), fmaxf(m1.z, m1.w)));
+        mx = fmaxf(mx, fmaxf(fmaxf(fmaxf(m2.x, m2.y), fmaxf(m2.z, m2.w)), fmaxf(fmaxf(m3.x, m3.y), m3.z)));   // 15 warps
     }
-    sum = mk_block_sum(c, sum);      // barrier publishes sc[]
 
-    // ---- weighted V ----
-    if (g < Gp) {
-        float2 acc = make_float2(0.f, 0.f);
+    // ---- P . V ----
+    float acc[VPL];
 #pragma unroll
-        for (int j = 0; j < MK_VPF; j++) {
-            const int t = g + j * Gp;
-            if (t < pos) {
-                const float2 vf = __half22float2(vreg[j]);
-                const float pv = c.sc()[t];
-                acc.x = fmaf(pv, vf.x, acc.x);
-                acc.y = fmaf(pv, vf.y, acc.y);
-            }
-        }
-        for (int t0 = g + MK_VPF * Gp; t0 < pos; t0 += 4 * Gp) {        // remainder, four loads in flight
-            __half2 vv[4];
+    for (int e = 0; e < VPL; e++) acc[e] = 0.f;
+    float lsum = 0.f;
+    const bool vlane = VPL > 1 || true;
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int t = t0 + j * Gp;
-                vv[j] = __floats2half2_rn(0.f, 0.f);
-                if (t < pos) vv[j] = __ldcg(reinterpret_cast<const __half2*>(vc + (size_t)t * a.kv_dim) + dp);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int t = t0 + j * Gp;
-                if (t < pos) {
-                    const float2 vf = __half22float2(vv[j]);
-                    const float pv = c.sc()[t];
-                    acc.x = fmaf(pv, vf.x, acc.x);
-                    acc.y = fmaf(pv, vf.y, acc.y);
-                }
-            }
+    for (int j = 0; j < NV; j++) {
+        const int t = w + j * MK_NW;
+        if (t < pos) {                           // uniform over the warp
+            const float p = (a.dbg & 2) ? expf(c.sc()[t] - mx) : __expf(c.sc()[t] - mx);
+            lsum += p;
+            fma_v<VPL>(acc, p, vreg[j]);
         }
-        if (g == pos % Gp) {                                             // the new position belongs to one group
-            const float pv = c.sc()[pos];
-            acc.x = fmaf(pv, vn[2 * dp], acc.x);
-            acc.y = fmaf(pv, vn[2 * dp + 1], acc.y);
-        }
-        c.part()[g * HD + 2 * dp] = acc.x;
-        c.part()[g * HD + 2 * dp + 1] = acc.y;
     }
+    for (int t0 = w + NV * MK_NW; t0 < pos; t0 += 4 * MK_NW) {   // remainder, four loads in flight
+        uint2 vv[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int t = t0 + j * MK_NW;
+            vv[j] = make_uint2(0u, 0u);
+            if (t < pos) vv[j] = ldcg_v<VPL>(vc + (size_t)t * a.kv_dim + lane * VPL);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int t = t0 + j * MK_NW;
+            if (t < pos) {
+                const float p = __expf(c.sc()[t] - mx);
+                lsum += p;
+                fma_v<VPL>(acc, p, vv[j]);
+            }
+        }
+    }
+    if (w == pos % MK_NW) {                                       // the new position belongs to one warp
+        const float p = (a.dbg & 2) ? expf(c.sc()[pos] - mx) : __expf(c.sc()[pos] - mx);
+        lsum += p;
+        const float* vn = c.xs() + 2 * HD + lane * VPL;
+#pragma unroll
+        for (int e = 0; e < VPL; e++) acc[e] = fmaf(p, vn[e], acc[e]);
+    }
+    (void)vlane;
+#pragma unroll
+    for (int e = 0; e < VPL; e++) c.part()[w * HD + lane * VPL + e] = acc[e];
+    if (lane == 0) c.red()[48 + w] = lsum;
     consumer_sync();
     if (tid < HD) {
-        float s = 0.f;
-#pragma unroll 1
-        for (int gg = 0; gg < Gp; gg++) s += c.part()[gg * HD + tid];
-        st_tagged(a.xattn + head * HD + tid, s / sum, tag_out);
+        float s = 0.f, l = 0.f;
+#pragma unroll
+        for (int gg = 0; gg < MK_NW; gg++) { s += c.part()[gg * HD + tid]; l += c.red()[48 + gg]; }
+        st_tagged(a.xattn + head * HD + tid, (a.dbg & 2) ? s / l : __fdividef(s, l), tag_out);
     }
-    consumer_sync();     // part / xs are reused by the next phase
 }
 
 // ---------------------------------------------------------------------

@@ -301,6 +301,11 @@ class CUDAFusedInference:
         self._check(self._lib.mg_trace_step(self._h, _np_ptr(buf), cap, C.byref(n_ctas), C.byref(n_ev)), "TraceStep")
         return buf[: n_ctas.value * n_ev.value].reshape(n_ctas.value, n_ev.value)
 
+    def SetWaitLimit(self, ms: int) -> None:
+        """Limit of every wait inside the persistent kernel; a wait that runs out makes the step
+        raise with MG_ERR_TIMEOUT (the reference's WaitMailbox spins without one)."""
+        self._check(self._lib.mg_set_wait_limit_ms(self._h, int(ms)), "SetWaitLimit")
+
     @property
     def stream(self) -> int:
         return self._lib.mg_stream(self._h) or 0

@@ -83,6 +83,23 @@ def test_mailbox_times_out_when_nothing_was_queued(cuda, mglib):
         eng.close()
 
 
+def test_mailbox_survives_the_sender(cuda, mglib):
+    """The receiving stage waits on its own event: the sender may be gone by the time it asks."""
+    cfg = mc.TINY
+    a, b = CUDAFusedInference(cfg), CUDAFusedInference(cfg)
+    try:
+        fill_models(cfg, seed=2, jitter=0.1, engine=a)
+        h = np.random.default_rng(5).standard_normal(cfg.dim).astype(np.float32)
+        a.PartialStep(h, 0, 0, 1)
+        a.QueueHiddenTo(b)
+        want = a.ExportHidden()
+        a.close()
+        b.WaitMailbox(1000)
+        assert np.array_equal(b.ExportHidden(), want)
+    finally:
+        a.close(); b.close()
+
+
 def test_l3_bridge_returns_the_hidden_state(cuda, oracle, mglib):
     cfg = mc.TINY
     eng, om = CUDAFusedInference(cfg), oracle.OracleModel(cfg)
