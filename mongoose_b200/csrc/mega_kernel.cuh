@@ -332,6 +332,7 @@ struct MkCtx {
     // byte offsets of the regions inside mk_smem, fixed for the launch
     uint32_t xs_off, hs_off, part_off, bar_off;
     int redsel;                   // which half of the RMS partial-sum buffer the current phase uses (0 / 16)
+    int probe_base;               // profiling build: trace slot base of the phase being probed (-1: none)
     __device__ __forceinline__ MkCtx(const MegaArgs& args) : a(args), entry(0), slot(0), par(0), pf(0), redsel(0) {
         xs_off = (uint32_t)a.nslot * (uint32_t)a.slot_bytes;
         hs_off = xs_off + 4u * (uint32_t)a.xs_floats;
@@ -375,7 +376,11 @@ __device__ __forceinline__ void mk_fail(MkCtx& c, int code, int where) {
     mk_fail_impl(c.abort_flag(), c.status(), code, where);
 }
 
+#ifdef MK_PROBE_P
+constexpr int MK_EV = 64;
+#else
 constexpr int MK_EV = 32;             // trace events per layer
+#endif
 #define MK_TRACE_EVENTS(L) (((L) + 1) * MK_EV)
 __device__ __forceinline__ void mk_trace(const MegaArgs& a, int step, int ev) {
     if (a.trace && step == 0 && threadIdx.x == 0)
@@ -387,7 +392,7 @@ __device__ __forceinline__ void mk_trace(const MegaArgs& a, int step, int ev) {
 // instructions each to the code a phase runs through (the kernel's speed is bounded by the length
 // of the instruction stream of a phase as much as by its data).  All waits are bounded.
 __device__ __noinline__ void mk_wait_bar_slow(volatile int* abort_flag, MegaStatus* status, long long limit,
-                                              uint32_t bar_s, uint32_t parity, int code, int where) {
+                                              uint32_t bar_s, uint32_t parity, int code, int where, unsigned sleep_ns) {
     if (*abort_flag) return;
     const long long t0 = global_ns();
     for (unsigned int it = 1;; ++it) {
@@ -400,7 +405,7 @@ __device__ __noinline__ void mk_wait_bar_slow(volatile int* abort_flag, MegaStat
         if (ok) return;
         // a spinning try_wait occupies the shared-memory pipe that the working warps' loads and shuffles
         // go through: back off between attempts (longer for the producer, which runs a ring ahead)
-        __nanosleep(code == MK_ERR_EMPTY ? 400u : 40u);
+        if (sleep_ns) __nanosleep(sleep_ns);
         if ((it & 63u) == 0u) {
             if (*abort_flag) return;
             if (*(volatile int*)&status->error) { *abort_flag = 1; return; }
@@ -410,7 +415,8 @@ __device__ __noinline__ void mk_wait_bar_slow(volatile int* abort_flag, MegaStat
 }
 __device__ __forceinline__ void mk_wait_bar(MkCtx& c, unsigned long long* bar, uint32_t parity, int code) {
     if (mbar_try(bar, parity)) return;
-    mk_wait_bar_slow(c.abort_flag(), c.status(), c.a.wait_cycles, smem_u32(bar), parity, code, (int)c.entry);
+    mk_wait_bar_slow(c.abort_flag(), c.status(), c.a.wait_cycles, smem_u32(bar), parity, code, (int)c.entry,
+                     code == MK_ERR_EMPTY ? (unsigned)(c.a.dbg >> 8) : 0u);
 }
 
 // Re-read a pair of exchange words (16-byte aligned) until both carry `tag`; sys = the words may be
@@ -488,64 +494,17 @@ __device__ __forceinline__ void mk_poll2_sum(MkCtx& c, const Tagged* p, int stri
 // of the block's largest element per term.
 //
 // Shared-memory layout (at xs), chosen so that the B operand of the MMA is one
-// 8-byte load per lane: blocks are kept in pairs of 192 bytes,
-//   pair j: plane 0 of block 2j | plane 0 of block 2j+1 | plane 1 of 2j | plane 1 of 2j+1 | plane 2 ...
-// and inside a 32-byte plane element e = 16h + 4t + b sits at byte 8t + 4h + b
-// (lane t of an MMA quad reads its two k-quads, columns 4t.. and 16+4t.., as
-// one 8-byte word).  After the planes: one float2 {s, -8 s sum(T)} per block
-// (the second half only for 4-bit weights: their stored nibbles carry a +8 offset).
+// 8-byte load per lane: 96 bytes per block, plane 0 | plane 1 | plane 2, and inside a
+// 32-byte plane element e = 16h + 4t + b sits at byte 8t + 4h + b (lane t of an MMA quad
+// reads its two k-quads, columns 4t.. and 16+4t.., as one 8-byte word).  After the planes
+// (one spare block, so that a tile of two blocks may begin at the last block of an odd
+// count): one float2 {s, -8 s sum(T)} per block (the second half only for 4-bit weights:
+// their stored nibbles carry a +8 offset).
 // ---------------------------------------------------------------------
-__device__ __forceinline__ uint8_t* xq_base(MkCtx& c) { return reinterpret_cast<uint8_t*>(c.xs()); }
-__host__ __device__ inline int xq_plane_bytes(int K) { return ((K + 63) >> 6) * 192; }
-__device__ __forceinline__ float2* xq_scales(MkCtx& c, int K) {
-    return reinterpret_cast<float2*>(xq_base(c) + xq_plane_bytes(K));
-}
+__host__ __device__ inline int xq_plane_bytes(int K) { return ((K >> 5) + 1) * 96; }
 // Bytes of the staged-activation buffer a phase with input width K needs.
 __host__ __device__ inline int xs_bytes_of(int fmt, int K) {
     return fmt == FMT_F16 ? K * 4 : xq_plane_bytes(K) + ((K >> 5) + 2) * 8;
-}
-
-// All 32 lanes call; lanes 16j..16j+15 hold the 32 values of one block (u0, u1 = elements i, i+1).
-// `want_sum`: the block's sum(T) is only needed by 4-bit weights.
-__device__ __forceinline__ void xq_store_pair(MkCtx& c, int K, int i, bool ok, float u0, float u1, bool want_sum) {
-    float m = fmaxf(fabsf(u0), fabsf(u1));
-    m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 1));
-    m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 2));
-    m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 4));
-    m = fmaxf(m, __shfl_xor_sync(MG_FULL_MASK, m, 8));
-    // an approximate reciprocal is enough: the value represented is T * (m / 8355709); the factor is two
-    // below the largest three-digit T so that neither the reciprocal's nor the product's rounding can
-    // carry |T| past 8355711
-    const float inv = m > 0.f ? 8355709.0f * __frcp_rn(m) : 0.f;
-    const int t0 = __float2int_rn(u0 * inv);
-    const int t1 = __float2int_rn(u1 * inv);
-    int ts = 0;
-    if (want_sum) {
-        ts = t0 + t1;
-        ts += __shfl_xor_sync(MG_FULL_MASK, ts, 1);
-        ts += __shfl_xor_sync(MG_FULL_MASK, ts, 2);
-        ts += __shfl_xor_sync(MG_FULL_MASK, ts, 4);
-        ts += __shfl_xor_sync(MG_FULL_MASK, ts, 8);
-    }
-    if (ok) {
-        // signed digits: a0 = sext(T & 255), a1 = sext(((T + 128) >> 8) & 255), a2 = ((T + 128) >> 8) + 128 >> 8
-        const int p1a = (t0 + 128) >> 8, p1b = (t1 + 128) >> 8;
-        const int p2a = (p1a + 128) >> 8, p2b = (p1b + 128) >> 8;
-        const int kb = i >> 5, j = i & 31;
-        uint8_t* dst = xq_base(c) + (kb >> 1) * 192 + (kb & 1) * 32 + ((j & 15) >> 2) * 8 + (j >> 4) * 4 + (j & 3);
-        *reinterpret_cast<unsigned short*>(dst) = (unsigned short)((t0 & 0xff) | ((t1 & 0xff) << 8));
-        *reinterpret_cast<unsigned short*>(dst + 64) = (unsigned short)((p1a & 0xff) | ((p1b & 0xff) << 8));
-        *reinterpret_cast<unsigned short*>(dst + 128) = (unsigned short)((p2a & 0xff) | ((p2b & 0xff) << 8));
-        if ((threadIdx.x & 15) == 0) {
-            const float sc = m * (1.0f / 8355709.0f);
-            xq_scales(c, K)[kb] = make_float2(sc, -8.0f * sc * (float)ts);
-        }
-    }
-}
-// An odd number of blocks leaves the second half of the last pair unwritten: wide tiles read its
-// scale (against all-zero weights), so it must be a finite number.
-__device__ __forceinline__ void xq_pad(MkCtx& c, int K) {
-    if (((K >> 5) & 1) && threadIdx.x == 0) xq_scales(c, K)[K >> 5] = make_float2(0.f, 0.f);
 }
 
 // Poll n tagged values into shared memory dst[0..n) (n even).  All consumer threads call.
@@ -775,7 +734,7 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
 struct LaneGeom {
     uint32_t a_off;     // this lane's offset inside a tile's A bytes
     uint32_t d_off;     // offset of its pair of block scales inside the tile
-    uint32_t b_addr;    // its B word in block pair 0 (fp16 weights: its float4 of x in block 0)
+    uint32_t b_addr;    // its B word in block 0 (fp16 weights: its float4 of x in block 0)
     uint32_t s_addr;    // float2 {s, -8 s sum T} of block 0
     bool bvalid;        // lane supplies a plane column (others supply zeros)
     int t;
@@ -793,20 +752,22 @@ __device__ __forceinline__ LaneGeom lane_geom(const MkCtx& c, int lane, int wide
         L.a_off = FMT == FMT_Q8_0 ? lane * 16 : lane * 8;
         L.d_off = (FMT == FMT_Q8_0 ? 512 : 256) + g * 4;
         L.bvalid = g < 6 && (wide || (g & 1) == 0);
-        L.b_addr = xs + (g >> 1) * 64 + (wide ? (g & 1) * 32 : 0) + t * 8;
+        L.b_addr = xs + (g >> 1) * 32 + (wide ? (g & 1) * 96 : 0) + t * 8;
         L.s_addr = xs + xq_plane_bytes(K);
     }
     return L;
 }
 
-template <int FMT>
-__device__ __forceinline__ void tile_mac(uint32_t tile, int kt, int wide, const LaneGeom& L, float& acc0, float& acc1) {
+// One tile: `tile` = its ring address, bp = this lane's B word of the tile's (first) block, sp = the
+// block's scale pair.  Per tile a lane issues four shared-memory loads, the MMA, two conversions of
+// each kind and four multiply-adds; all addresses are kept as running pointers by the caller.
+template <int FMT, bool WIDE>
+__device__ __forceinline__ void tile_mac(uint32_t tile, uint32_t bp, uint32_t sp, const LaneGeom& L, float& acc0, float& acc1) {
     if (FMT == FMT_F16) {
         // 16 row-slots x 16 columns of halves: lane (g, t) holds columns 4t..4t+3 of slots g and g + 8
         const uint4 A = lds128(tile + L.a_off);
-        const uint32_t xa = L.b_addr + (wide ? 2 * kt : kt) * 64;
-        const float4 xe = lds128f(xa);
-        const float4 xo = wide ? lds128f(xa + 64) : xe;
+        const float4 xe = lds128f(bp);
+        const float4 xo = WIDE ? lds128f(bp + 64) : xe;
         const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&A.x));
         const float2 a1 = __half22float2(*reinterpret_cast<const __half2*>(&A.y));
         const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&A.z));
@@ -817,11 +778,11 @@ __device__ __forceinline__ void tile_mac(uint32_t tile, int kt, int wide, const 
         acc1 = fmaf(b1.x, xo.z, acc1); acc1 = fmaf(b1.y, xo.w, acc1);
         return;
     }
-    const int kb = wide ? 2 * kt : kt;                      // (even) block of the tile
     uint2 B = make_uint2(0u, 0u);
-    if (L.bvalid) B = lds64(L.b_addr + (kb >> 1) * 192 + (wide ? 0 : (kb & 1) * 32));
-    const float2 se = lds64f(L.s_addr + kb * 8);
-    const float2 so = wide ? lds64f(L.s_addr + kb * 8 + 8) : se;
+    if (L.bvalid) B = lds64(bp);
+    float4 sc;                                                // {s, off} of the even block, {s, off} of the odd one
+    if (WIDE) sc = lds128f(sp);
+    else { const float2 s1 = lds64f(sp); sc = make_float4(s1.x, s1.y, s1.x, s1.y); }
     const uint32_t dd = lds32(tile + L.d_off);
     int d[4];
     if (FMT == FMT_Q8_0) {
@@ -833,17 +794,71 @@ __device__ __forceinline__ void tile_mac(uint32_t tile, int kt, int wide, const 
         mma_u8s8(d, A.x & 0x0f0f0f0fu, A.y & 0x0f0f0f0fu, (A.x >> 4) & 0x0f0f0f0fu, (A.y >> 4) & 0x0f0f0f0fu, B);
     }
     const float2 df = __half22float2(*reinterpret_cast<const __half2*>(&dd));    // scales of slots g, g + 8
-    const float c0 = (float)d[0];
-    const float c1 = (float)(wide ? d[3] : d[2]);
+    // int -> float without the (slow) conversion pipe: |sum| <= 32 * 128 * 127 < 2^22, so adding the integer to
+    // the bit pattern of 1.5 * 2^23 and subtracting that constant is exact
+    const float c0 = __int_as_float(d[0] + 0x4B400000) - 12582912.0f;
+    const float c1 = __int_as_float((WIDE ? d[3] : d[2]) + 0x4B400000) - 12582912.0f;
     if (FMT == FMT_Q8_0) {
-        acc0 = fmaf(df.x * se.x, c0, acc0);
-        acc1 = fmaf(df.y * so.x, c1, acc1);
+        acc0 = fmaf(df.x * sc.x, c0, acc0);
+        acc1 = fmaf(df.y * sc.z, c1, acc1);
     } else {
         // sum (nib - 8) x = sum nib x - 8 sum x; the correction rides in the lanes of plane 0
-        const float oe = L.t == 0 ? se.y : 0.f, oo = L.t == 0 ? so.y : 0.f;
-        acc0 = fmaf(df.x, fmaf(se.x, c0, oe), acc0);
-        acc1 = fmaf(df.y, fmaf(so.x, c1, oo), acc1);
+        const float oe = L.t == 0 ? sc.y : 0.f, oo = L.t == 0 ? sc.w : 0.f;
+        acc0 = fmaf(df.x, fmaf(sc.x, c0, oe), acc0);
+        acc1 = fmaf(df.y, fmaf(sc.z, c1, oo), acc1);
     }
+}
+
+// The tiles of one pass for this warp: ring entries in order, whole rounds per entry, then the
+// incomplete last round.  Every warp observes and releases every entry, also those it has no tile
+// in (a warp that skipped ahead could meet a slot whose barrier is a whole ring revolution behind
+// and take the stale phase for its own).
+#ifdef MK_PROBE_P
+#define MK_SET_PROBE(B) c.probe_base = (MK_PROBE_P == 5 ? (B) : -1)
+#define MK_ESTAMP(EV) do { if (a.trace && threadIdx.x == 0 && c.probe_base >= 0) a.trace[(size_t)blockIdx.x * MK_TRACE_EVENTS(a.n_layers) + c.probe_base + (EV)] = clock64(); } while (0)
+#else
+#define MK_SET_PROBE(B) do { } while (0)
+#define MK_ESTAMP(EV) do { } while (0)
+#endif
+template <int FMT, bool WIDE>
+__device__ __forceinline__ void mk_pass_tiles(const MegaArgs& a, MkCtx& c, const LaneGeom& L, bool act, int S, int kp, int nfull,
+                                              int rem, int R, uint32_t woff, uint32_t wrem, uint32_t rstride, float& acc0,
+                                              float& acc1) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t sm0 = smem_u32(mk_smem);
+    // running pointers of this warp's next tile: B word and scale pair advance S k-tiles per round
+    constexpr uint32_t kBStep = FMT == FMT_F16 ? (WIDE ? 128u : 64u) : (WIDE ? 192u : 96u);
+    constexpr uint32_t kSStep = WIDE ? 16u : 8u;
+    uint32_t bp = L.b_addr + (uint32_t)kp * kBStep, sp = L.s_addr + (uint32_t)kp * kSStep;
+    const uint32_t bstep = (uint32_t)S * kBStep, sstep = (uint32_t)S * kSStep;
+    float acc2 = 0.f, acc3 = 0.f;
+    for (int r0 = 0; r0 < nfull; r0 += R) {
+        const int rounds = min(R, nfull - r0);
+        mk_wait_bar(c, &c.full()[c.slot], c.par, MK_ERR_FULL);
+        MK_ESTAMP(32 + 2 * (r0 / R));
+        if (act) {
+            uint32_t tile = sm0 + (uint32_t)c.slot * (uint32_t)a.slot_bytes + woff;
+            int rr = 0;
+            for (; rr + 2 <= rounds; rr += 2) {                // two independent tiles in flight
+                tile_mac<FMT, WIDE>(tile, bp, sp, L, acc0, acc1);
+                tile_mac<FMT, WIDE>(tile + rstride, bp + bstep, sp + sstep, L, acc2, acc3);
+                tile += 2 * rstride; bp += 2 * bstep; sp += 2 * sstep;
+            }
+            if (rr < rounds) { tile_mac<FMT, WIDE>(tile, bp, sp, L, acc0, acc1); bp += bstep; sp += sstep; }
+        }
+        MK_ESTAMP(33 + 2 * (r0 / R));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&c.empty()[c.slot]);
+        c.advance();
+    }
+    if (rem) {                                                 // the incomplete last round: an entry of its own
+        mk_wait_bar(c, &c.full()[c.slot], c.par, MK_ERR_FULL);
+        if (act && kp < rem) tile_mac<FMT, WIDE>(sm0 + (uint32_t)c.slot * (uint32_t)a.slot_bytes + wrem, bp, sp, L, acc2, acc3);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&c.empty()[c.slot]);
+        c.advance();
+    }
+    acc0 += acc2; acc1 += acc3;
 }
 
 // ---------------------------------------------------------------------
@@ -879,8 +894,8 @@ __device__ __forceinline__ void xq_store_fast(uint32_t dst, uint32_t sc_addr, bo
     if (ok) {
         // signed digits a0 = byte 0 of T, a1 = byte 1 of T + 128, a2 = byte 2 of T + 128 + 32768
         sts16(dst, __byte_perm((unsigned)t0, (unsigned)t1, 0x0040));
-        sts16(dst + 64, __byte_perm((unsigned)(t0 + 128), (unsigned)(t1 + 128), 0x0051));
-        sts16(dst + 128, __byte_perm((unsigned)(t0 + 32896), (unsigned)(t1 + 32896), 0x0062));
+        sts16(dst + 32, __byte_perm((unsigned)(t0 + 128), (unsigned)(t1 + 128), 0x0051));
+        sts16(dst + 64, __byte_perm((unsigned)(t0 + 32896), (unsigned)(t1 + 32896), 0x0062));
         if (lead) {
             const float sc = m > 1e-30f ? m * (1.0f / 8355709.0f) : 0.f;
             asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(sc_addr), "f"(sc), "f"(-8.0f * sc * (float)ts));
@@ -943,29 +958,39 @@ __device__ __forceinline__ void stage_issue(const MegaArgs& a, const StageSrc& s
 
 // Completes the loads of NS strides, stages them; ss accumulates the squares of a hidden state.
 // st_dst / st_sc: staging addresses of this thread's stride-0 pair; stride number kk0 + k.
+// Three straight passes - complete the polls (the only place with calls and branches), residual and
+// norm weight, fixed point - so that the shuffle and conversion chains of the NS strides overlap.
 template <int NS, int FMT, bool NORMED, bool TP>
 __device__ __forceinline__ void stage_finish(const MegaArgs& a, MkCtx& c, const StageSrc& s, int i0, int kk0, uint4 (&r)[NS],
                                              float2 (&nw)[NS], uint32_t st_dst, uint32_t st_sc, float& ss) {
     const int tid = threadIdx.x;
+    float v0[NS], v1[NS];
 #pragma unroll
     for (int k = 0; k < NS; k++) {
         const int i = i0 + k * MK_STRIDE + 2 * tid;
-        const bool ok = i < s.n;
-        float v0 = 0.f, v1 = 0.f;
-        if (ok) {
-            if (TP && NORMED && s.kind == SRC_POLL) mk_poll2_sum(c, s.src + i, a.dim, a.tp_n, s.tag, v0, v1);
-            else { mk_poll2_finish(c, s.src + i, s.tag, r[k]); v0 = __uint_as_float(r[k].x); v1 = __uint_as_float(r[k].z); }
-            if (NORMED) {
-                *reinterpret_cast<float2*>(c.hs() + i) = make_float2(v0, v1);
-                ss = fmaf(v0, v0, ss);
-                ss = fmaf(v1, v1, ss);
-                v0 *= nw[k].x; v1 *= nw[k].y;
-            }
+        v0[k] = 0.f; v1[k] = 0.f;
+        if (i < s.n) {
+            if (TP && NORMED && s.kind == SRC_POLL) mk_poll2_sum(c, s.src + i, a.dim, a.tp_n, s.tag, v0[k], v1[k]);
+            else { mk_poll2_finish(c, s.src + i, s.tag, r[k]); v0[k] = __uint_as_float(r[k].x); v1[k] = __uint_as_float(r[k].z); }
         }
-        if (FMT != FMT_F16) {
-            if (NS == 1 || i0 + k * MK_STRIDE < s.n)         // (uniform) strides wholly beyond the vector need no shuffles
-                xq_store_fast(st_dst + 2880u * (kk0 + k), st_sc + 240u * (kk0 + k), ok, (tid & 15) == 0, v0, v1, FMT == FMT_Q4_0);
-        } else if (ok) *reinterpret_cast<float2*>(c.xs() + i) = make_float2(v0, v1);
+    }
+#pragma unroll
+    for (int k = 0; k < NS; k++) {
+        const int i = i0 + k * MK_STRIDE + 2 * tid;
+        if (NORMED) {
+            if (i < s.n) *reinterpret_cast<float2*>(c.hs() + i) = make_float2(v0[k], v1[k]);
+            ss = fmaf(v0[k], v0[k], ss);
+            ss = fmaf(v1[k], v1[k], ss);
+            v0[k] *= nw[k].x; v1[k] *= nw[k].y;
+        }
+        if (FMT == FMT_F16 && i < s.n) *reinterpret_cast<float2*>(c.xs() + i) = make_float2(v0[k], v1[k]);
+    }
+    if (FMT != FMT_F16) {
+#pragma unroll
+        for (int k = 0; k < NS; k++) {
+            const int i = i0 + k * MK_STRIDE + 2 * tid;
+            xq_store_fast(st_dst + 2880u * (kk0 + k), st_sc + 240u * (kk0 + k), i < s.n, (tid & 15) == 0, v0[k], v1[k], FMT == FMT_Q4_0);
+        }
     }
 }
 
@@ -1014,9 +1039,8 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
     const int sp = S == 1 ? 1 : (S + 3) & ~3;                // splits per slot as stored
     const uint32_t part_s = sm0 + c.part_off;
     const int lim = P == PH_QKV ? (a.q_dim + 2 * a.kv_dim) / 2 : P == PH_GU ? a.ffn_dim : P == PH_HEAD ? a.vocab : a.dim;
-    // staging addresses of this thread's first pair (element 2 tid); stride k adds 15 block pairs
-    const uint32_t st_dst = sm0 + c.xs_off + (uint32_t)((tid >> 5) * 192 + ((tid >> 4) & 1) * 32 + ((tid & 7) >> 1) * 8 +
-                                                        ((tid >> 3) & 1) * 4 + (tid & 1) * 2);
+    // staging addresses of this thread's first pair (element 2 tid); stride k adds 30 blocks
+    const uint32_t st_dst = sm0 + c.xs_off + (uint32_t)((tid >> 4) * 96 + ((tid & 7) >> 1) * 8 + ((tid >> 3) & 1) * 4 + (tid & 1) * 2);
     const uint32_t st_sc = sm0 + c.xs_off + (uint32_t)xq_plane_bytes(s.n) + (uint32_t)(tid >> 4) * 8u;
     // epilogue of the (single) row-slot this thread finishes, for the phases that fit one round
     const int nslots = nrg * 16;
@@ -1089,44 +1113,24 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
     MK_STAMP(26);
 
     // ---- 3. tiles ----
+#ifdef MK_PROBE_P
+    c.probe_base = P == MK_PROBE_P ? trace_base : -1;
+#endif
     for (int rg0 = 0; rg0 < nrg; rg0 += RS) {
         const int nrs = min(RS, nrg - rg0);
         const int step = nrs * S;
         const int R = rounds_per_entry(g.tpe, step);
         const bool act = rs < nrs;
-        const uint32_t rstride = (uint32_t)(step * tile_bytes);
-        const uint32_t woff = (uint32_t)((rs * S + kp) * tile_bytes);
-        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-        int kt = kp;
-        for (int r0 = 0; r0 < g.nfull; r0 += R) {
-            const int rounds = min(R, g.nfull - r0);
-            mk_wait_bar(c, &c.full()[c.slot], c.par, MK_ERR_FULL);
-            if (act) {
-                uint32_t tile = sm0 + (uint32_t)c.slot * (uint32_t)a.slot_bytes + woff;
-                int rr = 0;
-                for (; rr + 2 <= rounds; rr += 2, tile += 2 * rstride, kt += 2 * S) {     // two independent tiles in flight
-                    tile_mac<FMT>(tile, kt, wide, L, acc0, acc1);
-                    tile_mac<FMT>(tile + rstride, kt + S, wide, L, acc2, acc3);
-                }
-                if (rr < rounds) { tile_mac<FMT>(tile, kt, wide, L, acc0, acc1); kt += S; }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&c.empty()[c.slot]);
-            c.advance();
-        }
         const int rem = nkt - g.nfull * S;
-        if (rem) {                                           // the incomplete last round: an entry of its own
-            mk_wait_bar(c, &c.full()[c.slot], c.par, MK_ERR_FULL);
-            if (act && kp < rem)
-                tile_mac<FMT>(sm0 + (uint32_t)c.slot * (uint32_t)a.slot_bytes + (uint32_t)((rs * rem + kp) * tile_bytes), kt, wide, L, acc0, acc1);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&c.empty()[c.slot]);
-            c.advance();
-        }
+        float acc0 = 0.f, acc1 = 0.f;
+        if (wide) mk_pass_tiles<FMT, true>(a, c, L, act, S, kp, g.nfull, rem, R, (uint32_t)((rs * S + kp) * tile_bytes),
+                                           (uint32_t)((rs * rem + kp) * tile_bytes), (uint32_t)(step * tile_bytes), acc0, acc1);
+        else mk_pass_tiles<FMT, false>(a, c, L, act, S, kp, g.nfull, rem, R, (uint32_t)((rs * S + kp) * tile_bytes),
+                                       (uint32_t)((rs * rem + kp) * tile_bytes), (uint32_t)(step * tile_bytes), acc0, acc1);
         MK_STAMP(27);
         if (act) {
             // quad sum: lanes t = 0..2 hold the three digit planes (fp16 weights: four column quarters)
-            acc0 = (acc0 + acc2) * wt; acc1 = (acc1 + acc3) * wt;
+            acc0 *= wt; acc1 *= wt;
             acc0 += __shfl_xor_sync(MG_FULL_MASK, acc0, 1); acc1 += __shfl_xor_sync(MG_FULL_MASK, acc1, 1);
             acc0 += __shfl_xor_sync(MG_FULL_MASK, acc0, 2); acc1 += __shfl_xor_sync(MG_FULL_MASK, acc1, 2);
             // lane t of a quad stores split kp + t: t = 0 the sum, the others the zero padding
@@ -1257,10 +1261,10 @@ __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int la
                                              unsigned int tag_out) {
     constexpr int DPL = HD / 4;                // dims per lane in the score phase
     constexpr int KV4 = DPL / 8;               // 16-byte pieces of K per lane and position
-    constexpr int NPRE = HD == 128 ? 2 : 4;    // positions per unit held in registers
-    constexpr int UNITS = MK_CONSUMERS / 4;    // 120
+    constexpr int NPRE = HD == 128 ? 2 : 4;    // score passes whose K rows are held in registers
+    constexpr int PPP = 8;                     // positions per warp and pass (four lanes each)
     constexpr int VPL = HD / 32;               // dims per lane in P . V
-    constexpr int NV = 16;                     // positions per warp held in registers
+    constexpr int NV = 16;                     // positions per warp whose V rows are held in registers
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int head = blockIdx.x;
     const int kvh = head / (a.n_heads / a.n_kv_heads);
@@ -1268,13 +1272,16 @@ __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int la
     __half* kc = a.kc + lbase + kvh * HD;
     __half* vc = a.vc + lbase + kvh * HD;
     const uint32_t xs_s = smem_u32(mk_smem) + c.xs_off;        // q | new k | new v, HD floats each
-    const int u = tid >> 2, qp = tid & 3;
+    const int uq = lane >> 2, qp = lane & 3;
+    // Warp w owns positions w, w + 15, w + 30, ...: it computes their scores AND their share of
+    // P . V, so the scores never leave the warp; pass i covers its positions number 8 i .. 8 i + 7.
+    const int t_first = w + MK_NW * uq;
 
     // ---- cached rows (positions < pos) into registers ----
     uint4 kreg[NPRE][KV4];
 #pragma unroll
     for (int i = 0; i < NPRE; i++) {
-        const int t = u + i * UNITS;
+        const int t = t_first + i * (MK_NW * PPP);
 #pragma unroll
         for (int j = 0; j < KV4; j++) kreg[i][j] = make_uint4(0u, 0u, 0u, 0u);
         if (t < pos) {
@@ -1290,6 +1297,7 @@ __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int la
         vreg[j] = make_uint2(0u, 0u);
         if (t < pos) vreg[j] = ldcg_v<VPL>(vc + (size_t)t * a.kv_dim + lane * VPL);
     }
+    MK_ESTAMP(40);
 
     // ---- gather q, new k, new v (HD values each); append the new row to the cache ----
     for (int i = 2 * tid; i < 3 * HD; i += 2 * MK_CONSUMERS) {
@@ -1306,76 +1314,83 @@ __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int la
         if (which == 2) *reinterpret_cast<__half2*>(vc + (size_t)pos * a.kv_dim + d) = __floats2half2_rn(v0, v1);
     }
     consumer_sync();
+    MK_ESTAMP(41);
 
-    // ---- scores ----
+    // ---- scores of this warp's positions ----
     const float scale = rsqrtf((float)HD);
     const uint32_t q_s = xs_s + (uint32_t)(qp * DPL) * 4u;
     float mx = -INFINITY;
+    const int npass = (pos - w + MK_NW * PPP) / (MK_NW * PPP);      // passes in which this warp has a position <= pos (w <= pos)
 #pragma unroll
     for (int i = 0; i < NPRE; i++) {
-        const int t = u + i * UNITS;
-        if (i * UNITS <= pos) {                 // uniform
-            float dot = 0.f;
-            if (t == pos) {                     // the new position's K row sits in shared memory (already fp16-rounded values)
+        if (i == 0 || (w <= pos && i < npass)) {                   // uniform over the warp
+            const int t = t_first + i * (MK_NW * PPP);
+            if (t == pos) {
+                // the new position's K row sits in shared memory (fp16-rounded values: the conversion is exact)
                 const float* kn = c.xs() + HD + qp * DPL;
-                const float* qq = c.xs() + qp * DPL;
 #pragma unroll
-                for (int d = 0; d < DPL; d++) dot = fmaf(qq[d], kn[d], dot);
-            } else {
+                for (int j = 0; j < KV4; j++) {
+                    __half2 h[4];
 #pragma unroll
-                for (int j = 0; j < KV4; j++) dot += dot8_kq(kreg[i][j], q_s + j * 32);
+                    for (int e = 0; e < 4; e++) h[e] = __floats2half2_rn(kn[8 * j + 2 * e], kn[8 * j + 2 * e + 1]);
+                    kreg[i][j] = *reinterpret_cast<const uint4*>(h);
+                }
             }
+            float dot = 0.f;
+#pragma unroll
+            for (int j = 0; j < KV4; j++) dot += dot8_kq(kreg[i][j], q_s + j * 32);
             dot += __shfl_xor_sync(MG_FULL_MASK, dot, 1);
             dot += __shfl_xor_sync(MG_FULL_MASK, dot, 2);
             dot *= scale;
             if (t <= pos) { if (qp == 0) c.sc()[t] = dot; mx = fmaxf(mx, dot); }
         }
     }
-    for (int t0 = NPRE * UNITS; t0 <= pos; t0 += UNITS) {      // contexts beyond the registers: rows from L2
-        const int t = t0 + u;
-        float dot = 0.f;
-        if (t == pos) {
-            const float* kn = c.xs() + HD + qp * DPL;
-            const float* qq = c.xs() + qp * DPL;
+    for (int i = NPRE; w <= pos && i < npass; i++) {              // contexts beyond the registers: rows from L2
+        const int t = t_first + i * (MK_NW * PPP);
+        uint4 kk[KV4];
 #pragma unroll
-            for (int d = 0; d < DPL; d++) dot = fmaf(qq[d], kn[d], dot);
-        } else if (t < pos) {
+        for (int j = 0; j < KV4; j++) kk[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (t < pos) {
             const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)t * a.kv_dim + qp * DPL);
-            uint4 kk[KV4];
 #pragma unroll
             for (int j = 0; j < KV4; j++) kk[j] = __ldcg(kp + j);
+        } else if (t == pos) {
+            const float* kn = c.xs() + HD + qp * DPL;
 #pragma unroll
-            for (int j = 0; j < KV4; j++) dot += dot8_kq(kk[j], q_s + j * 32);
+            for (int j = 0; j < KV4; j++) {
+                __half2 h[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) h[e] = __floats2half2_rn(kn[8 * j + 2 * e], kn[8 * j + 2 * e + 1]);
+                kk[j] = *reinterpret_cast<const uint4*>(h);
+            }
         }
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < KV4; j++) dot += dot8_kq(kk[j], q_s + j * 32);
         dot += __shfl_xor_sync(MG_FULL_MASK, dot, 1);
         dot += __shfl_xor_sync(MG_FULL_MASK, dot, 2);
         dot *= scale;
         if (t <= pos) { if (qp == 0) c.sc()[t] = dot; mx = fmaxf(mx, dot); }
     }
-    mx = warp_max(mx);
-    if (lane == 0) c.red()[32 + w] = mx;
-    consumer_sync();
-    {
-        const uint32_t rr = smem_u32(mk_smem) + c.part_off + (uint32_t)(MK_PART_FLOATS + 32) * 4u;
-        const float4 m0 = lds128f(rr), m1 = lds128f(rr + 16), m2 = lds128f(rr + 32), m3 = lds128f(rr + 48);
-        mx = fmaxf(fmaxf(fmaxf(m0.x, m0.y), fmaxf(m0.z, m0.w)), fmaxf(fmaxf(m1.x, m1.y), fmaxf(m1.z, m1.w)));
-        mx = fmaxf(mx, fmaxf(fmaxf(fmaxf(m2.x, m2.y), fmaxf(m2.z, m2.w)), fmaxf(fmaxf(m3.x, m3.y), m3.z)));   // 15 warps
-    }
+    mx = warp_max(mx);                       // -inf: the warp has no position
+    __syncwarp();                            // the scores in sc[] were written by lanes of this warp
+    MK_ESTAMP(42);
+    MK_ESTAMP(43);
 
-    // ---- P . V ----
+    // ---- this warp's share of P . V, relative to its own maximum ----
     float acc[VPL];
 #pragma unroll
     for (int e = 0; e < VPL; e++) acc[e] = 0.f;
     float lsum = 0.f;
-    const bool vlane = VPL > 1 || true;
+    const int last = max(pos - 1, 0);
 #pragma unroll
     for (int j = 0; j < NV; j++) {
         const int t = w + j * MK_NW;
-        if (t < pos) {                           // uniform over the warp
-            const float p = (a.dbg & 2) ? expf(c.sc()[t] - mx) : __expf(c.sc()[t] - mx);
-            lsum += p;
-            fma_v<VPL>(acc, p, vreg[j]);
-        }
+        // straight-line: positions beyond the context contribute p = 0 (their V registers hold zeros)
+        float p = __expf(c.sc()[min(t, last)] - mx);
+        p = t < pos ? p : 0.f;
+        lsum += p;
+        fma_v<VPL>(acc, p, vreg[j]);
     }
     for (int t0 = w + NV * MK_NW; t0 < pos; t0 += 4 * MK_NW) {   // remainder, four loads in flight
         uint2 vv[4];
@@ -1388,30 +1403,46 @@ __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int la
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int t = t0 + j * MK_NW;
-            if (t < pos) {
-                const float p = __expf(c.sc()[t] - mx);
-                lsum += p;
-                fma_v<VPL>(acc, p, vv[j]);
-            }
+            float p = __expf(c.sc()[min(t, last)] - mx);
+            p = t < pos ? p : 0.f;
+            lsum += p;
+            fma_v<VPL>(acc, p, vv[j]);
         }
     }
     if (w == pos % MK_NW) {                                       // the new position belongs to one warp
-        const float p = (a.dbg & 2) ? expf(c.sc()[pos] - mx) : __expf(c.sc()[pos] - mx);
+        const float p = __expf(c.sc()[pos] - mx);
         lsum += p;
         const float* vn = c.xs() + 2 * HD + lane * VPL;
 #pragma unroll
         for (int e = 0; e < VPL; e++) acc[e] = fmaf(p, vn[e], acc[e]);
     }
-    (void)vlane;
+    MK_ESTAMP(44);
 #pragma unroll
     for (int e = 0; e < VPL; e++) c.part()[w * HD + lane * VPL + e] = acc[e];
-    if (lane == 0) c.red()[48 + w] = lsum;
+    if (lane == 0) { c.red()[32 + w] = mx; c.red()[48 + w] = lsum; }
     consumer_sync();
+    MK_ESTAMP(45);
+    // ---- merge the warps' partial results: weights exp(m_w - M) ----
     if (tid < HD) {
-        float s = 0.f, l = 0.f;
+        const uint32_t rr = smem_u32(mk_smem) + c.part_off + (uint32_t)(MK_PART_FLOATS + 32) * 4u;
+        float m[16], l[16];
 #pragma unroll
-        for (int gg = 0; gg < MK_NW; gg++) { s += c.part()[gg * HD + tid]; l += c.red()[48 + gg]; }
-        st_tagged(a.xattn + head * HD + tid, (a.dbg & 2) ? s / l : __fdividef(s, l), tag_out);
+        for (int q = 0; q < 4; q++) {
+            const float4 mm = lds128f(rr + 16 * q), ll = lds128f(rr + 64 + 16 * q);
+            m[4 * q] = mm.x; m[4 * q + 1] = mm.y; m[4 * q + 2] = mm.z; m[4 * q + 3] = mm.w;
+            l[4 * q] = ll.x; l[4 * q + 1] = ll.y; l[4 * q + 2] = ll.z; l[4 * q + 3] = ll.w;
+        }
+        float M = m[0];
+#pragma unroll
+        for (int g = 1; g < MK_NW; g++) M = fmaxf(M, m[g]);
+        float s = 0.f, lt = 0.f;
+#pragma unroll
+        for (int g = 0; g < MK_NW; g++) {
+            const float f = __expf(m[g] - M);                  // 0 for a warp without positions (m = -inf)
+            s = fmaf(f, c.part()[g * HD + tid], s);
+            lt = fmaf(f, l[g], lt);
+        }
+        st_tagged(a.xattn + head * HD + tid, __fdividef(s, lt), tag_out);
     }
 }
 
@@ -1450,6 +1481,7 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
             if (l == a.ls) s0.kind = a.embed ? SRC_EMBED : SRC_PLAIN;                                              \
             mk_run_phase<PH_QKV, FMT, TP>(a, c, s0, l, base + 1, l * MK_EV, best);                                 \
             if ((int)blockIdx.x < a.n_heads) {                                                                     \
+                MK_SET_PROBE(l * MK_EV);                                                                           \
                 if (a.head_dim == 64) mk_attention<64>(a, c, l, pos, base + 1, base + 2);                          \
                 else if (a.head_dim == 128) mk_attention<128>(a, c, l, pos, base + 1, base + 2);                   \
                 else mk_attention<32>(a, c, l, pos, base + 1, base + 2);                                           \

@@ -295,7 +295,7 @@ class CUDAFusedInference:
 
     def TraceStep(self) -> np.ndarray:
         """SM-clock stamps [n_ctas, n_events] of one greedy step (see mg_trace_step)."""
-        cap = 256 * (self.cfg.n_layers + 1) * 32
+        cap = 256 * (self.cfg.n_layers + 1) * 64
         buf = np.zeros(cap, np.int64)
         n_ctas, n_ev = C.c_int(), C.c_int()
         self._check(self._lib.mg_trace_step(self._h, _np_ptr(buf), cap, C.byref(n_ctas), C.byref(n_ev)), "TraceStep")

@@ -110,16 +110,22 @@ def test_step_token_uses_tied_embedding(pair, oracle):
     for pos in range(4):
         nxt = eng.StepToken(tok, pos, logitsOut=logits)
         want = om.step_token(tok, pos)
-        # fp32 reassociation can carry a K or V value across an fp16 rounding boundary (one ulp = 5e-4 of
-        # that value, in the cache for good); with embedding-sized hidden states (|h| ~ 0.05) such a flip
-        # shows in the logits at the 1e-4 level.  The tight bound holds while the caches agree bit for bit.
-        flips = 0
+        # fp32 reassociation can carry a K or V value across an fp16 rounding boundary (one step = 5e-4 of
+        # that value, in the cache for good).  Quantized weights times a quantized embedding row have few
+        # significant bits, so exact rounding ties - where the double-precision oracle and any fp32
+        # evaluation part ways - are not rare here, and with embedding-sized hidden states (|h| ~ 0.05) one
+        # flipped large element shows in the logits at the 1e-4 level.  The tight bound holds while the
+        # caches agree to fp32 noise; a cache that differs by fp16 steps (never more than 2^-10 of its
+        # maximum) loosens it to 5e-4.
+        kv_err = 0.0
         for l in range(cfg.n_layers):
             k, v = eng.ReadKV(l, 0, pos + 1)
             ok, ov = om.kv_cache(l)
-            flips += int((k != ok[:pos + 1]).sum() + (v != ov[:pos + 1]).sum())
-        assert flips <= 4 * (pos + 1), f"pos {pos}: {flips} cache entries differ from the oracle's"
-        assert_close(logits, want, 1e-4 if flips == 0 else 5e-4, f"pos {pos} ({flips} fp16 rounding flips in the KV cache)")
+            for got_bits, want_bits in ((k, ok[:pos + 1]), (v, ov[:pos + 1])):
+                gf, wf = oracle.f16_bits_to_f32(got_bits), oracle.f16_bits_to_f32(want_bits)
+                kv_err = max(kv_err, float(np.abs(gf - wf).max() / np.abs(wf).max()))
+        assert kv_err <= 2 ** -10, f"pos {pos}: KV cache differs from the oracle's by {kv_err:.2e} of its maximum"
+        assert_close(logits, want, 1e-4 if kv_err < 1e-6 else 5e-4, f"pos {pos} (KV cache differs by {kv_err:.1e})")
         assert nxt == int(np.argmax(logits)), "device argmax disagrees with its own logits"
         assert eng.StepToken(tok, pos) == nxt, "argmax-only path disagrees"
         tok = nxt

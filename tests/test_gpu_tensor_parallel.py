@@ -19,7 +19,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TOL = 1e-4   # relative to max|y|, the same bound as the single-GPU engine tests
 
 
-def run_ranks(world, cases, nccl_exchange=False, kernels_path=False):
+def run_ranks(world, cases, nccl_exchange=False, kernels_path=False, timeout=300):
     import torch
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs, {torch.cuda.device_count()} visible")
@@ -28,7 +28,7 @@ def run_ranks(world, cases, nccl_exchange=False, kernels_path=False):
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                           "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
                           os.path.join(ROOT, "tests", "tp_worker.py"), *cases],
-                         capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+                         capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
     assert out.returncode == 0, (out.stdout[-1500:], out.stderr[-3000:])
     found = [l for l in out.stdout.splitlines() if l.startswith("TP_RESULTS ")]
     assert len(found) == 1, (out.stdout[-1500:], out.stderr[-3000:])
@@ -72,4 +72,21 @@ def test_two_ranks_with_nccl_exchange_match_the_oracle():
 def test_four_ranks_with_replicated_kv_heads_match_the_oracle():
     # 2 KV heads over 4 ranks: every KV head is held by two ranks that split its Q heads
     cases = ["tiny", "tiny-bias-ragged", "hd128-gqa"]
+    check(run_ranks(4, cases), cases)
+
+
+def test_eight_ranks_split_the_q_groups_of_shared_kv_heads():
+    """28 Q heads over 4 KV heads on 8 ranks: consecutive ranks share a KV head and take 4 + 3 of its Q heads."""
+    cases = ["gqa-28-4", "tiny-bias-ragged"]
+    check(run_ranks(8, cases), cases)
+
+
+def test_two_ranks_on_7b_class_widths():
+    """Real 7B-class layer shapes (dim 3584, head_dim 128, FFN 18944) split over two ranks."""
+    cases = ["qwen7b-width-2L"]
+    check(run_ranks(2, cases, timeout=900), cases)
+
+
+def test_four_ranks_on_the_7b_head_geometry():
+    cases = ["gqa-28-4"]
     check(run_ranks(4, cases), cases)

@@ -33,6 +33,12 @@ CASES = {
     "tiny-kv1": (mc.TINY.with_(name="tiny-kv1", n_kv_heads=1), True),
     "hd128-gqa": (mc.TINY.with_(name="hd128-gqa", dim=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn_dim=1184,
                                vocab=1500, n_layers=2), True),
+    # the 7B-class head geometry on a small model: 28 Q heads over 4 KV heads; with 8 ranks every KV head is
+    # held by two ranks that take 4 + 3 of its Q heads
+    "gqa-28-4": (mc.TINY.with_(name="gqa-28-4", dim=896, n_heads=28, n_kv_heads=4, head_dim=32, ffn_dim=1024,
+                              vocab=1608, n_layers=2), True),
+    # real 7B-class widths (head_dim 128, FFN 18944), two layers and a cut vocabulary
+    "qwen7b-width-2L": (mc.QWEN25_7B.with_(name="qwen7b-width-2L", n_layers=2, vocab=4000, max_seq=48), False),
 }
 
 
