@@ -5,11 +5,12 @@
 // The Go side declares these entry points (kernels.go:62-67, 206-211;
 // cuda_graph.go:211-234) but the reference ships no source for them; the
 // block layout is the one cuda_q4_0.go:13-17 uploads.  Raw blocks are only
-// 2-byte aligned, so these kernels read them with 16-bit loads; the engine
-// (mg_*) re-packs blocks at upload and does not use this file's kernels.
+// 2-byte aligned; the engine (mg_*) re-packs blocks at upload and does not
+// use this file's kernels.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdio>
 
 #include <mutex>
@@ -29,45 +30,66 @@ struct __align__(8) ActBlock {   // 40 bytes per 32 activations
 static_assert(sizeof(ActBlock) == 40, "activation block is 40 bytes");
 
 // ---------------- fp32-activation matvecs on raw blocks ----------------
-// One warp per row; lane handles blocks lane, lane+32, ...
+// Raw GGUF blocks (34 / 18 bytes) are only 2-byte aligned, so a lane cannot fetch its block with a
+// vector load.  Instead a warp takes a CHUNK of 32 consecutive blocks of a row - a contiguous byte
+// range - and copies the aligned 4-byte words that cover it from global to shared memory, lane by
+// lane (coalesced, every weight byte read once); each lane then pulls the words of ITS block out of
+// shared memory, re-aligns them with a funnel shift by 16 or 32 bits, and multiplies them with the
+// activation slice staged once per CTA.  One warp walks rows warp, warp + nwarps, ...; the 32 block
+// sums meet in a shuffle reduction.
+constexpr int kRawWarps = 8;
 template <int FMT>
-__global__ void __launch_bounds__(256) raw_block_matvec_kernel(const float* __restrict__ act,
-                                                              const uint8_t* __restrict__ w, float* out, int N,
-                                                              int K) {
+__global__ void __launch_bounds__(kRawWarps * 32) raw_block_matvec_kernel(const float* __restrict__ act,
+                                                                         const uint8_t* __restrict__ w, float* out, int N,
+                                                                         int K) {
+    constexpr int BB = FMT == FMT_Q8_0 ? 34 : 18;           // bytes per block
+    constexpr int QW = FMT == FMT_Q8_0 ? 8 : 4;             // 4-byte words of quants per block
+    constexpr int CW = (32 * BB + 3) / 4 + 1;               // words that cover a chunk, whatever its alignment
+    extern __shared__ __align__(16) float raw_xs[];         // K floats, then kRawWarps * CW words
+    uint32_t* stage = reinterpret_cast<uint32_t*>(raw_xs + K) + (threadIdx.x >> 5) * CW;
     const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= N) return;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) raw_xs[i] = act[i];
+    __syncthreads();
     const int nb = K / 32;
-    constexpr int BB = FMT == FMT_Q8_0 ? 34 : 18;
-    const uint8_t* wr = w + (size_t)row * nb * BB;
-    float acc = 0.f;
-    for (int b = lane; b < nb; b += 32) {
-        const unsigned short* p = reinterpret_cast<const unsigned short*>(wr + (size_t)b * BB);
-        const float d = half_bits_to_float(p[0]);
-        const float* x = act + (size_t)b * 32;
-        float s = 0.f;
-        if (FMT == FMT_Q8_0) {
+    const int nwarps = gridDim.x * kRawWarps;
+    for (int row = blockIdx.x * kRawWarps + (threadIdx.x >> 5); row < N; row += nwarps) {
+        const size_t row0 = (size_t)row * nb * BB;           // byte offset of the row (always even)
+        float acc = 0.f;
+        for (int b0 = 0; b0 < nb; b0 += 32) {
+            const int nblk = min(32, nb - b0);
+            const size_t c0 = row0 + (size_t)b0 * BB, c1 = c0 + (size_t)nblk * BB;
+            const size_t a0 = ((size_t)(w + c0)) & ~(size_t)3;                       // first aligned word (address)
+            const int nw = (int)((((size_t)(w + c1)) + 3 - a0) >> 2);
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(a0);
+            for (int i = lane; i < nw; i += 32) stage[i] = __ldcs(src + i);
+            __syncwarp();
+            if (lane < nblk) {
+                const int off = (int)((size_t)(w + c0) - a0) + lane * BB;               // this block inside the staged words
+                const uint32_t* q = stage + (off >> 2);
+                const int sh = (off & 2) ? 32 : 16;                                     // quants start 2 bytes after the scale
+                const uint32_t w0 = q[0];
+                const float d = half_bits_to_float((unsigned short)((off & 2) ? (w0 >> 16) : (w0 & 0xffffu)));
+                uint32_t qw[QW];
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const unsigned short v = p[1 + i];
-                s = fmaf(x[2 * i], (float)(int8_t)(v & 0xFF), s);
-                s = fmaf(x[2 * i + 1], (float)(int8_t)(v >> 8), s);
+                for (int i = 0; i < QW; i++) qw[i] = __funnelshift_rc(q[i], q[i + 1], sh);
+                const float4* x = reinterpret_cast<const float4*>(raw_xs + (size_t)(b0 + lane) * 32);
+                float s;
+                if (FMT == FMT_Q8_0)
+                    s = Chunk<FMT_Q8_0>::dot(make_uint4(qw[0], qw[1], qw[2], qw[3]), x) +
+                        Chunk<FMT_Q8_0>::dot(make_uint4(qw[4], qw[5], qw[6], qw[7]), x + 4);
+                else
+                    s = Chunk<FMT_Q4_0>::dot(make_uint4(qw[0], qw[1], qw[2], qw[3]), x);
+                acc = fmaf(d, s, acc);
             }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const unsigned short v = p[1 + i];
-                const int b0 = v & 0xFF, b1 = v >> 8;
-                s = fmaf(x[2 * i], (float)((b0 & 0xF) - 8), s);
-                s = fmaf(x[2 * i + 16], (float)((b0 >> 4) - 8), s);
-                s = fmaf(x[2 * i + 1], (float)((b1 & 0xF) - 8), s);
-                s = fmaf(x[2 * i + 17], (float)((b1 >> 4) - 8), s);
-            }
+            __syncwarp();
         }
-        acc = fmaf(d, s, acc);
+        acc = warp_sum(acc);
+        if (lane == 0) out[row] = acc;
     }
-    acc = warp_sum(acc);
-    if (lane == 0) out[row] = acc;
+}
+template <int FMT>
+inline size_t raw_matvec_smem(int K) {
+    return (size_t)K * 4 + (size_t)kRawWarps * ((32 * (FMT == FMT_Q8_0 ? 34 : 18) + 3) / 4 + 1) * 4;
 }
 
 // ---------------- activation quantizer: one warp per block of 32 ----------------
@@ -140,18 +162,39 @@ int static_fail(int code, const char* fmt, int a, int b) {
     return code;
 }
 
+// Grid: every SM gets the same number of CTAs (rows are walked with a stride), enough warps to hide
+// the loads.  Wide inputs need more than the default 48 KB of dynamic shared memory: raised once.
+template <int FMT>
+static void launch_raw_matvec(const float* act, const void* w_blocks, float* out, int N, int K, cudaStream_t stream) {
+    if (N <= 0 || K < 32 || K % 32) return;
+    static int sms = 0;
+    static bool raised = false;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    const size_t smem = raw_matvec_smem<FMT>(K);
+    if (smem > 48 * 1024 && !raised) {
+        cudaFuncSetAttribute((const void*)raw_block_matvec_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        raised = true;
+    }
+    const int per_sm = smem > 100 * 1024 ? 1 : smem > 48 * 1024 ? 2 : 4;
+    const int grid = std::min(cdiv(N, kRawWarps), sms * per_sm);
+    raw_block_matvec_kernel<FMT><<<grid, kRawWarps * 32, smem, stream>>>(act, (const uint8_t*)w_blocks, out, N, K);
+}
+
 }  // namespace
 
 extern "C" {
 
 void mongoose_q4_0_matvec(const float* act, const void* w_blocks, float* out, int N, int K, cudaStream_t stream) {
-    if (N <= 0 || K < 32) return;
-    raw_block_matvec_kernel<FMT_Q4_0><<<cdiv(N, 8), 256, 0, stream>>>(act, (const uint8_t*)w_blocks, out, N, K);
+    launch_raw_matvec<FMT_Q4_0>(act, w_blocks, out, N, K, stream);
 }
 
 void mongoose_q8_0_matvec(const float* act, const void* w_blocks, float* out, int N, int K, cudaStream_t stream) {
-    if (N <= 0 || K < 32) return;
-    raw_block_matvec_kernel<FMT_Q8_0><<<cdiv(N, 8), 256, 0, stream>>>(act, (const uint8_t*)w_blocks, out, N, K);
+    launch_raw_matvec<FMT_Q8_0>(act, w_blocks, out, N, K, stream);
 }
 
 void mongoose_q8_quantize_act(const float* act, void* q8_out, int K, cudaStream_t stream) {

@@ -49,7 +49,7 @@ namespace mg {
 constexpr int MK_NW = 15;                       // consumer warps
 constexpr int MK_CONSUMERS = MK_NW * 32;        // 480
 constexpr int MK_THREADS = MK_CONSUMERS + 32;   // + producer warp = 512 threads, 128 registers each
-constexpr int MK_SLOT = 16384;                  // ring slot bytes
+constexpr int MK_SLOT = 32768;                  // ring slot bytes
 constexpr int MK_MAX_SLOTS = 14;
 constexpr int MK_PART_FLOATS = 2048;
 constexpr int MK_EPOCHS_PER_LAYER = 8;
