@@ -268,6 +268,24 @@ MG_API int mg_partial_step_continue(mg_engine* e, int pos, int layer_start, int 
                                     float* logits_out);
 /* Hands src's device-resident hidden state to dst (another GPU: cudaMemcpyPeerAsync) on src's stream
  * and makes dst's stream wait for it; asynchronous. */
+/* StepLayerResident (cuda_fused_infer_q4.go:451-605): ONE layer at position pos, with HOST snapshots of
+ * the hidden state before (pre_out) and after (post_out) it; layer 0 uploads hidden_in, later layers
+ * continue on the device-resident hidden state; logits_out (any layer, as in the reference) adds the
+ * final norm and lm_head on the layer's output.  Any of the three outputs may be NULL. */
+MG_API int mg_step_layer_resident(mg_engine* e, int layer, int pos, const float* hidden_in, float* pre_out,
+                                  float* post_out, float* logits_out);
+/* vNodes (SetVNodeCount / RecordStageDone / WaitStageDone / SyncStream1 / QueueHiddenToL3OnStream1 /
+ * PartialStepQ4ContinueOnStream1, cuda_fused_infer.go:630-684, cuda_fused_infer_q4.go:391-444).  The
+ * reference overlaps two pipeline stages of one GPU on two compute streams; here a stage is one
+ * persistent launch over every SM, so "stream 1" is an ordering domain only: the calls keep their
+ * names, their order and their results, the stages run one after the other. */
+MG_API int mg_set_vnode_count(mg_engine* e, int n);
+MG_API int mg_vnode_count(const mg_engine* e);
+MG_API int mg_record_stage_done(mg_engine* e);
+MG_API int mg_wait_stage_done(mg_engine* e);
+MG_API int mg_sync_stream1(mg_engine* e);
+MG_API int mg_partial_step_continue_on_stream1(mg_engine* e, int pos, int layer_start, int layer_end, float* logits_out);
+MG_API int mg_queue_hidden_to_l3_on_stream1(mg_engine* e);
 MG_API int mg_queue_hidden_to(mg_engine* src, mg_engine* dst);
 /* WaitMailbox (cuda_fused_infer.go:575-591) with a deadline: MG_OK once the hidden state last queued
  * to e has arrived, MG_ERR_TIMEOUT after timeout_ms (also when nothing was queued). */

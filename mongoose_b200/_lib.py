@@ -81,6 +81,14 @@ SIGNATURES = {
     "mg_read_kv": (ci, [vp, ci, ci, ci, vp, vp]),
     "mg_trace_step": (ci, [vp, vp, ci, vp, vp]),
     "mg_set_wait_limit_ms": (ci, [vp, ci]),
+    "mg_step_layer_resident": (ci, [vp, ci, ci, vp, vp, vp, vp]),
+    "mg_set_vnode_count": (ci, [vp, ci]),
+    "mg_vnode_count": (ci, [vp]),
+    "mg_record_stage_done": (ci, [vp]),
+    "mg_wait_stage_done": (ci, [vp]),
+    "mg_sync_stream1": (ci, [vp]),
+    "mg_partial_step_continue_on_stream1": (ci, [vp, ci, ci, ci, vp]),
+    "mg_queue_hidden_to_l3_on_stream1": (ci, [vp]),
     "mg_set_layer_range": (ci, [vp, ci, ci]),
     "mg_partial_step_continue": (ci, [vp, ci, ci, ci, vp, vp]),
     "mg_queue_hidden_to": (ci, [vp, vp]),

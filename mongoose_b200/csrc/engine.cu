@@ -129,6 +129,10 @@ struct mg_engine {
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t compute_done = nullptr, l3_done = nullptr;
     bool l3_queued = false;
+    // second compute stream of the reference's vNode scheme (SetVNodeCount(2), cuda_fused_infer.go:630-666)
+    int vnodes = 1;
+    cudaStream_t stream1 = nullptr;
+    cudaEvent_t stage_done = nullptr, s1_in = nullptr, s1_out = nullptr;
     // tensor parallelism (mg_tp_init)
     Shard sh;
     ncclComm_t comm = nullptr;
@@ -1208,6 +1212,10 @@ void mg_destroy(mg_engine* e) {
     if (e->mail_event) cudaEventDestroy(e->mail_event);
     if (e->compute_done) cudaEventDestroy(e->compute_done);
     if (e->l3_done) cudaEventDestroy(e->l3_done);
+    if (e->stage_done) cudaEventDestroy(e->stage_done);
+    if (e->s1_in) cudaEventDestroy(e->s1_in);
+    if (e->s1_out) cudaEventDestroy(e->s1_out);
+    if (e->stream1) { cudaStreamSynchronize(e->stream1); cudaStreamDestroy(e->stream1); }
     if (e->stream) cudaStreamDestroy(e->stream);
     delete e;
 }
@@ -1375,6 +1383,113 @@ int mg_partial_step_continue(mg_engine* e, int pos, int layer_start, int layer_e
         MG_CUDA(e, cudaMemcpyAsync(hidden_out, e->h, (size_t)c.dim * 4, cudaMemcpyDeviceToHost, e->stream));
     MG_CUDA(e, cudaStreamSynchronize(e->stream));
     return check_mega_status(e);
+}
+
+// ---- StepLayerResident (cuda_fused_infer_q4.go:451-605): one layer with snapshots of the hidden state
+// before and after it; layer 0 takes the hidden state from the host, later layers continue on the
+// device-resident one; logits_out asks for the final norm + lm_head on top of the layer's output.
+int mg_step_layer_resident(mg_engine* e, int layer, int pos, const float* hidden_in, float* pre_out, float* post_out,
+                           float* logits_out) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if ((rc = ensure_built(e))) return rc;
+    const mg_config& c = e->cfg;
+    if (layer < 0 || layer >= c.n_layers || pos < 0 || pos >= c.max_seq || (layer == 0 && !hidden_in))
+        return fail(e, MG_ERR_ARG, "mg_step_layer_resident: bad arguments (layer %d, pos %d)", layer, pos);
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    e->pin_i[0] = pos; e->pin_i[1] = 0;
+    MG_CUDA(e, cudaMemcpyAsync(e->st, e->pin_i, 8, cudaMemcpyHostToDevice, e->stream));
+    if (layer == 0) MG_CUDA(e, cudaMemcpyAsync(e->h, hidden_in, (size_t)c.dim * 4, cudaMemcpyHostToDevice, e->stream));
+    if (pre_out) MG_CUDA(e, cudaMemcpyAsync(pre_out, e->h, (size_t)c.dim * 4, cudaMemcpyDeviceToHost, e->stream));
+    const bool last = layer == c.n_layers - 1;
+    const bool fused_head = logits_out && last && !post_out;      // the head in the same launch (post_out needs the layer's output first)
+    if ((rc = run_step(e, layer, layer + 1, MODE_HIDDEN, fused_head ? HEAD_LOGITS : HEAD_NONE))) return rc;
+    if (post_out && !fused_head) MG_CUDA(e, cudaMemcpyAsync(post_out, e->h, (size_t)c.dim * 4, cudaMemcpyDeviceToHost, e->stream));
+    if (logits_out && !fused_head) {
+        // final norm + lm_head on the hidden state as it stands (the reference does this for any layer)
+        if ((rc = run_step(e, c.n_layers, c.n_layers, MODE_HIDDEN, HEAD_LOGITS))) return rc;
+    }
+    if (logits_out)
+        MG_CUDA(e, cudaMemcpyAsync(logits_out, e->sh.size > 1 ? e->logits_all : e->logits, (size_t)c.vocab * 4,
+                                   cudaMemcpyDeviceToHost, e->stream));
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
+    return check_mega_status(e);
+}
+
+// ---- vNodes (cuda_fused_infer.go:630-684): the reference runs two pipeline stages of one GPU on two
+// compute streams with separate scratch sets.  Here a stage is one persistent launch that occupies
+// every SM, so two stages of one GPU cannot overlap; "stream 1" is kept as an ordering domain: work
+// issued to it runs on the engine's stream behind whatever stream 1 was waiting for, and whatever waits
+// on stream 1 afterwards waits for it.
+int mg_set_vnode_count(mg_engine* e, int n) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if (n < 1 || n > 2) return fail(e, MG_ERR_ARG, "mg_set_vnode_count: 1 or 2 vNodes, not %d", n);
+    if (n == 2 && !e->stream1) {
+        MG_CUDA(e, cudaStreamCreateWithFlags(&e->stream1, cudaStreamNonBlocking));
+        MG_CUDA(e, cudaEventCreateWithFlags(&e->stage_done, cudaEventDisableTiming));
+        MG_CUDA(e, cudaEventCreateWithFlags(&e->s1_in, cudaEventDisableTiming));
+        MG_CUDA(e, cudaEventCreateWithFlags(&e->s1_out, cudaEventDisableTiming));
+    }
+    e->vnodes = n;
+    return MG_OK;
+}
+int mg_vnode_count(const mg_engine* e) { return e ? e->vnodes : 0; }
+
+static int need_stream1(mg_engine* e, const char* what) {
+    if (int rc = check_engine(e)) return rc;
+    if (e->vnodes < 2 || !e->stream1) return fail(e, MG_ERR_STATE, "%s: call mg_set_vnode_count(e, 2) first", what);
+    return MG_OK;
+}
+int mg_record_stage_done(mg_engine* e) {
+    if (int rc = need_stream1(e, "mg_record_stage_done")) return rc;
+    MG_CUDA(e, cudaEventRecord(e->stage_done, e->stream));
+    return MG_OK;
+}
+int mg_wait_stage_done(mg_engine* e) {
+    if (int rc = need_stream1(e, "mg_wait_stage_done")) return rc;
+    MG_CUDA(e, cudaStreamWaitEvent(e->stream1, e->stage_done, 0));
+    return MG_OK;
+}
+int mg_sync_stream1(mg_engine* e) {
+    if (int rc = need_stream1(e, "mg_sync_stream1")) return rc;
+    MG_CUDA(e, cudaStreamSynchronize(e->stream1));
+    return check_mega_status(e);
+}
+// PartialStepQ4ContinueOnStream1 (cuda_fused_infer_q4.go:391-444): asynchronous; results are read after
+// mg_sync_stream1 (hidden state: mg_export_hidden; logits: the pointer given here, written by a copy
+// that stream 1 also waits for).
+int mg_partial_step_continue_on_stream1(mg_engine* e, int pos, int layer_start, int layer_end, float* logits_out) {
+    int rc = need_stream1(e, "mg_partial_step_continue_on_stream1");
+    if (rc) return rc;
+    if ((rc = ensure_built(e))) return rc;
+    const mg_config& c = e->cfg;
+    if (pos < 0 || pos >= c.max_seq || layer_start < 0 || layer_end < layer_start)
+        return fail(e, MG_ERR_ARG, "mg_partial_step_continue_on_stream1: bad arguments (pos %d, layers [%d,%d))", pos, layer_start, layer_end);
+    if (layer_end > c.n_layers) layer_end = c.n_layers;
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));   // pin_i is reused
+    MG_CUDA(e, cudaEventRecord(e->s1_in, e->stream1));
+    MG_CUDA(e, cudaStreamWaitEvent(e->stream, e->s1_in, 0));
+    e->pin_i[0] = pos; e->pin_i[1] = 0;
+    MG_CUDA(e, cudaMemcpyAsync(e->st, e->pin_i, 8, cudaMemcpyHostToDevice, e->stream));
+    const bool want_logits = layer_end >= c.n_layers && logits_out;
+    if ((rc = run_step(e, layer_start, layer_end, MODE_HIDDEN, want_logits ? HEAD_LOGITS : HEAD_NONE))) return rc;
+    if (want_logits)
+        MG_CUDA(e, cudaMemcpyAsync(logits_out, e->logits, (size_t)c.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
+    MG_CUDA(e, cudaEventRecord(e->s1_out, e->stream));
+    MG_CUDA(e, cudaStreamWaitEvent(e->stream1, e->s1_out, 0));
+    return MG_OK;
+}
+int mg_queue_hidden_to_l3_on_stream1(mg_engine* e) {
+    if (int rc = need_stream1(e, "mg_queue_hidden_to_l3_on_stream1")) return rc;
+    MG_CUDA(e, cudaEventRecord(e->compute_done, e->stream1));
+    MG_CUDA(e, cudaStreamWaitEvent(e->copy_stream, e->compute_done, 0));
+    MG_CUDA(e, cudaMemcpyAsync(e->l3, e->h, (size_t)e->cfg.dim * sizeof(float), cudaMemcpyDeviceToHost, e->copy_stream));
+    MG_CUDA(e, cudaEventRecord(e->l3_done, e->copy_stream));
+    MG_CUDA(e, cudaStreamWaitEvent(e->stream, e->l3_done, 0));
+    MG_CUDA(e, cudaStreamWaitEvent(e->stream1, e->l3_done, 0));
+    e->l3_queued = true;
+    return MG_OK;
 }
 
 int mg_queue_hidden_to(mg_engine* src, mg_engine* dst) {

@@ -166,6 +166,65 @@ class CUDAFusedInference:
         self._require_fp16("PartialStepFP16")
         return self.PartialStep(hiddenIn, pos, layerStart, layerEnd, hiddenOut, logitsOut)
 
+    # -- GGUF Q4_0 names (cuda_fused_infer_q4.go:92-444) ----------------------------------------
+    # The engine's format is fixed at creation (layer_fmt / head_fmt), so the Q4_0 entry points are the
+    # same calls on an engine created with Q4_0 layers; they refuse an engine of another format.
+    def _require_q4(self, what: str):
+        if self.cfg.layer_fmt != 1:
+            raise MongooseError(f"{what}: this engine was not created with Q4_0 layers (layer_fmt {self.cfg.layer_fmt})")
+
+    def PartialStepQ4(self, hiddenIn, pos: int, layerStart: int, layerEnd: int, hiddenOut=None, logitsOut=None) -> int:
+        self._require_q4("PartialStepQ4")
+        return self.PartialStep(hiddenIn, pos, layerStart, layerEnd, hiddenOut, logitsOut)
+
+    def PartialStepQ4Continue(self, pos: int, layerStart: int, layerEnd: int, hiddenOut=None, logitsOut=None) -> int:
+        self._require_q4("PartialStepQ4Continue")
+        return self.PartialStepContinue(pos, layerStart, layerEnd, hiddenOut, logitsOut)
+
+    def PartialStepQ4ContinueOnStream1(self, pos: int, layerStart: int, layerEnd: int, logitsOut=None) -> int:
+        """Asynchronous (cuda_fused_infer_q4.go:391-444): read the results after SyncStream1()."""
+        self._require_q4("PartialStepQ4ContinueOnStream1")
+        return self.PartialStepContinueOnStream1(pos, layerStart, layerEnd, logitsOut)
+
+    def PartialStepContinueOnStream1(self, pos: int, layerStart: int, layerEnd: int, logitsOut=None) -> int:
+        self._check(self._lib.mg_partial_step_continue_on_stream1(self._h, pos, layerStart, layerEnd, _host_ptr(logitsOut)),
+                    "PartialStepContinueOnStream1")
+        return 0
+
+    def StepLayerResident(self, layer: int, pos: int, hiddenIn=None, preOut=None, postOut=None, logitsOut=None) -> None:
+        """One layer with snapshots of the hidden state before and after it (+ logits), the call the
+        reference's needle trainers drive (cuda_fused_infer_q4.go:451-605)."""
+        self._check(self._lib.mg_step_layer_resident(self._h, layer, pos, _host_ptr(hiddenIn), _host_ptr(preOut),
+                                                     _host_ptr(postOut), _host_ptr(logitsOut)), "StepLayerResident")
+
+    # -- vNodes (cuda_fused_infer.go:630-684) -----------------------------------------------------
+    def SetVNodeCount(self, n: int) -> None:
+        self._check(self._lib.mg_set_vnode_count(self._h, n), "SetVNodeCount")
+
+    def VNodeCount(self) -> int:
+        return int(self._lib.mg_vnode_count(self._h))
+
+    def RecordStageDone(self) -> None:
+        self._check(self._lib.mg_record_stage_done(self._h), "RecordStageDone")
+
+    def WaitStageDone(self) -> None:
+        self._check(self._lib.mg_wait_stage_done(self._h), "WaitStageDone")
+
+    def SyncStream1(self) -> None:
+        self._check(self._lib.mg_sync_stream1(self._h), "SyncStream1")
+
+    def QueueHiddenToL3OnStream1(self) -> None:
+        self._check(self._lib.mg_queue_hidden_to_l3_on_stream1(self._h), "QueueHiddenToL3OnStream1")
+
+    def SwapHiddenBuffer(self) -> None:
+        """The reference alternates two hidden buffers so that an upload cannot overtake the L3 copy
+        (cuda_fused_infer.go:733-737); here the copy is ordered before the next step by an event, so
+        there is nothing to swap."""
+
+    def DisableFusedDispatch(self) -> None:
+        """The reference can fall back from its one-call dispatch to 17 calls per layer
+        (cuda_fused_infer.go:739-742); this engine has one path."""
+
     # -- layer-range pipeline (cuda_fused_infer.go:461-737) -------------------------------------
     def SetLayerRange(self, layerStart: int, layerEnd: int) -> None:
         """This engine is a pipeline stage holding layers [layerStart, layerEnd); the last stage also
