@@ -234,6 +234,20 @@ MG_API int mg_read_kv(mg_engine* e, int layer, int pos0, int npos, uint16_t* k_o
  * 11+3p = the CTA's tiles of phase p multiplied, 12+3p = all warps past them; other slots unused.
  * Needs the persistent kernel; capacity is in stamps. */
 MG_API int mg_trace_step(mg_engine* e, long long* stamps, int capacity, int* n_ctas, int* n_events);
+/* Device memory.  An engine reserves ONE device allocation at mg_create, sized from the model's shape,
+ * and carves every buffer out of it best-fit in 256-byte units (the reference's GPUArena,
+ * gpu_alloc.go:45-241; without it the reference pays one cudaMalloc per tensor, cuda_tensor.go:19-28).
+ * The calls below hand pieces of the same arena to the caller: the counterparts of tw_gpu_alloc /
+ * tw_gpu_upload / tw_gpu_download / tw_gpu_zero (cuda_tensor.go:19-44) and ArenaStats
+ * (gpu_alloc.go:58-66).  A request the arena cannot serve is passed to cudaMalloc (counted in
+ * `outside`). */
+MG_API int mg_device_alloc(mg_engine* e, size_t bytes, void** out);
+MG_API int mg_device_free(mg_engine* e, void* p);
+MG_API int mg_device_upload(mg_engine* e, void* dst, const void* host, size_t bytes);
+MG_API int mg_device_download(mg_engine* e, void* host, const void* src, size_t bytes);
+MG_API int mg_device_zero(mg_engine* e, void* dst, size_t bytes);
+MG_API int mg_arena_stats(const mg_engine* e, size_t* total, size_t* in_use, size_t* peak, size_t* largest_free,
+                          int* outside);
 /* Limit of every wait inside the persistent kernel (ring barriers, exchange polls), in milliseconds
  * of SM clock at 2 GHz; the default is about a second.  A wait that runs out makes the step return
  * MG_ERR_TIMEOUT; the context stays usable.  The reference's device-side waits (WaitMailbox,

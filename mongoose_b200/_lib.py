@@ -81,6 +81,12 @@ SIGNATURES = {
     "mg_read_kv": (ci, [vp, ci, ci, ci, vp, vp]),
     "mg_trace_step": (ci, [vp, vp, ci, vp, vp]),
     "mg_set_wait_limit_ms": (ci, [vp, ci]),
+    "mg_device_alloc": (ci, [vp, C.c_size_t, C.POINTER(vp)]),
+    "mg_device_free": (ci, [vp, vp]),
+    "mg_device_upload": (ci, [vp, vp, vp, C.c_size_t]),
+    "mg_device_download": (ci, [vp, vp, vp, C.c_size_t]),
+    "mg_device_zero": (ci, [vp, vp, C.c_size_t]),
+    "mg_arena_stats": (ci, [vp, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t), C.POINTER(ci)]),
     "mg_step_layer_resident": (ci, [vp, ci, ci, vp, vp, vp, vp]),
     "mg_set_vnode_count": (ci, [vp, ci]),
     "mg_vnode_count": (ci, [vp]),

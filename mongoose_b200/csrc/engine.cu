@@ -22,6 +22,7 @@
 #include <cstdio>
 #include <cstring>
 #include <map>
+#include <type_traits>
 #include <string>
 #include <vector>
 
@@ -77,6 +78,78 @@ struct NcclApi {
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
 };
 
+
+// One device allocation per engine, carved at create time and sub-allocated best-fit in 256-byte
+// units with coalescing frees: the counterpart of the reference's GPUArena (gpu_alloc.go:45-241).
+// Requests the arena cannot serve fall through to cudaMalloc and are remembered as such.
+struct Arena {
+    uint8_t* base = nullptr;
+    size_t size = 0;
+    std::map<size_t, size_t> free_blocks;      // offset -> length
+    std::map<size_t, size_t> used_blocks;      // offset -> length
+    std::map<void*, size_t> outside;           // cudaMalloc'ed because the arena was full
+    size_t peak = 0, in_use = 0;
+
+    bool init(size_t bytes) {
+        bytes = (bytes + 255) & ~(size_t)255;
+        if (cudaMalloc((void**)&base, bytes) != cudaSuccess) { cudaGetLastError(); base = nullptr; return false; }
+        size = bytes;
+        free_blocks[0] = bytes;
+        return true;
+    }
+    void destroy() {
+        for (auto& kv : outside) cudaFree(kv.first);
+        outside.clear();
+        if (base) cudaFree(base);
+        base = nullptr; size = 0; free_blocks.clear(); used_blocks.clear();
+    }
+    void* alloc(size_t bytes) {
+        if (bytes == 0) bytes = 1;
+        const size_t need = (bytes + 255) & ~(size_t)255;
+        auto best = free_blocks.end();
+        for (auto it = free_blocks.begin(); it != free_blocks.end(); ++it)
+            if (it->second >= need && (best == free_blocks.end() || it->second < best->second)) best = it;
+        if (best == free_blocks.end()) {
+            void* p = nullptr;
+            if (cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+            outside[p] = bytes;
+            return p;
+        }
+        const size_t off = best->first, len = best->second;
+        free_blocks.erase(best);
+        if (len > need) free_blocks[off + need] = len - need;
+        used_blocks[off] = need;
+        in_use += need;
+        peak = std::max(peak, in_use);
+        return base + off;
+    }
+    void release(void* p) {
+        if (!p) return;
+        auto o = outside.find(p);
+        if (o != outside.end()) { cudaFree(p); outside.erase(o); return; }
+        const size_t off = (size_t)((uint8_t*)p - base);
+        auto u = used_blocks.find(off);
+        if (u == used_blocks.end()) return;            // not ours: ignore rather than corrupt the lists
+        const size_t len = u->second;
+        in_use -= len;
+        used_blocks.erase(u);
+        size_t start = off, total = len;
+        auto next = free_blocks.lower_bound(off);          // first free block behind this one
+        if (next != free_blocks.begin()) {
+            auto prev = std::prev(next);
+            if (prev->first + prev->second == off) { start = prev->first; total += prev->second; free_blocks.erase(prev); }
+        }
+        auto nx = free_blocks.find(off + len);
+        if (nx != free_blocks.end()) { total += nx->second; free_blocks.erase(nx); }
+        free_blocks[start] = total;
+    }
+    size_t largest_free() const {
+        size_t m = 0;
+        for (auto& kv : free_blocks) m = std::max(m, kv.second);
+        return m;
+    }
+};
+
 }  // namespace
 
 struct mg_engine {
@@ -120,6 +193,7 @@ struct mg_engine {
     long long launches = 0;
     int capture_kernels = 0;            // kernels enqueued by the current enqueue_step
     size_t dev_bytes = 0;
+    Arena arena;                        // every device buffer of this engine except the peer-mapped exchange buffer
     // layer-range pipeline (mg_set_layer_range, mg_queue_hidden_to, L3 bridge)
     int own_ls = 0, own_le = 0;         // layers this engine holds weights for; [0, n_layers) by default
     cudaEvent_t sent_event = nullptr;   // recorded after this engine's hidden state has been copied to the next stage
@@ -159,6 +233,10 @@ int fail(mg_engine* e, int code, const char* fmt, ...) {
     return code;
 }
 
+// allocation calls of this file in the shape of cudaMalloc / cudaFree, served by the engine's arena
+#define ARENA_MALLOC(e, pp, bytes) ((*(pp) = static_cast<std::remove_reference<decltype(*(pp))>::type>((e)->arena.alloc(bytes))) ? cudaSuccess : cudaErrorMemoryAllocation)
+#define ARENA_FREE(e, p) (e)->arena.release((void*)(p))
+
 #define MG_CUDA(e, call)                                                                        \
     do {                                                                                        \
         cudaError_t _c = (call);                                                                \
@@ -169,12 +247,9 @@ int fail(mg_engine* e, int code, const char* fmt, ...) {
 
 template <typename T>
 int dev_alloc(mg_engine* e, T** p, size_t count) {
-    void* v = nullptr;
-    cudaError_t c = cudaMalloc(&v, count * sizeof(T));
-    if (c != cudaSuccess) {
-        cudaGetLastError();
-        return fail(e, MG_ERR_NOMEM, "cudaMalloc(%zu bytes) failed: %s", count * sizeof(T), cudaGetErrorString(c));
-    }
+    void* v = e->arena.alloc(count * sizeof(T));
+    if (!v) return fail(e, MG_ERR_NOMEM, "device allocation of %zu bytes failed (arena of %zu bytes, %zu in use)",
+                        count * sizeof(T), e->arena.size, e->arena.in_use);
     e->dev_bytes += count * sizeof(T);
     *p = static_cast<T*>(v);
     return MG_OK;
@@ -366,8 +441,8 @@ void split_raw_blocks(int fmt, const uint8_t* raw, size_t ld_bytes, int rows, in
 int upload_planes(mg_engine* e, int idx, int fmt, int rows, int K, const std::vector<uint8_t>& qs,
                   const std::vector<unsigned short>& ds) {
     DevMatrix& m = e->mats[idx];
-    if (m.qs) { cudaFree(m.qs); e->dev_bytes -= (size_t)m.rows * plane_row_bytes(m.fmt, m.cols); m.qs = nullptr; }
-    if (m.ds) { cudaFree(m.ds); e->dev_bytes -= (size_t)m.rows * (m.cols / 32) * 2; m.ds = nullptr; }
+    if (m.qs) { ARENA_FREE(e, m.qs); e->dev_bytes -= (size_t)m.rows * plane_row_bytes(m.fmt, m.cols); m.qs = nullptr; }
+    if (m.ds) { ARENA_FREE(e, m.ds); e->dev_bytes -= (size_t)m.rows * (m.cols / 32) * 2; m.ds = nullptr; }
     int rc = dev_alloc(e, &m.qs, qs.size());
     if (rc) return rc;
     MG_CUDA(e, cudaMemcpy(m.qs, qs.data(), qs.size(), cudaMemcpyHostToDevice));
@@ -648,15 +723,15 @@ int enqueue_step(mg_engine* e, cudaStream_t s, int ls, int le, int mode, int hea
 // Persistent-kernel path: tape construction and launch
 // ------------------------------------------------------------------
 void free_mega(mg_engine* e) {
-    auto drop = [&](void* p, size_t bytes) { if (p) { cudaFree(p); e->dev_bytes -= bytes; } };
+    auto drop = [&](void* p, size_t bytes) { if (p) { ARENA_FREE(e, p); e->dev_bytes -= bytes; } };
     drop(e->tape, e->tape_bytes); e->tape = nullptr; e->tape_bytes = 0;
-    if (e->tape_off) { cudaFree(e->tape_off); e->tape_off = nullptr; }
-    if (e->mk_norms) { cudaFree(e->mk_norms); e->mk_norms = nullptr; }
-    if (e->mk_bias) { cudaFree(e->mk_bias); e->mk_bias = nullptr; }
-    if (e->xbuf) { cudaFree(e->xbuf); e->xbuf = nullptr; }
-    if (e->mk_status) { cudaFree(e->mk_status); e->mk_status = nullptr; }
-    if (e->mk_trace) { cudaFree(e->mk_trace); e->mk_trace = nullptr; }
-    if (e->h_in) { cudaFree(e->h_in); e->h_in = nullptr; }
+    if (e->tape_off) { ARENA_FREE(e, e->tape_off); e->tape_off = nullptr; }
+    if (e->mk_norms) { ARENA_FREE(e, e->mk_norms); e->mk_norms = nullptr; }
+    if (e->mk_bias) { ARENA_FREE(e, e->mk_bias); e->mk_bias = nullptr; }
+    if (e->xbuf) { ARENA_FREE(e, e->xbuf); e->xbuf = nullptr; }
+    if (e->mk_status) { ARENA_FREE(e, e->mk_status); e->mk_status = nullptr; }
+    if (e->mk_trace) { ARENA_FREE(e, e->mk_trace); e->mk_trace = nullptr; }
+    if (e->h_in) { ARENA_FREE(e, e->h_in); e->h_in = nullptr; }
     e->mega_ok = false;
 }
 
@@ -902,9 +977,9 @@ int build_mega(mg_engine* e) {
     if ((rc = dev_alloc(e, &e->tape, tape.size()))) { e->tape_bytes = 0; return rc; }
     MG_CUDA(e, cudaMemcpy(e->tape, tape.data(), tape.size(), cudaMemcpyHostToDevice));
     tape = {};
-    MG_CUDA(e, cudaMalloc((void**)&e->tape_off, off.size() * 8));
+    MG_CUDA(e, ARENA_MALLOC(e, &e->tape_off, off.size() * 8));
     MG_CUDA(e, cudaMemcpy(e->tape_off, off.data(), off.size() * 8, cudaMemcpyHostToDevice));
-    MG_CUDA(e, cudaMalloc((void**)&e->mk_norms, (size_t)L * 2 * c.dim * 4));
+    MG_CUDA(e, ARENA_MALLOC(e, &e->mk_norms, (size_t)L * 2 * c.dim * 4));
     bool any_bias = false;
     for (int l = 0; l < L; l++) {
         if (!owned(l)) continue;
@@ -914,7 +989,7 @@ int build_mega(mg_engine* e) {
     }
     if (any_bias) {
         const size_t bw = (size_t)q_dim + 2 * c.kv_dim;
-        MG_CUDA(e, cudaMalloc((void**)&e->mk_bias, (size_t)L * bw * 4));
+        MG_CUDA(e, ARENA_MALLOC(e, &e->mk_bias, (size_t)L * bw * 4));
         MG_CUDA(e, cudaMemset(e->mk_bias, 0, (size_t)L * bw * 4));     // an unset bias adds zero
         for (int l = 0; l < L; l++) {
             if (!owned(l)) continue;
@@ -926,9 +1001,9 @@ int build_mega(mg_engine* e) {
         }
     }
     const size_t nx = (size_t)2 * c.dim + 2 * q_dim + 2 * c.kv_dim + c.ffn_dim + 2;   // xh xhm | xq | xkv | xattn | xmid | xtok
-    MG_CUDA(e, cudaMalloc((void**)&e->xbuf, nx * sizeof(Tagged)));
+    MG_CUDA(e, ARENA_MALLOC(e, &e->xbuf, nx * sizeof(Tagged)));
     MG_CUDA(e, cudaMemset(e->xbuf, 0, nx * sizeof(Tagged)));
-    MG_CUDA(e, cudaMalloc((void**)&e->mk_status, sizeof(MegaStatus)));
+    MG_CUDA(e, ARENA_MALLOC(e, &e->mk_status, sizeof(MegaStatus)));
     MG_CUDA(e, cudaMemset(e->mk_status, 0, sizeof(MegaStatus)));
     e->mega_ok = true;
     return MG_OK;
@@ -1122,9 +1197,26 @@ int mg_create(const mg_config* cfg, mg_engine** out) {
     e->mats.resize(nw);
     e->vecs.assign(nw, nullptr);
 
+    e->out_cap = c.max_seq > 4096 ? c.max_seq : 4096;
     const int half = c.head_dim / 2;
     const size_t kv_elems = (size_t)c.n_layers * c.max_seq * c.kv_dim;
-    e->out_cap = c.max_seq > 4096 ? c.max_seq : 4096;
+    {
+        // The arena: every buffer this engine will ever need, from the model's shape - the weight planes,
+        // the tape (a second copy of the layer weights and lm_head in consumption order), fp16 KV, tables,
+        // activations, exchange words - plus slack for alignment.  (MG_ARENA_MB overrides the size; what
+        // does not fit falls through to cudaMalloc.)
+        size_t planes = 0;
+        for (int idx = 0; idx < nw; idx++) {
+            bool is_matrix; int rows, cols, fmt;
+            slot_info(c, idx, &is_matrix, &rows, &cols, &fmt);
+            planes += is_matrix ? (size_t)rows * plane_row_bytes(fmt, cols) + (fmt == FMT_F16 ? 0 : (size_t)rows * (cols / 32) * 2) + 512
+                                : (size_t)cols * 4 + 256;
+        }
+        size_t want = 2 * planes + planes / 16 + kv_elems * 4 + (size_t)c.max_seq * half * 8 + (size_t)c.vocab * 8 +
+                      (size_t)(c.dim * 64 + c.ffn_dim * 16) + (size_t)e->out_cap * 4 + (64u << 20);
+        if (const char* mb = getenv("MG_ARENA_MB")) want = (size_t)atoll(mb) << 20;
+        if (!e->arena.init(want)) fprintf(stderr, "[mongoose-b200] arena of %zu MB not available: falling back to one allocation per buffer\n", want >> 20);
+    }
     if ((rc = dev_alloc(e, &e->cos_tab, (size_t)c.max_seq * half))) return bail(rc);
     if ((rc = dev_alloc(e, &e->sin_tab, (size_t)c.max_seq * half))) return bail(rc);
     if ((rc = dev_alloc(e, &e->kc, kv_elems))) return bail(rc);
@@ -1185,14 +1277,14 @@ void mg_destroy(mg_engine* e) {
     drop_graphs(e);
     free_mega(e);
     for (auto& m : e->mats) {
-        if (m.qs) cudaFree(m.qs);
-        if (m.ds) cudaFree(m.ds);
+        if (m.qs) ARENA_FREE(e, m.qs);
+        if (m.ds) ARENA_FREE(e, m.ds);
     }
     for (float* v : e->vecs)
-        if (v) cudaFree(v);
-    cudaFree(e->cos_tab); cudaFree(e->sin_tab); cudaFree(e->kc); cudaFree(e->vc);
-    cudaFree(e->h); cudaFree(e->h2); cudaFree(e->q); cudaFree(e->attn); cudaFree(e->mid); cudaFree(e->logits);
-    cudaFree(e->st); cudaFree(e->out_tokens);
+        if (v) ARENA_FREE(e, v);
+    ARENA_FREE(e, e->cos_tab); ARENA_FREE(e, e->sin_tab); ARENA_FREE(e, e->kc); ARENA_FREE(e, e->vc);
+    ARENA_FREE(e, e->h); ARENA_FREE(e, e->h2); ARENA_FREE(e, e->q); ARENA_FREE(e, e->attn); ARENA_FREE(e, e->mid); ARENA_FREE(e, e->logits);
+    ARENA_FREE(e, e->st); ARENA_FREE(e, e->out_tokens);
     if (e->comm && e->zero_vec) {
         // no rank unmaps or frees its receive buffer while a peer may still be writing to it
         if (g_nccl.AllReduce(e->zero_vec, e->zero_vec, 1, ncclFloat, ncclSum, e->comm, e->stream) == ncclSuccess)
@@ -1201,9 +1293,9 @@ void mg_destroy(mg_engine* e) {
     for (int p = 0; p < kMaxRanks; p++)
         if (e->xchg_peer[p] && e->xchg_peer[p] != e->xchg) cudaIpcCloseMemHandle(e->xchg_peer[p]);
     if (e->xchg) cudaFree(e->xchg);
-    if (e->xchg_status) cudaFree(e->xchg_status);
-    if (e->zero_vec) cudaFree(e->zero_vec);
-    if (e->logits_all) cudaFree(e->logits_all);
+    if (e->xchg_status) ARENA_FREE(e, e->xchg_status);
+    if (e->zero_vec) ARENA_FREE(e, e->zero_vec);
+    if (e->logits_all) ARENA_FREE(e, e->logits_all);
     if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
     if (e->pin_i) cudaFreeHost(e->pin_i);
     if (e->copy_stream) { cudaStreamSynchronize(e->copy_stream); cudaStreamDestroy(e->copy_stream); }
@@ -1217,6 +1309,7 @@ void mg_destroy(mg_engine* e) {
     if (e->s1_out) cudaEventDestroy(e->s1_out);
     if (e->stream1) { cudaStreamSynchronize(e->stream1); cudaStreamDestroy(e->stream1); }
     if (e->stream) cudaStreamDestroy(e->stream);
+    e->arena.destroy();
     delete e;
 }
 
@@ -1758,7 +1851,7 @@ int mg_trace_step(mg_engine* e, long long* stamps, int capacity, int* n_ctas, in
     if (!e->mega_ok) return fail(e, MG_ERR_UNSUPPORTED, "mg_trace_step: the persistent kernel is not in use (%s)", e->err.c_str());
     const int ev = MK_TRACE_EVENTS(e->cfg.n_layers), G = e->num_sms;
     if (!stamps || capacity < G * ev) return fail(e, MG_ERR_ARG, "mg_trace_step: need room for %d stamps", G * ev);
-    if (!e->mk_trace) MG_CUDA(e, cudaMalloc((void**)&e->mk_trace, (size_t)G * ev * 8));
+    if (!e->mk_trace) MG_CUDA(e, ARENA_MALLOC(e, &e->mk_trace, (size_t)G * ev * 8));
     MG_CUDA(e, cudaMemsetAsync(e->mk_trace, 0, (size_t)G * ev * 8, e->stream));
     e->trace_next = true;
     if ((rc = launch_mega(e, 0, e->cfg.n_layers, MODE_EMBED, HEAD_ARGMAX, 1))) return rc;
@@ -1767,6 +1860,54 @@ int mg_trace_step(mg_engine* e, long long* stamps, int capacity, int* n_ctas, in
     if (n_ctas) *n_ctas = G;
     if (n_events) *n_events = ev;
     return check_mega_status(e);
+}
+
+// ---- raw device memory from the engine's arena: the counterparts of tw_gpu_alloc / upload / download /
+// zero (cuda_tensor.go:19-44) and ArenaStats (gpu_alloc.go:58-66) for callers that keep their own
+// device buffers (scratch vectors, caller-owned weights for the mongoose_* entry points).
+int mg_device_alloc(mg_engine* e, size_t bytes, void** out) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if (!out) return MG_ERR_ARG;
+    *out = e->arena.alloc(bytes);
+    if (!*out) return fail(e, MG_ERR_NOMEM, "mg_device_alloc: %zu bytes not available", bytes);
+    return MG_OK;
+}
+int mg_device_free(mg_engine* e, void* p) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    e->arena.release(p);
+    return MG_OK;
+}
+int mg_device_upload(mg_engine* e, void* dst, const void* host, size_t bytes) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if (!dst || !host) return MG_ERR_ARG;
+    MG_CUDA(e, cudaMemcpy(dst, host, bytes, cudaMemcpyHostToDevice));
+    return MG_OK;
+}
+int mg_device_download(mg_engine* e, void* host, const void* src, size_t bytes) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if (!src || !host) return MG_ERR_ARG;
+    MG_CUDA(e, cudaMemcpy(host, src, bytes, cudaMemcpyDeviceToHost));
+    return MG_OK;
+}
+int mg_device_zero(mg_engine* e, void* dst, size_t bytes) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if (!dst) return MG_ERR_ARG;
+    MG_CUDA(e, cudaMemset(dst, 0, bytes));
+    return MG_OK;
+}
+int mg_arena_stats(const mg_engine* e, size_t* total, size_t* in_use, size_t* peak, size_t* largest_free, int* outside) {
+    if (!e) return MG_ERR_ARG;
+    if (total) *total = e->arena.size;
+    if (in_use) *in_use = e->arena.in_use;
+    if (peak) *peak = e->arena.peak;
+    if (largest_free) *largest_free = e->arena.largest_free();
+    if (outside) *outside = (int)e->arena.outside.size();
+    return MG_OK;
 }
 
 int mg_set_wait_limit_ms(mg_engine* e, int ms) {
@@ -1823,7 +1964,9 @@ int mg_tp_init(mg_engine* e, int rank, int size, const void* id, size_t bytes) {
     const char* env = getenv("MG_TP_NCCL");
     bool want_fused = !(env && env[0] == '1') && size <= kMaxRanks;
     {
-        if ((rc = dev_alloc(e, &e->xchg, xchg_bytes(e)))) return rc;
+        // an allocation of its own, not a piece of the arena: CUDA IPC maps whole allocations into the peers
+        MG_CUDA(e, cudaMalloc((void**)&e->xchg, xchg_bytes(e)));
+        e->dev_bytes += xchg_bytes(e);
         if ((rc = dev_alloc(e, &e->xchg_status, (size_t)1))) return rc;
         MG_CUDA(e, cudaMemset(e->xchg, 0, xchg_bytes(e)));
         MG_CUDA(e, cudaMemset(e->xchg_status, 0, sizeof(XchgStatus)));

@@ -360,6 +360,30 @@ class CUDAFusedInference:
         self._check(self._lib.mg_trace_step(self._h, _np_ptr(buf), cap, C.byref(n_ctas), C.byref(n_ev)), "TraceStep")
         return buf[: n_ctas.value * n_ev.value].reshape(n_ctas.value, n_ev.value)
 
+    # -- device memory from the engine's arena (cuda_tensor.go:19-44, gpu_alloc.go:45-241) ----------
+    def DeviceAlloc(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        self._check(self._lib.mg_device_alloc(self._h, nbytes, C.byref(p)), "DeviceAlloc")
+        return p.value
+
+    def DeviceFree(self, ptr: int) -> None:
+        self._check(self._lib.mg_device_free(self._h, ptr), "DeviceFree")
+
+    def DeviceUpload(self, ptr: int, host: np.ndarray) -> None:
+        a = np.ascontiguousarray(host)
+        self._check(self._lib.mg_device_upload(self._h, ptr, _np_ptr(a), a.nbytes), "DeviceUpload")
+
+    def DeviceDownload(self, host: np.ndarray, ptr: int) -> None:
+        self._check(self._lib.mg_device_download(self._h, _np_ptr(host), ptr, host.nbytes), "DeviceDownload")
+
+    def DeviceZero(self, ptr: int, nbytes: int) -> None:
+        self._check(self._lib.mg_device_zero(self._h, ptr, nbytes), "DeviceZero")
+
+    def ArenaStats(self) -> dict:
+        t, u, p, lf, o = C.c_size_t(), C.c_size_t(), C.c_size_t(), C.c_size_t(), C.c_int()
+        self._check(self._lib.mg_arena_stats(self._h, C.byref(t), C.byref(u), C.byref(p), C.byref(lf), C.byref(o)), "ArenaStats")
+        return {"total": t.value, "in_use": u.value, "peak": p.value, "largest_free": lf.value, "outside": o.value}
+
     def SetWaitLimit(self, ms: int) -> None:
         """Limit of every wait inside the persistent kernel; a wait that runs out makes the step
         raise with MG_ERR_TIMEOUT (the reference's WaitMailbox spins without one)."""
