@@ -332,6 +332,12 @@ MG_API int mg_tp_unique_id(void* id_out, size_t bytes);
  * weight is set.  NCCL is resolved from libnccl.so.2 at this point, not at load time. */
 MG_API int mg_tp_init(mg_engine* e, int rank, int size, const void* id, size_t bytes);
 /* The stream the engine enqueues on (for event timing by the caller). */
+/* Test aid (no counterpart in the reference): rank 0 of a `size`-rank tensor-parallel group whose peers
+ * do not exist, on one GPU.  Nothing ever writes the other ranks' rows of the receive buffer, so the
+ * first in-kernel wait for them runs out after the wait limit and the step returns MG_ERR_TIMEOUT with
+ * the exchange named in mg_last_error: the way to exercise the bounded device-side waits without a
+ * second GPU and without faulting or hanging one. */
+MG_API int mg_tp_init_absent_peers(mg_engine* e, int size);
 MG_API cudaStream_t mg_stream(mg_engine* e);
 /* Kernels launched by this engine since creation (graph replays count their kernel nodes). */
 MG_API long long mg_launch_count(const mg_engine* e);

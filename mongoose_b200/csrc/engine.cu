@@ -215,6 +215,7 @@ struct mg_engine {
     bool any_weight_set = false;
     // exchange fused into the kernels: receive buffer of this rank, mapped into every peer
     bool tp_fused = false;
+    bool absent_peers = false;          // test aid: a tensor-parallel rank whose peers do not exist (mg_tp_init_absent_peers)
     uint8_t* xchg = nullptr;            // [2 slots][size][dim] tagged words, then this rank's counters
     uint8_t* xchg_peer[kMaxRanks] = {}; // rank p's buffer as seen from here (own entry = xchg)
     XchgStatus* xchg_status = nullptr;
@@ -835,7 +836,7 @@ int build_mega(mg_engine* e) {
             why = "one CTA does not fit an SM";
         }
     }
-    if (e->sh.size > 1) {
+    if (e->sh.size > 1 && e->comm) {
         // every rank must take the same path: the persistent kernels of the ranks wait for one another
         int* d_ok = nullptr;
         int h_ok = ok ? 1 : 0;
@@ -1073,6 +1074,8 @@ int check_mega_status(mg_engine* e) {
     MG_CUDA(e, cudaMemcpy(&s, e->mk_status, sizeof s, cudaMemcpyDeviceToHost));
     if (s.error) {
         cudaMemset(e->mk_status, 0, sizeof s);
+        if (s.error == MK_ERR_POLL && s.who >= 0)
+            return fail(e, MG_ERR_TIMEOUT, "persistent kernel: the rows of rank %d never arrived (exchange %u, CTA %d)", s.who, (unsigned)s.where, s.cta);
         return fail(e, MG_ERR_TIMEOUT, "persistent kernel: wait %d timed out (where %d, CTA %d)", s.error, s.where, s.cta);
     }
     return MG_OK;
@@ -1092,7 +1095,7 @@ int run_step(mg_engine* e, int ls, int le, int mode, int head) {
     if (int rc = check_range(e, ls, le, head != HEAD_NONE && le >= e->cfg.n_layers, mode == MODE_EMBED)) return rc;
     if (e->mega_ok && le > ls) {
         if (int rc = launch_mega(e, ls, le, mode, head, 1)) return rc;
-        if (e->sh.size > 1 && head == HEAD_LOGITS && le >= e->cfg.n_layers)   // every rank gets every rank's slice
+        if (e->sh.size > 1 && e->comm && head == HEAD_LOGITS && le >= e->cfg.n_layers)   // every rank gets every rank's slice
             MG_NCCL(e, g_nccl.AllGather(e->logits, e->logits_all, (size_t)e->sh.v_stride, ncclFloat, e->comm, e->stream));
         return MG_OK;
     }
@@ -2014,6 +2017,33 @@ int mg_tp_init(mg_engine* e, int rank, int size, const void* id, size_t bytes) {
     // Programmatic dependent launch stays off under tensor parallelism, on both exchange paths: the
     // per-phase kernels alternate with library collectives (NCCL path), and with the in-kernel exchange
     // an early-launched consumer would spin on words that a peer's not-yet-running kernel must write.
+    e->use_pdl = false;
+    e->built = false;
+    return MG_OK;
+}
+
+// Test aid for the in-kernel exchange deadline on ONE GPU: rank 0 of a `size`-rank group whose peers do
+// not exist.  The receive buffer is this engine's own, every "peer" pointer aliases it, and nothing
+// ever writes the other ranks' rows: the first wait for them runs out after the wait limit
+// (mg_set_wait_limit_ms), the kernel records which exchange it was and returns, and the step reports
+// MG_ERR_TIMEOUT.  No NCCL communicator is made; only the greedy / hidden-state calls are meaningful.
+int mg_tp_init_absent_peers(mg_engine* e, int size) {
+    int rc = check_engine(e);
+    if (rc) return rc;
+    if (e->any_weight_set || e->comm || e->xchg) return fail(e, MG_ERR_STATE, "mg_tp_init_absent_peers: call once, before any weight is set");
+    if (size < 2 || size > kMaxRanks) return fail(e, MG_ERR_ARG, "mg_tp_init_absent_peers: 2..%d ranks", kMaxRanks);
+    std::string why;
+    Shard s;
+    if (!make_shard(e->cfg, 0, size, &s, &why)) return fail(e, MG_ERR_UNSUPPORTED, "mg_tp_init_absent_peers: %s", why.c_str());
+    e->sh = s;
+    MG_CUDA(e, cudaMalloc((void**)&e->xchg, xchg_bytes(e)));
+    e->dev_bytes += xchg_bytes(e);
+    if ((rc = dev_alloc(e, &e->xchg_status, (size_t)1))) return rc;
+    MG_CUDA(e, cudaMemset(e->xchg, 0, xchg_bytes(e)));
+    MG_CUDA(e, cudaMemset(e->xchg_status, 0, sizeof(XchgStatus)));
+    for (int p = 0; p < size; p++) e->xchg_peer[p] = e->xchg;
+    e->tp_fused = true;
+    e->absent_peers = true;
     e->use_pdl = false;
     e->built = false;
     return MG_OK;

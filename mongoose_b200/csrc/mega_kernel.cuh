@@ -62,7 +62,7 @@ struct MegaStatus {
     int error;          // first error code (0 = none)
     int where;          // phase / tag that timed out
     int cta;
-    int pad;
+    int who;            // exchange polls: the rank whose row had not arrived (-1: not an exchange between ranks)
 };
 
 struct Tagged {         // one exchanged activation
@@ -365,11 +365,12 @@ struct MkCtx {
     __device__ __forceinline__ int nslot() const { return a.nslot; }
 };
 
-__device__ __noinline__ void mk_fail_impl(volatile int* abort_flag, MegaStatus* status, int code, int where) {
+__device__ __noinline__ void mk_fail_impl(volatile int* abort_flag, MegaStatus* status, int code, int where, int who = -1) {
     *abort_flag = 1;
     if (atomicCAS(&status->error, 0, code) == 0) {
         status->where = where;
         status->cta = blockIdx.x;
+        status->who = who;
     }
 }
 __device__ __forceinline__ void mk_fail(MkCtx& c, int code, int where) {
@@ -422,7 +423,7 @@ __device__ __forceinline__ void mk_wait_bar(MkCtx& c, unsigned long long* bar, u
 // Re-read a pair of exchange words (16-byte aligned) until both carry `tag`; sys = the words may be
 // written by another GPU.  Returns the raw words: x, z = values, y, w = tags.
 __device__ __noinline__ uint4 mk_poll16_slow(volatile int* abort_flag, MegaStatus* status, long long limit,
-                                             const Tagged* p, unsigned int tag, int sys) {
+                                             const Tagged* p, unsigned int tag, int sys, int who = -1) {
     uint4 r = make_uint4(0u, tag, 0u, tag);
     if (*abort_flag) return r;
     const long long t0 = global_ns();
@@ -432,7 +433,7 @@ __device__ __noinline__ uint4 mk_poll16_slow(volatile int* abort_flag, MegaStatu
         if ((it & 63u) == 0u) {
             if (*abort_flag) return r;
             if (*(volatile int*)&status->error) { *abort_flag = 1; return r; }
-            if (global_ns() - t0 > limit) { mk_fail_impl(abort_flag, status, MK_ERR_POLL, (int)tag); return r; }
+            if (global_ns() - t0 > limit) { mk_fail_impl(abort_flag, status, MK_ERR_POLL, (int)tag, who); return r; }
         }
     }
 }
@@ -446,9 +447,9 @@ __device__ __forceinline__ void mk_poll2(MkCtx& c, const Tagged* p, unsigned int
     v0 = __uint_as_float(r.x);
     v1 = __uint_as_float(r.z);
 }
-__device__ __forceinline__ uint4 mk_poll16_sys(MkCtx& c, const Tagged* q, unsigned int tag) {
+__device__ __forceinline__ uint4 mk_poll16_sys(MkCtx& c, const Tagged* q, unsigned int tag, int who = -1) {
     uint4 w = ld_poll16_sys(q);
-    if (w.y != tag || w.w != tag) w = mk_poll16_slow(c.abort_flag(), c.status(), c.a.wait_cycles, q, tag, 1);
+    if (w.y != tag || w.w != tag) w = mk_poll16_slow(c.abort_flag(), c.status(), c.a.wait_cycles, q, tag, 1, who);
     return w;
 }
 // One exchange word (the token of the previous step).
@@ -473,11 +474,11 @@ __device__ __forceinline__ float mk_poll1(MkCtx& c, const Tagged* p, unsigned in
 // order (every rank forms the same bits).  p points into row 0, rows are `stride` words apart.
 __device__ __forceinline__ void mk_poll2_sum(MkCtx& c, const Tagged* p, int stride, int n, unsigned int tag, float& v0,
                                              float& v1) {
-    const uint4 first = mk_poll16_sys(c, p, tag);
+    const uint4 first = mk_poll16_sys(c, p, tag, 0);
     v0 = __uint_as_float(first.x);
     v1 = __uint_as_float(first.z);
     for (int r = 1; r < n; r++) {
-        const uint4 w = mk_poll16_sys(c, p + (size_t)r * stride, tag);
+        const uint4 w = mk_poll16_sys(c, p + (size_t)r * stride, tag, r);
         v0 += __uint_as_float(w.x);
         v1 += __uint_as_float(w.z);
     }
@@ -1560,7 +1561,7 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
                         }
                         for (int r = 0; r < a.tp_n; r++) {
                             // raw words: the halves of a key are bit patterns, not numbers
-                            const uint4 w = mk_poll16_sys(c, a.xbest + 2 * r, tagx);
+                            const uint4 w = mk_poll16_sys(c, a.xbest + 2 * r, tagx, r);
                             const unsigned long long k = ((unsigned long long)w.x << 32) | (unsigned long long)w.z;
                             key = k > key ? k : key;
                         }

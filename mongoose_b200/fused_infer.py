@@ -389,6 +389,12 @@ class CUDAFusedInference:
         raise with MG_ERR_TIMEOUT (the reference's WaitMailbox spins without one)."""
         self._check(self._lib.mg_set_wait_limit_ms(self._h, int(ms)), "SetWaitLimit")
 
+    def TpInitAbsentPeers(self, size: int) -> None:
+        """Test aid without a counterpart in the reference: make this engine rank 0 of a `size`-rank
+        tensor-parallel group whose other ranks do not exist, so the bounded waits inside the
+        persistent kernel can be shown to run out on one GPU.  Call before uploading weights."""
+        self._check(self._lib.mg_tp_init_absent_peers(self._h, int(size)), "TpInitAbsentPeers")
+
     @property
     def stream(self) -> int:
         return self._lib.mg_stream(self._h) or 0

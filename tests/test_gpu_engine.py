@@ -193,3 +193,35 @@ def test_error_behaviour(cuda, mglib):
     with pytest.raises(MongooseError):
         eng.Generate(np.array([1, 2, 3], np.int32), cfg.max_seq)
     eng.close()
+
+
+def test_in_kernel_exchange_wait_runs_out_and_returns(cuda, oracle, mglib):
+    """The bounded device-side waits, on one GPU: a tensor-parallel rank whose peer never sends.  The
+    kernel gives up after the wait limit, names the missing rank and the exchange, and returns; the
+    context stays usable (a fresh engine decodes correctly afterwards).  Nothing faults or hangs."""
+    import time
+    cfg = mc.TINY
+    eng = CUDAFusedInference(cfg)
+    try:
+        eng.TpInitAbsentPeers(2)
+        fill_models(cfg, seed=1, jitter=0.1, engine=eng)
+        eng.BuildFusedDispatch()
+        assert "not used" not in eng._lib.mg_last_error(eng._h).decode(), "the persistent kernel must be the path under test"
+        eng.SetWaitLimit(2)
+        t0 = time.perf_counter()
+        with pytest.raises(MongooseError, match=r"rows of rank 1 never arrived \(exchange \d+"):
+            eng.StepToken(1, 0)
+        assert time.perf_counter() - t0 < 2.0, "every wait is bounded: the step must come back promptly"
+        # a second step fails the same way and as promptly
+        with pytest.raises(MongooseError, match="never arrived"):
+            eng.StepToken(2, 1)
+    finally:
+        eng.close()
+    eng, om = CUDAFusedInference(cfg), oracle.OracleModel(cfg)
+    try:
+        fill_models(cfg, seed=1, jitter=0.1, engine=eng, oracle_model=om)
+        logits = np.empty(cfg.vocab, np.float32)
+        eng.StepToken(1, 0, logitsOut=logits)
+        assert_close(logits, om.step_token(1, 0), 1e-4, "a fresh engine after the timeout")
+    finally:
+        eng.close(); om.close()
