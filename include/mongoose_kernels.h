@@ -248,6 +248,10 @@ MG_API int mg_device_download(mg_engine* e, void* host, const void* src, size_t 
 MG_API int mg_device_zero(mg_engine* e, void* dst, size_t bytes);
 MG_API int mg_arena_stats(const mg_engine* e, size_t* total, size_t* in_use, size_t* peak, size_t* largest_free,
                           int* outside);
+/* Which decode path a built engine runs (no counterpart in the reference, whose path is fixed): bit 0 the
+ * persistent kernel, bit 1 its feed-forward block without an exchange of the middle vector (one GPU),
+ * bit 2 tensor-parallel exchange inside the kernels.  0 = the graph of per-phase kernels. */
+MG_API int mg_decode_path(const mg_engine* e);
 /* Limit of every wait inside the persistent kernel (ring barriers, exchange polls), in milliseconds
  * of SM clock at 2 GHz; the default is about a second.  A wait that runs out makes the step return
  * MG_ERR_TIMEOUT; the context stays usable.  The reference's device-side waits (WaitMailbox,

@@ -81,6 +81,7 @@ SIGNATURES = {
     "mg_read_kv": (ci, [vp, ci, ci, ci, vp, vp]),
     "mg_trace_step": (ci, [vp, vp, ci, vp, vp]),
     "mg_set_wait_limit_ms": (ci, [vp, ci]),
+    "mg_decode_path": (ci, [vp]),
     "mg_tp_init_absent_peers": (ci, [vp, ci]),
     "mg_device_alloc": (ci, [vp, C.c_size_t, C.POINTER(vp)]),
     "mg_device_free": (ci, [vp, vp]),

@@ -184,6 +184,12 @@ struct mg_engine {
     int mk_nslot = 0, mk_slot = MK_SLOT, mk_xs = 0, mk_sc = 0;
     int mk_prefetch = 0;                // L2 prefetch distance of the tape, bytes
     long long mk_wait = MK_WAIT_CYCLES; // limit of every wait inside the persistent kernel, SM clocks
+    // feed-forward block without a grid-wide exchange (one GPU): accumulators [3][dim] + arrival counter,
+    // and the host's mirror of where the next launch continues
+    bool ffn_fused = false;
+    long long* mk_acc = nullptr;
+    int mk_buf = 0;
+    unsigned int mk_ctr = 0;
     PhaseGeom mk_geom[5] = {};
     size_t mk_smem = 0;
     size_t tape_bytes = 0;
@@ -731,6 +737,8 @@ void free_mega(mg_engine* e) {
     if (e->mk_bias) { ARENA_FREE(e, e->mk_bias); e->mk_bias = nullptr; }
     if (e->xbuf) { ARENA_FREE(e, e->xbuf); e->xbuf = nullptr; }
     if (e->mk_status) { ARENA_FREE(e, e->mk_status); e->mk_status = nullptr; }
+    if (e->mk_acc) { ARENA_FREE(e, e->mk_acc); e->mk_acc = nullptr; }
+    e->ffn_fused = false;
     if (e->mk_trace) { ARENA_FREE(e, e->mk_trace); e->mk_trace = nullptr; }
     if (e->h_in) { ARENA_FREE(e, e->h_in); e->h_in = nullptr; }
     e->mega_ok = false;
@@ -808,6 +816,35 @@ bool mega_feasible(mg_engine* e, std::string* why) {
         if (e->mk_geom[p].nkt == 0) { *why = "no tile layout for a phase"; return false; }
         xs_bytes = std::max(xs_bytes, xs_bytes_of(s.fmt, s.K));
     }
+    // Down projection on each CTA's own window of the middle vector (no exchange between gate/up and
+    // down; one GPU).  The window is the blocks of columns the CTA's gate/up items touch, rounded up
+    // to whole wide tiles, the same width on every CTA.  MG_FFN_FUSED=0 keeps the exchange.
+    e->ffn_fused = false;
+    {
+        const char* env = getenv("MG_FFN_FUSED");
+        const int kblk = kblock_of(c.layer_fmt), total = c.ffn_dim / kblk;
+        const PhaseGeom& gu = e->mk_geom[PH_GU];
+        const int units = (c.ffn_dim + (1 << gu.ipg_shift) - 1) >> gu.ipg_shift;
+        int nkt = 0;
+        for (int cta = 0; cta < G; cta++) {
+            const int ub = unit_begin(units, cta, G), n = unit_begin(units, cta + 1, G) - ub;
+            if (n == 0) continue;
+            const int lo = ub << gu.ipg_shift, hi = std::min((ub + n) << gu.ipg_shift, c.ffn_dim);
+            nkt = std::max(nkt, ((hi - 1) / kblk - lo / kblk + 2) / 2);
+        }
+        const int Kl = 2 * nkt * kblk;
+        if (e->sh.size == 1 && !(env && env[0] == '0') && c.ffn_dim % kblk == 0 && nkt > 0 && total >= 2 * nkt &&
+            Kl <= 2 * MK_CONSUMERS && MK_NW * nkt <= slot / tile_bytes_of(c.layer_fmt)) {
+            PhaseGeom g{};
+            g.wide = 1; g.S = 1; g.RS = MK_NW; g.nkt = nkt; g.ipg_shift = 3;
+            g.tile_bytes = tile_bytes_of(c.layer_fmt); g.tpe = slot / g.tile_bytes;
+            g.kblocks = 2 * nkt; g.K = Kl; g.nfull = nkt;
+            e->mk_geom[PH_DOWN] = g;
+            e->ffn_fused = true;
+            const int stage = c.layer_fmt == FMT_F16 ? 0 : (xs_bytes_of(c.layer_fmt, Kl) + 15) & ~15;
+            xs_bytes = std::max(xs_bytes, stage + Kl * 4);
+        }
+    }
     const int xs = ((xs_bytes + 15) / 16) * 4;
     const int sc = (c.max_seq + 3) & ~3;
     int dev_max = 0;
@@ -868,8 +905,24 @@ int build_mega(mg_engine* e) {
         if (first) *first = ub;
         return unit_begin(units, cta + 1, G) - ub;
     };
+    // fused feed-forward block: a CTA with gate/up items multiplies ALL rows of the down projection
+    // by its own window of columns (first block: down_window_block)
+    auto gu_start = [&](int cta, int* n) {
+        int ub = 0;
+        *n = phase_units(PH_GU, cta, &ub);
+        return ub << e->mk_geom[PH_GU].ipg_shift;
+    };
+    auto units_of = [&](int p, int cta, int* first) {
+        if (p == PH_DOWN && e->ffn_fused) {
+            int n = 0;
+            gu_start(cta, &n);
+            if (first) *first = 0;
+            return n > 0 ? (c.dim + 7) >> 3 : 0;
+        }
+        return phase_units(p, cta, first);
+    };
     auto phase_bytes = [&](int p, int cta) {
-        return (unsigned long long)phase_units(p, cta, nullptr) * e->mk_geom[p].nkt * e->mk_geom[p].tile_bytes;
+        return (unsigned long long)units_of(p, cta, nullptr) * e->mk_geom[p].nkt * e->mk_geom[p].tile_bytes;
     };
     // a pipeline stage streams only the layers it owns (and lm_head only with the last layer)
     auto owned = [&](int l) { return l < L ? (l >= e->own_ls && l < e->own_le) : e->own_le >= L; };
@@ -911,16 +964,25 @@ int build_mega(mg_engine* e) {
             const int col = l < L ? l * 4 + p : L * 4;
             for (int cta = 0; cta < G; cta++) {
                 int ub = 0;
-                const int nrg = phase_units(p, cta, &ub);
+                const int nrg = units_of(p, cta, &ub);
+                const int kblk = kblock_of(s.fmt), all_blocks = s.K / kblk;
+                int kb0 = 0;                         // first block of columns of this CTA's tiles
+                if (p == PH_DOWN && e->ffn_fused) {
+                    int n = 0;
+                    kb0 = down_window_block(gu_start(cta, &n), kblk, all_blocks, g.nkt);
+                }
                 uint8_t* dst = tape.data() + off[(size_t)cta * ncol + col];
                 // tiles in the order the warps take them: pass, round, row-group of the pass, K-split
-                for (int rb = 0; rb * g.RS < nrg; rb++) {
-                    const int nrs = std::min(g.RS, nrg - rb * g.RS);
-                    for (int k0 = 0; k0 < g.nkt; k0 += g.S) {
-                        const int nkp = std::min(g.S, g.nkt - k0);
+                // (fused down projection: row-group by row-group, its k-tiles together)
+                const bool by_rg = p == PH_DOWN && e->ffn_fused;
+                const int oRS = by_rg ? 1 : g.RS, oS = by_rg ? g.nkt : g.S;
+                for (int rb = 0; rb * oRS < nrg; rb++) {
+                    const int nrs = std::min(oRS, nrg - rb * oRS);
+                    for (int k0 = 0; k0 < g.nkt; k0 += oS) {
+                        const int nkp = std::min(oS, g.nkt - k0);
                         for (int rs = 0; rs < nrs; rs++)
                             for (int kp = 0; kp < nkp; kp++, dst += g.tile_bytes) {
-                                const int rgi = ub + rb * g.RS + rs, kt = k0 + kp;
+                                const int rgi = ub + rb * oRS + rs, kt = k0 + kp;
                                 // source row and block of every row-slot (nullptr: the slot is empty)
                                 const uint8_t* sq[16];
                                 const unsigned short* sd[16];
@@ -928,9 +990,9 @@ int build_mega(mg_engine* e) {
                                     int j, which, kpar;
                                     slot_item(g.wide, s.rpi, sl, &j, &which, &kpar);
                                     const int item = rgi * ipg + j;
-                                    const int kb = g.wide ? 2 * kt + kpar : kt;
+                                    const int kb = kb0 + (g.wide ? 2 * kt + kpar : kt);
                                     sq[sl] = nullptr; sd[sl] = nullptr;
-                                    if (item >= s.items || kb >= g.kblocks) continue;
+                                    if (item >= s.items || kb >= all_blocks) continue;
                                     int mm[2], rr[2];
                                     item_rows(c, q_dim, p, item, mm, rr);
                                     const uint8_t* rowq = hq[mm[which]].data() + (size_t)rr[which] * rq;
@@ -1006,6 +1068,11 @@ int build_mega(mg_engine* e) {
     MG_CUDA(e, cudaMemset(e->xbuf, 0, nx * sizeof(Tagged)));
     MG_CUDA(e, ARENA_MALLOC(e, &e->mk_status, sizeof(MegaStatus)));
     MG_CUDA(e, cudaMemset(e->mk_status, 0, sizeof(MegaStatus)));
+    if (e->ffn_fused) {
+        MG_CUDA(e, ARENA_MALLOC(e, &e->mk_acc, ((size_t)3 * c.dim + 2) * 8));
+        MG_CUDA(e, cudaMemset(e->mk_acc, 0, ((size_t)3 * c.dim + 2) * 8));
+        e->mk_buf = 0; e->mk_ctr = 0;
+    }
     e->mega_ok = true;
     return MG_OK;
 }
@@ -1048,6 +1115,15 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
     }
     a.h_in = e->h; a.h_out = e->h; a.logits = e->logits; a.st = e->st; a.out_tokens = e->out_tokens;
     a.status = e->mk_status;
+    a.ffn_fused = e->ffn_fused ? 1 : 0;
+    if (e->ffn_fused) {
+        // the accumulators rotate and the arrival counter runs on from launch to launch
+        const unsigned int n = (unsigned)n_steps * (unsigned)(le - ls);
+        a.acc = e->mk_acc; a.ctr = reinterpret_cast<unsigned int*>(e->mk_acc + (size_t)3 * c.dim);
+        a.acc_buf0 = e->mk_buf; a.ctr0 = e->mk_ctr;
+        e->mk_buf = (int)((e->mk_buf + n) % 3u);
+        e->mk_ctr += n * (unsigned)e->num_sms;
+    }
     a.trace = e->trace_next ? e->mk_trace : nullptr;
     e->trace_next = false;
     void* params[] = {&a};
@@ -1074,6 +1150,11 @@ int check_mega_status(mg_engine* e) {
     MG_CUDA(e, cudaMemcpy(&s, e->mk_status, sizeof s, cudaMemcpyDeviceToHost));
     if (s.error) {
         cudaMemset(e->mk_status, 0, sizeof s);
+        if (e->mk_acc) {
+            // the aborted launch left the accumulators and the arrival counter anywhere: start over
+            cudaMemset(e->mk_acc, 0, ((size_t)3 * e->cfg.dim + 2) * 8);
+            e->mk_buf = 0; e->mk_ctr = 0;
+        }
         if (s.error == MK_ERR_POLL && s.who >= 0)
             return fail(e, MG_ERR_TIMEOUT, "persistent kernel: the rows of rank %d never arrived (exchange %u, CTA %d)", s.who, (unsigned)s.where, s.cta);
         return fail(e, MG_ERR_TIMEOUT, "persistent kernel: wait %d timed out (where %d, CTA %d)", s.error, s.where, s.cta);
@@ -1911,6 +1992,11 @@ int mg_arena_stats(const mg_engine* e, size_t* total, size_t* in_use, size_t* pe
     if (largest_free) *largest_free = e->arena.largest_free();
     if (outside) *outside = (int)e->arena.outside.size();
     return MG_OK;
+}
+
+int mg_decode_path(const mg_engine* e) {
+    if (!e) return MG_ERR_ARG;
+    return (e->mega_ok ? 1 : 0) | (e->mega_ok && e->ffn_fused ? 2 : 0) | (e->tp_fused ? 4 : 0);
 }
 
 int mg_set_wait_limit_ms(mg_engine* e, int ms) {

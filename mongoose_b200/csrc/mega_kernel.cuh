@@ -147,6 +147,13 @@ struct MegaArgs {
     MegaStatus* status;
     long long* trace;       // optional [grid][(n_layers + 1) * MK_EV] SM-clock stamps of CTA thread 0 (first step)
     int trace_step;         // always 0: the step whose stamps are kept
+    // Feed-forward block without a grid-wide exchange of its middle vector (one GPU only; see
+    // mk_down_fused): three rotating accumulators of dim 64-bit fixed-point sums and an arrival counter.
+    int ffn_fused;
+    int acc_buf0;           // accumulator (0..2) of this launch's first layer
+    unsigned int ctr0;      // value of the arrival counter when the launch starts
+    long long* acc;         // [3][dim]
+    unsigned int* ctr;
 };
 
 // ---------------------------------------------------------------------
@@ -228,6 +235,13 @@ __host__ inline PhaseGeom choose_geom(int fmt, int K, int items, int rpi, int gr
     }
     if (best_cost < 0) best.nkt = 0;     // no feasible layout
     return best;
+}
+
+// Fused feed-forward block: first block of columns of the down projection's window on the CTA whose
+// gate/up items start at `start` (the window is 2 nkt blocks wide and stays inside the matrix).
+__host__ __device__ inline int down_window_block(int start, int kblk, int total_blocks, int nkt) {
+    const int b = start / kblk, last = total_blocks - 2 * nkt;
+    return b < last ? b : last;
 }
 
 // QKV pair -> matrix (0 q, 1 k, 2 v) and its two rows.
@@ -585,12 +599,26 @@ __device__ __forceinline__ void mk_produce_phase(MkCtx& c, const MegaArgs& a, co
     }
 }
 
+// Fused down projection: the tiles lie row-group by row-group (nkt tiles each); an entry holds whole
+// sets of MK_NW row-groups, one per consumer warp (see mk_down_fused).
+__device__ __forceinline__ void mk_produce_down_fused(MkCtx& c, const MegaArgs& a, const uint8_t* src, int nrg) {
+    const PhaseGeom g = a.geom[PH_DOWN];
+    const int per_entry = (g.tpe / (MK_NW * g.nkt)) * MK_NW;        // row-groups per entry
+    for (int rg0 = 0; rg0 < nrg; rg0 += per_entry) {
+        mk_produce_entry(c, a, src, (uint32_t)(min(per_entry, nrg - rg0) * g.nkt * g.tile_bytes), PH_DOWN);
+        if (*c.abort_flag()) return;
+    }
+}
+
 __device__ __forceinline__ void mk_producer(MkCtx& c, const MegaArgs& a) {
     if ((threadIdx.x & 31) != 0) return;
     const unsigned long long* off = a.tape_off + (size_t)blockIdx.x * (a.n_layers * 4 + 2);
     for (int step = 0; step < a.n_steps; step++) {
         for (int l = a.ls; l < a.le; l++)
-            for (int p = 0; p < 4; p++) mk_produce_phase(c, a, a.tape + off[l * 4 + p], p, c.phase_tab()[8 + p]);
+            for (int p = 0; p < 4; p++) {
+                if (p == PH_DOWN && a.ffn_fused) mk_produce_down_fused(c, a, a.tape + off[l * 4 + p], c.phase_tab()[8 + p]);
+                else mk_produce_phase(c, a, a.tape + off[l * 4 + p], p, c.phase_tab()[8 + p]);
+            }
         if (a.le >= a.n_layers && a.head)
             mk_produce_phase(c, a, a.tape + off[a.n_layers * 4], PH_HEAD, c.phase_tab()[8 + PH_HEAD]);
     }
@@ -810,6 +838,62 @@ __device__ __forceinline__ void tile_mac(uint32_t tile, uint32_t bp, uint32_t sp
     }
 }
 
+// A wide tile whose input side (B words / fp16 weights: x values, and the scale pairs) is already in
+// registers: the same columns serve every row-group, so a warp that walks down the rows loads them once.
+struct TileIn {
+    uint2 B;
+    float4 sc;          // {s, off} of the even block, {s, off} of the odd one
+    float4 xe, xo;      // fp16 weights: this lane's four x values of the even / odd block
+};
+template <int FMT>
+__device__ __forceinline__ TileIn tile_in(uint32_t bp, uint32_t sp, const LaneGeom& L) {
+    TileIn in;
+    in.B = make_uint2(0u, 0u);
+    in.sc = make_float4(0.f, 0.f, 0.f, 0.f);
+    in.xe = in.xo = in.sc;
+    if (FMT == FMT_F16) { in.xe = lds128f(bp); in.xo = lds128f(bp + 64); }
+    else {
+        if (L.bvalid) in.B = lds64(bp);
+        in.sc = lds128f(sp);
+    }
+    return in;
+}
+template <int FMT>
+__device__ __forceinline__ void tile_mac_in(uint32_t tile, const TileIn& in, const LaneGeom& L, float& acc0, float& acc1) {
+    if (FMT == FMT_F16) {
+        const uint4 A = lds128(tile + L.a_off);
+        const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&A.x));
+        const float2 a1 = __half22float2(*reinterpret_cast<const __half2*>(&A.y));
+        const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&A.z));
+        const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(&A.w));
+        acc0 = fmaf(a0.x, in.xe.x, acc0); acc0 = fmaf(a0.y, in.xe.y, acc0);
+        acc0 = fmaf(a1.x, in.xe.z, acc0); acc0 = fmaf(a1.y, in.xe.w, acc0);
+        acc1 = fmaf(b0.x, in.xo.x, acc1); acc1 = fmaf(b0.y, in.xo.y, acc1);
+        acc1 = fmaf(b1.x, in.xo.z, acc1); acc1 = fmaf(b1.y, in.xo.w, acc1);
+        return;
+    }
+    const uint32_t dd = lds32(tile + L.d_off);
+    int d[4];
+    if (FMT == FMT_Q8_0) {
+        const uint4 A = lds128(tile + L.a_off);
+        mma_s8s8(d, A.x, A.y, A.z, A.w, in.B);
+    } else {
+        const uint2 A = lds64(tile + L.a_off);
+        mma_u8s8(d, A.x & 0x0f0f0f0fu, A.y & 0x0f0f0f0fu, (A.x >> 4) & 0x0f0f0f0fu, (A.y >> 4) & 0x0f0f0f0fu, in.B);
+    }
+    const float2 df = __half22float2(*reinterpret_cast<const __half2*>(&dd));
+    const float c0 = __int_as_float(d[0] + 0x4B400000) - 12582912.0f;
+    const float c1 = __int_as_float(d[3] + 0x4B400000) - 12582912.0f;
+    if (FMT == FMT_Q8_0) {
+        acc0 = fmaf(df.x * in.sc.x, c0, acc0);
+        acc1 = fmaf(df.y * in.sc.z, c1, acc1);
+    } else {
+        const float oe = L.t == 0 ? in.sc.y : 0.f, oo = L.t == 0 ? in.sc.w : 0.f;
+        acc0 = fmaf(df.x, fmaf(in.sc.x, c0, oe), acc0);
+        acc1 = fmaf(df.y, fmaf(in.sc.z, c1, oo), acc1);
+    }
+}
+
 // The tiles of one pass for this warp: ring entries in order, whole rounds per entry, then the
 // incomplete last round.  Every warp observes and releases every entry, also those it has no tile
 // in (a warp that skipped ahead could meet a slot whose barrier is a whole ring revolution behind
@@ -911,7 +995,49 @@ __device__ __forceinline__ void xq_store_fast(uint32_t dst, uint32_t sc_addr, bo
 // vector's length: the shuffles and conversions of the strides then overlap instead of queueing
 // behind branches).
 // ---------------------------------------------------------------------
-enum : int { SRC_POLL = 0, SRC_EMBED = 1, SRC_PLAIN = 2 };
+
+// ---------------------------------------------------------------------
+// Fixed-point accumulators.  Where many CTAs add partial sums into one vector, they add 64-bit
+// integers (value * 2^36, rounded): integer addition is associative, so the sum does not depend on
+// the order in which the CTAs arrive and a decode step stays reproducible bit for bit.  Range
+// +-1.3e8, resolution 1.5e-11: far outside / below anything a hidden state holds.
+// ---------------------------------------------------------------------
+constexpr float MK_FIX = 68719476736.0f;          // 2^36
+constexpr float MK_UNFIX = 1.0f / 68719476736.0f;
+// v * 2^36 as a 64-bit integer without the 64-bit conversion (a long instruction sequence): the
+// integer part of v * 2^12 and the remainder * 2^24 are two 32-bit conversions.  Exact for
+// |v| < 2^19 (every fp32 there is a multiple of 2^-36 unless |v| < 2^-12, which rounds to 2^-36).
+__device__ __forceinline__ long long mk_fix(float v) {
+    const float x = v * 4096.0f;
+    const int hi = __float2int_rn(x);
+    const int lo = __float2int_rn((x - (float)hi) * 16777216.0f);
+    return ((long long)hi << 24) + (long long)lo;
+}
+__device__ __forceinline__ float mk_unfix(unsigned int lo, unsigned int hi) {
+    return __ll2float_rn((long long)(((unsigned long long)hi << 32) | (unsigned long long)lo)) * MK_UNFIX;
+}
+__device__ __forceinline__ void red_add_s64(long long* p, long long v) {
+    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// One thread waits until the arrival counter has reached `target` (wrap-safe), bounded like every wait.
+__device__ __noinline__ void mk_wait_ctr(volatile int* abort_flag, MegaStatus* status, long long limit,
+                                         const unsigned int* ctr, unsigned int target) {
+    if ((int)(ld_acquire_u32(ctr) - target) >= 0) return;
+    const long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if ((int)(ld_acquire_u32(ctr) - target) >= 0) return;
+        if (*abort_flag) return;
+        if (global_ns() - t0 > limit) { mk_fail_impl(abort_flag, status, MK_ERR_POLL, (int)target); return; }
+    }
+}
+
+enum : int { SRC_POLL = 0, SRC_EMBED = 1, SRC_PLAIN = 2, SRC_ACC = 3 };
 constexpr int MK_STRIDE = 2 * MK_CONSUMERS;
 
 struct StageSrc {
@@ -949,6 +1075,9 @@ __device__ __forceinline__ void stage_issue(const MegaArgs& a, const StageSrc& s
             if (NORMED) nw[k] = *reinterpret_cast<const float2*>(s.norm_w + i);
             if (s.kind == SRC_POLL) {
                 if (!TP || !NORMED) r[k] = ld_poll16(s.src + i);
+            } else if (!TP && s.kind == SRC_ACC) {
+                // two 64-bit sums, complete: the arrival counter was waited for
+                r[k] = ld_poll16(s.src + i);
             } else {
                 const float2 v = mk_direct_pair(a, s.kind, s.token, i);
                 r[k].x = __float_as_uint(v.x); r[k].z = __float_as_uint(v.y);
@@ -972,6 +1101,7 @@ __device__ __forceinline__ void stage_finish(const MegaArgs& a, MkCtx& c, const 
         v0[k] = 0.f; v1[k] = 0.f;
         if (i < s.n) {
             if (TP && NORMED && s.kind == SRC_POLL) mk_poll2_sum(c, s.src + i, a.dim, a.tp_n, s.tag, v0[k], v1[k]);
+            else if (!TP && s.kind == SRC_ACC) { v0[k] = mk_unfix(r[k].x, r[k].y); v1[k] = mk_unfix(r[k].z, r[k].w); }
             else { mk_poll2_finish(c, s.src + i, s.tag, r[k]); v0[k] = __uint_as_float(r[k].x); v1[k] = __uint_as_float(r[k].z); }
         }
     }
@@ -1079,6 +1209,11 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
 
     // ---- 2. poll and stage the input, barrier ----
     float ss = 0.f;
+    if (!TP && s.kind == SRC_ACC) {
+        // the hidden state sits in an accumulator that is complete once every CTA has arrived
+        if (tid == 0) mk_wait_ctr(c.abort_flag(), c.status(), a.wait_cycles, a.ctr, s.tag);
+        consumer_sync();
+    }
     if (FMT != FMT_F16 && ((s.n >> 5) & 1) && tid == 0)    // odd number of blocks: the unused half pair's scale must be finite
         *reinterpret_cast<float2*>(mk_smem + c.xs_off + xq_plane_bytes(s.n) + (s.n >> 5) * 8) = make_float2(0.f, 0.f);
     if (s.n <= MK_STRIDE) {
@@ -1146,6 +1281,15 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
     mk_trace(a, 0, trace_base + 11 + 3 * (P == PH_HEAD ? 0 : P));
     consumer_sync();                     // every warp is done with xs; the partial sums are published
     mk_trace(a, 0, trace_base + 12 + 3 * (P == PH_HEAD ? 0 : P));
+    const bool to_mid = P == PH_GU && !TP && a.ffn_fused;      // gate/up feeding the down projection of this very CTA
+    if (to_mid) {
+        // the middle vector of this CTA's down projection: the elements it owns come from the epilogue
+        // below, every other position of the window is zero (xs is free: the tiles are done)
+        const int e0 = c.phase_tab()[5], lo = ub << g.ipg_shift, hi = min((ub + nrg) << g.ipg_shift, lim);
+        float* mid = reinterpret_cast<float*>(mk_smem + c.xs_off + c.phase_tab()[6]);
+        for (int j = tid; j < a.geom[PH_DOWN].K; j += MK_CONSUMERS)
+            if (e0 + j < lo || e0 + j >= hi) mid[j] = 0.f;
+    }
 
     // ---- 4. epilogue: whole warps (the shuffles need every lane) ----
     if ((tid & ~31) < nslots) {
@@ -1200,7 +1344,9 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
                         st_tagged(dst + e_r1, __half2float(__float2half_rn(t1)), tag_out);
                     }
                 } else if (P == PH_GU) {
-                    st_tagged(a.xmid + e_item, (a.dbg & 1) ? v * (1.0f / (1.0f + expf(-v))) * v1 : v * __fdividef(1.0f, 1.0f + __expf(-v)) * v1, tag_out);
+                    const float m = v * __fdividef(1.0f, 1.0f + __expf(-v)) * v1;
+                    if (to_mid) reinterpret_cast<float*>(mk_smem + c.xs_off + c.phase_tab()[6])[e_item - c.phase_tab()[5]] = m;
+                    else st_tagged(a.xmid + e_item, m, tag_out);
                 } else if (!TP) {
                     st_tagged((P == PH_WO ? a.xhm : a.xh) + e_item, e_res + v, tag_out);
                 } else {
@@ -1213,6 +1359,114 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
         }
     }
     mk_trace(a, 0, trace_base + 2 * (P == PH_HEAD ? 0 : P) + 1);
+}
+
+// ---------------------------------------------------------------------
+// Down projection without an exchange of the middle vector (one GPU).
+// A CTA's gate/up rows are a contiguous run of FFN features, so the silu(g) * u values it has just
+// produced are exactly a window of the down projection's input.  Instead of publishing them and
+// waiting for everybody else's, the CTA multiplies ITS window (2 nkt blocks of columns, all rows)
+// and adds the partial sums of all rows into the layer's accumulator; the other CTAs do the same
+// for their windows.  What replaces the exchange is an arrival counter: a consumer of the hidden
+// state waits until all CTAs have arrived, then reads the sums.  Three accumulators rotate: while
+// layer q adds into buffer q % 3, every CTA also clears its share of buffer (q + 1) % 3, which was
+// last read while layer q - 1 was staged - and every CTA has passed that point, since this CTA has
+// seen the counter of layer q - 1 complete.  The residual enters the same way (each CTA adds its
+// share of the hidden state that entered the block).
+//   Weights: wide tiles, row-group = 8 rows, nkt k-tiles = the window; warp w takes row-groups
+//   w, w + 15, ...; the sums leave the warp straight from registers (8 lanes x 8 bytes per tile row).
+// ---------------------------------------------------------------------
+template <int FMT>
+__device__ __forceinline__ void mk_down_fused(const MegaArgs& a, MkCtx& c, long long* acc_cur, long long* acc_next, int trace_base) {
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const PhaseGeom& g = a.geom[PH_DOWN];
+    const int nrg = c.phase_tab()[8 + PH_DOWN];
+    const uint32_t sm0 = smem_u32(mk_smem);
+#ifdef MK_PROBE_P
+    c.probe_base = MK_PROBE_P == PH_DOWN ? trace_base : -1;
+#endif
+    MK_ESTAMP(23);
+    // This CTA's share of the rows, [lo, hi): the residual enters there, and the same rows of the
+    // accumulator of the layer after this one are cleared.
+    const int lo = unit_begin(a.dim, blockIdx.x, gridDim.x), hi = unit_begin(a.dim, blockIdx.x + 1, gridDim.x);
+    for (int i = lo + tid; i < hi; i += MK_CONSUMERS) {
+        asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(acc_next + i), "l"(0ll) : "memory");
+        red_add_s64(acc_cur + i, mk_fix(c.hs()[i]));
+    }
+    MK_ESTAMP(25);
+    consumer_sync();                                  // the window of the middle vector is complete
+    MK_ESTAMP(26);
+    if (nrg > 0) {
+        if (FMT != FMT_F16) {
+            // fixed point: thread tid takes the pair (2 tid, 2 tid + 1) of the window; whole warps (a warp = two blocks)
+            if (tid < (g.K >> 1)) {
+                const float2 u = *reinterpret_cast<const float2*>(mk_smem + c.xs_off + c.phase_tab()[6] + 8 * tid);
+                const uint32_t st_dst = sm0 + c.xs_off + (uint32_t)((tid >> 4) * 96 + ((tid & 7) >> 1) * 8 + ((tid >> 3) & 1) * 4 + (tid & 1) * 2);
+                const uint32_t st_sc = sm0 + c.xs_off + (uint32_t)xq_plane_bytes(g.K) + (uint32_t)(tid >> 4) * 8u;
+                xq_store_fast(st_dst, st_sc, true, (tid & 15) == 0, u.x, u.y, FMT == FMT_Q4_0);
+            }
+            consumer_sync();
+        }
+        mk_trace(a, 0, trace_base + 2 * PH_DOWN);
+        const LaneGeom L = lane_geom<FMT>(c, lane, 1, g.K);
+        const float wt = FMT == FMT_F16 ? 1.0f : L.t == 0 ? 1.0f : L.t == 1 ? 256.0f : L.t == 2 ? 65536.0f : 0.0f;
+        constexpr uint32_t kBStep = FMT == FMT_F16 ? 128u : 192u, kSStep = 16u;
+        const int nkt = g.nkt;
+        const int per_entry = (g.tpe / (MK_NW * nkt)) * MK_NW;      // row-groups per ring entry
+        const uint32_t rg_bytes = (uint32_t)(nkt * g.tile_bytes);
+        const TileIn in0 = tile_in<FMT>(L.b_addr, L.s_addr, L);     // the whole window when it is one k-tile wide
+        for (int rg0 = 0; rg0 < nrg; rg0 += per_entry) {
+            const int n_here = min(per_entry, nrg - rg0);
+            mk_wait_bar(c, &c.full()[c.slot], c.par, MK_ERR_FULL);
+            MK_ESTAMP(32 + 2 * (rg0 / per_entry));
+            const uint32_t base = sm0 + (uint32_t)c.slot * (uint32_t)a.slot_bytes;
+            // this warp's row-groups of the entry: w, w + 15, ...; four of them in flight
+            for (int j = w; j < n_here; j += 4 * MK_NW) {
+                float s0[4], s1[4];
+                bool ok[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) { s0[u] = 0.f; s1[u] = 0.f; ok[u] = j + u * MK_NW < n_here; }
+                const uint32_t t0 = base + (uint32_t)j * rg_bytes;
+                if (nkt == 1) {
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+                        if (ok[u]) tile_mac_in<FMT>(t0 + (uint32_t)(u * MK_NW) * rg_bytes, in0, L, s0[u], s1[u]);
+                } else {
+                    for (int kt = 0; kt < nkt; kt++) {
+                        const TileIn in = tile_in<FMT>(L.b_addr + kt * kBStep, L.s_addr + kt * kSStep, L);
+#pragma unroll
+                        for (int u = 0; u < 4; u++)
+                            if (ok[u]) tile_mac_in<FMT>(t0 + (uint32_t)(u * MK_NW) * rg_bytes + (uint32_t)(kt * g.tile_bytes), in, L, s0[u], s1[u]);
+                    }
+                }
+                // even block + odd block of the same row, then the quad's digit planes
+                float v[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) v[u] = (s0[u] + s1[u]) * wt;
+#pragma unroll
+                for (int u = 0; u < 4; u++) v[u] += __shfl_xor_sync(MG_FULL_MASK, v[u], 1);
+#pragma unroll
+                for (int u = 0; u < 4; u++) v[u] += __shfl_xor_sync(MG_FULL_MASK, v[u], 2);
+                const int row = ((rg0 + j) << 3) + (lane >> 2);
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int r = row + u * 8 * MK_NW;
+                    if (ok[u] && L.t == 0 && r < a.dim) red_add_s64(acc_cur + r, mk_fix(v[u]));
+                }
+            }
+            MK_ESTAMP(33 + 2 * (rg0 / per_entry));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&c.empty()[c.slot]);
+            c.advance();
+        }
+    }
+    mk_trace(a, 0, trace_base + 11 + 3 * PH_DOWN);
+    consumer_sync();                                  // every warp's additions have been issued
+    mk_trace(a, 0, trace_base + 12 + 3 * PH_DOWN);
+    if (tid == 0) {
+        __threadfence();
+        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(a.ctr), "r"(1u) : "memory");
+    }
 }
 
 // ---------------------------------------------------------------------
@@ -1461,6 +1715,8 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
     const int pos0 = a.st->pos;
     int token = a.st->token;
     const bool do_head = a.le >= L && a.head;
+    const bool fused = !TP && a.ffn_fused;
+    int qn = 0;                              // layers finished in this launch
 
     for (int step = 0; step < a.n_steps; step++) {
         const unsigned int ep = a.epoch + (unsigned)step * (unsigned)(L * MK_EPOCHS_PER_LAYER + 8);
@@ -1476,9 +1732,16 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
         unsigned long long best = 0ull;
 
         // tags of layer l: +1 q/kv, +2 attn, +3 h after wo, +4 ffn mid, +5 h after down
+        // (fused feed-forward block: no +4 / +5; the hidden state after the block is accumulator
+        //  (acc_buf0 + qn) % 3, complete when the arrival counter reads ctr0 + (qn + 1) * grid)
 #define MK_LAYER(FMT)                                                                                              \
         {                                                                                                          \
             StageSrc s0{SRC_POLL, a.xh, tag_prev_h, a.dim, a.norms + (size_t)l * 2 * a.dim, token};                \
+            if (fused) {                                                                                           \
+                s0.kind = SRC_ACC;                                                                                 \
+                s0.src = reinterpret_cast<const Tagged*>(a.acc + (size_t)((a.acc_buf0 + qn + 2) % 3) * a.dim); \
+                s0.tag = a.ctr0 + (unsigned)qn * gridDim.x;                                                        \
+            }                                                                                                      \
             if (l == a.ls) s0.kind = a.embed ? SRC_EMBED : SRC_PLAIN;                                              \
             mk_run_phase<PH_QKV, FMT, TP>(a, c, s0, l, base + 1, l * MK_EV, best);                                 \
             if ((int)blockIdx.x < a.n_heads) {                                                                     \
@@ -1492,8 +1755,15 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
             mk_run_phase<PH_WO, FMT, TP>(a, c, s1, l, base + 3, l * MK_EV, best);                                  \
             const StageSrc s2{SRC_POLL, a.xhm, base + 3, a.dim, a.norms + (size_t)l * 2 * a.dim + a.dim, token};   \
             mk_run_phase<PH_GU, FMT, TP>(a, c, s2, l, base + 4, l * MK_EV, best);                                  \
-            const StageSrc s3{SRC_POLL, a.xmid, base + 4, a.ffn_dim, nullptr, token};                              \
-            mk_run_phase<PH_DOWN, FMT, TP>(a, c, s3, l, base + 5, l * MK_EV, best);                                \
+            if (fused) {                                                                                           \
+                mk_down_fused<FMT>(a, c, a.acc + (size_t)((a.acc_buf0 + qn) % 3) * a.dim,           \
+                                   a.acc + (size_t)((a.acc_buf0 + qn + 1) % 3) * a.dim, l * MK_EV); \
+                mk_trace(a, 0, l * MK_EV + 2 * PH_DOWN + 1);                                                       \
+            } else {                                                                                               \
+                const StageSrc s3{SRC_POLL, a.xmid, base + 4, a.ffn_dim, nullptr, token};                          \
+                mk_run_phase<PH_DOWN, FMT, TP>(a, c, s3, l, base + 5, l * MK_EV, best);                            \
+            }                                                                                                      \
+            qn++;                                                                                                  \
         }
         for (int l = a.ls; l < a.le; l++) {
             const unsigned int base = ep + (unsigned)l * MK_EPOCHS_PER_LAYER;
@@ -1506,7 +1776,12 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
 #undef MK_LAYER
         if (do_head) {
             const unsigned int base = ep + (unsigned)L * MK_EPOCHS_PER_LAYER;
-            const StageSrc sh{SRC_POLL, a.xh, base - MK_EPOCHS_PER_LAYER + 5, a.dim, a.final_norm, token};
+            StageSrc sh{SRC_POLL, a.xh, base - MK_EPOCHS_PER_LAYER + 5, a.dim, a.final_norm, token};
+            if (fused) {
+                sh.kind = SRC_ACC;
+                sh.src = reinterpret_cast<const Tagged*>(a.acc + (size_t)((a.acc_buf0 + qn + 2) % 3) * a.dim);
+                sh.tag = a.ctr0 + (unsigned)qn * gridDim.x;
+            }
             if (a.head_fmt == FMT_Q8_0) mk_run_phase<PH_HEAD, FMT_Q8_0, TP>(a, c, sh, L, base + 5, L * MK_EV, best);
             else if (a.head_fmt == FMT_Q4_0) mk_run_phase<PH_HEAD, FMT_Q4_0, TP>(a, c, sh, L, base + 5, L * MK_EV, best);
             else mk_run_phase<PH_HEAD, FMT_F16, TP>(a, c, sh, L, base + 5, L * MK_EV, best);
@@ -1516,7 +1791,15 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
             // partial layer range: CTA 0 hands the hidden state back
             if (blockIdx.x == 0 && a.h_out && step == a.n_steps - 1 && a.le > a.ls) {
                 const unsigned int tag_final_h = ep + (unsigned)(a.le - 1) * MK_EPOCHS_PER_LAYER + 5;
-                if (!TP) {
+                if (fused) {
+                    if (tid == 0) mk_wait_ctr(c.abort_flag(), c.status(), a.wait_cycles, a.ctr, a.ctr0 + (unsigned)qn * gridDim.x);
+                    consumer_sync();
+                    const Tagged* src = reinterpret_cast<const Tagged*>(a.acc + (size_t)((a.acc_buf0 + qn + 2) % 3) * a.dim);
+                    for (int i = tid; i < a.dim; i += MK_CONSUMERS) {
+                        const uint2 w = ld_poll8(src + i);
+                        c.hs()[i] = mk_unfix(w.x, w.y);
+                    }
+                } else if (!TP) {
                     mk_gather(c, a.xh, tag_final_h, c.hs(), a.dim);
                 } else {
                     for (int i = 2 * tid; i < a.dim; i += 2 * MK_CONSUMERS) {
@@ -1609,6 +1892,15 @@ __global__ void __launch_bounds__(MK_THREADS, 1) mega_decode_kernel(const __grid
                 const int S = a.geom[p].S, rs = w / S;
                 c.warp_tab()[p * 16 + w] = (unsigned short)(rs < a.geom[p].RS ? (rs | ((w - rs * S) << 8)) : 255);
             }
+        }
+        if (a.ffn_fused) {
+            // down projection on this CTA's own window of the middle vector: all row-groups, or none
+            const int kblk = kblock_of(a.layer_fmt);
+            const int start = c.phase_tab()[PH_GU] << a.geom[PH_GU].ipg_shift;
+            c.phase_tab()[PH_DOWN] = 0;
+            c.phase_tab()[8 + PH_DOWN] = c.phase_tab()[8 + PH_GU] > 0 ? (a.dim + 7) >> 3 : 0;
+            c.phase_tab()[5] = down_window_block(start, kblk, a.ffn_dim / kblk, a.geom[PH_DOWN].nkt) * kblk;
+            c.phase_tab()[6] = a.layer_fmt == FMT_F16 ? 0 : (xs_bytes_of(a.layer_fmt, a.geom[PH_DOWN].K) + 15) & ~15;
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -389,6 +389,11 @@ class CUDAFusedInference:
         raise with MG_ERR_TIMEOUT (the reference's WaitMailbox spins without one)."""
         self._check(self._lib.mg_set_wait_limit_ms(self._h, int(ms)), "SetWaitLimit")
 
+    def DecodePath(self) -> int:
+        """Bit 0: persistent kernel; bit 1: its feed-forward block without an exchange of the middle
+        vector; bit 2: tensor-parallel exchange inside the kernels (after BuildFusedDispatch)."""
+        return self._lib.mg_decode_path(self._h)
+
     def TpInitAbsentPeers(self, size: int) -> None:
         """Test aid without a counterpart in the reference: make this engine rank 0 of a `size`-rank
         tensor-parallel group whose other ranks do not exist, so the bounded waits inside the

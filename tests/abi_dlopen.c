@@ -21,7 +21,7 @@ static const char* kNames[] = {
     "mg_create", "mg_destroy", "mg_num_weights", "mg_set_weight", "mg_set_weight_raw", "mg_build",
     "mg_reset_kv", "mg_partial_step", "mg_partial_step_continue", "mg_export_hidden", "mg_step_token",
     "mg_generate", "mg_enqueue_greedy", "mg_set_cursor", "mg_get_cursor", "mg_sync", "mg_dequant_rows",
-    "mg_read_kv", "mg_trace_step", "mg_set_wait_limit_ms", "mg_tp_init_absent_peers", "mg_device_alloc", "mg_device_free", "mg_device_upload",
+    "mg_read_kv", "mg_trace_step", "mg_set_wait_limit_ms", "mg_decode_path", "mg_tp_init_absent_peers", "mg_device_alloc", "mg_device_free", "mg_device_upload",
     "mg_device_download", "mg_device_zero", "mg_arena_stats", "mg_step_layer_resident", "mg_set_vnode_count",
     "mg_vnode_count", "mg_record_stage_done", "mg_wait_stage_done", "mg_sync_stream1",
     "mg_partial_step_continue_on_stream1", "mg_queue_hidden_to_l3_on_stream1", "mg_upload_hidden", "mg_graph_launch", "mg_validate_replay",

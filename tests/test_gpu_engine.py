@@ -26,20 +26,39 @@ SMALL = [mc.TINY, mc.TINY_Q4,
 # Every case runs on the engine's default path (the persistent kernel where the model fits it);
 # the cases below run once more on the graph of per-phase kernels, which larger models use.
 KERNELS_PATH = ["tiny", "tiny-q4_0", "tiny-hd64", "tiny-hd128-f16", "qwen-width-2L-q4", "tinyllama-width-2L"]
-CASES = [(c, False) for c in SMALL] + [(c, True) for c in SMALL if c.name in KERNELS_PATH]
+# ... and these once more on the persistent kernel with the middle vector of the feed-forward block
+# exchanged between the CTAs (what tensor-parallel ranks run; one GPU keeps it inside each CTA)
+EXCHANGE_PATH = ["tiny", "tiny-q4_0", "tiny-hd128-f16", "tinyllama-width-2L"]
+CASES = ([(c, "") for c in SMALL] + [(c, "kernels") for c in SMALL if c.name in KERNELS_PATH] +
+         [(c, "exchange") for c in SMALL if c.name in EXCHANGE_PATH])
 
 
-@pytest.fixture(params=CASES, ids=lambda p: p[0].name + ("+kernels" if p[1] else ""))
+@pytest.fixture(params=CASES, ids=lambda p: p[0].name + ("+" + p[1] if p[1] else ""))
 def pair(request, cuda, oracle, mglib, monkeypatch):
-    cfg, kernels_path = request.param
-    if kernels_path:
+    cfg, path = request.param
+    if path == "kernels":
         monkeypatch.setenv("MG_NO_MEGA", "1")     # read when the engine is created
+    if path == "exchange":
+        monkeypatch.setenv("MG_FFN_FUSED", "0")   # read when the engine is built
     eng = CUDAFusedInference(cfg)
+    eng.intended_path = path
     om = oracle.OracleModel(cfg)
     blocks = fill_models(cfg, seed=1, jitter=0.1, engine=eng, oracle_model=om, raw_slots=True)
     yield cfg, eng, om, blocks
     eng.close()
     om.close()
+
+
+def test_the_intended_decode_path_runs(pair):
+    cfg, eng, om, _ = pair
+    eng.BuildFusedDispatch()
+    bits = eng.DecodePath()
+    if eng.intended_path == "kernels":
+        assert bits & 1 == 0
+    elif eng.intended_path == "exchange":
+        assert bits & 3 == 1
+    elif cfg.name != "qwen7b-width-1L" or bits & 1:
+        assert bits & 3 == 3, "one GPU: persistent kernel with the feed-forward block kept inside each CTA"
 
 
 def test_dequantized_weights_bit_exact(pair, oracle):
