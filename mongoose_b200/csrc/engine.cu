@@ -1085,7 +1085,7 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
     MegaArgs a{};
     a.dim = c.dim; a.kv_dim = c.kv_dim; a.head_dim = c.head_dim; a.n_heads = c.n_heads; a.n_kv_heads = c.n_kv_heads;
     a.ffn_dim = c.ffn_dim; a.vocab = c.vocab; a.n_layers = L; a.max_seq = c.max_seq;
-    a.layer_fmt = c.layer_fmt; a.head_fmt = c.head_fmt; a.eps = c.rms_eps; a.inv_dim = 1.0f / (float)c.dim; a.dbg = getenv("MG_DBG") ? atoi(getenv("MG_DBG")) : 0;
+    a.layer_fmt = c.layer_fmt; a.head_fmt = c.head_fmt; a.eps = c.rms_eps; a.inv_dim = 1.0f / (float)c.dim;
     a.ls = ls; a.le = le; a.head = (le >= L) ? head : 0; a.embed = (mode == MODE_EMBED); a.n_steps = n_steps;
     a.epoch = e->epoch;
     e->epoch += (unsigned)n_steps * (unsigned)(L * MK_EPOCHS_PER_LAYER + 8);

@@ -35,6 +35,15 @@
 //    fused epilogue (bias + RoPE + fp16 rounding, residual add, SiLU * up,
 //    argmax).  fp16 weights use the same tiles with fp32 FMAs.
 //
+//  * Feed-forward block on one GPU.  A CTA's gate/up rows are a contiguous run
+//    of FFN features, so its silu(g) * u values are a window of the down
+//    projection's input.  The CTA multiplies that window by ALL rows of the
+//    down matrix and adds the row sums, as 64-bit fixed point (associative, so
+//    the result does not depend on arrival order), into one of three rotating
+//    accumulators; an arrival counter tells the next phase when the sums are
+//    complete.  The FFN-wide middle vector never crosses SMs.  Tensor-parallel
+//    ranks keep the exchanged middle vector (their partial sums cross GPUs).
+//
 // Every wait (mbarrier, exchange poll) is bounded by a deadline in SM clocks
 // (MegaArgs::wait_cycles, about 1 s by default); on expiry the kernel records
 // an error code, stops waiting everywhere and runs to completion on whatever
@@ -97,7 +106,6 @@ struct MegaArgs {
     int layer_fmt, head_fmt;
     float eps;
     float inv_dim;          // 1 / dim
-    int dbg;                // experiment switches
     int ls, le;             // layer range
     int head;               // HEAD_NONE / HEAD_ARGMAX / HEAD_LOGITS (0/1/2)
     int embed;              // 1: hidden state from the embedding row of st->token, 0: from h_in
@@ -407,7 +415,7 @@ __device__ __forceinline__ void mk_trace(const MegaArgs& a, int step, int ev) {
 // instructions each to the code a phase runs through (the kernel's speed is bounded by the length
 // of the instruction stream of a phase as much as by its data).  All waits are bounded.
 __device__ __noinline__ void mk_wait_bar_slow(volatile int* abort_flag, MegaStatus* status, long long limit,
-                                              uint32_t bar_s, uint32_t parity, int code, int where, unsigned sleep_ns) {
+                                              uint32_t bar_s, uint32_t parity, int code, int where) {
     if (*abort_flag) return;
     const long long t0 = global_ns();
     for (unsigned int it = 1;; ++it) {
@@ -418,9 +426,6 @@ __device__ __noinline__ void mk_wait_bar_slow(volatile int* abort_flag, MegaStat
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok) : "r"(bar_s), "r"(parity) : "memory");
         if (ok) return;
-        // a spinning try_wait occupies the shared-memory pipe that the working warps' loads and shuffles
-        // go through: back off between attempts (longer for the producer, which runs a ring ahead)
-        if (sleep_ns) __nanosleep(sleep_ns);
         if ((it & 63u) == 0u) {
             if (*abort_flag) return;
             if (*(volatile int*)&status->error) { *abort_flag = 1; return; }
@@ -430,8 +435,7 @@ __device__ __noinline__ void mk_wait_bar_slow(volatile int* abort_flag, MegaStat
 }
 __device__ __forceinline__ void mk_wait_bar(MkCtx& c, unsigned long long* bar, uint32_t parity, int code) {
     if (mbar_try(bar, parity)) return;
-    mk_wait_bar_slow(c.abort_flag(), c.status(), c.a.wait_cycles, smem_u32(bar), parity, code, (int)c.entry,
-                     code == MK_ERR_EMPTY ? (unsigned)(c.a.dbg >> 8) : 0u);
+    mk_wait_bar_slow(c.abort_flag(), c.status(), c.a.wait_cycles, smem_u32(bar), parity, code, (int)c.entry);
 }
 
 // Re-read a pair of exchange words (16-byte aligned) until both carry `tag`; sys = the words may be
@@ -1300,7 +1304,7 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
             const float4 r0 = lds128f(rr), r1 = lds128f(rr + 16), r2 = lds128f(rr + 32), r3 = lds128f(rr + 48);
             const float t = ((r0.x + r0.y) + (r0.z + r0.w)) + ((r1.x + r1.y) + (r1.z + r1.w)) +
                             (((r2.x + r2.y) + (r2.z + r2.w)) + ((r3.x + r3.y) + (r3.z + r3.w)));
-            scale = (a.dbg & 4) ? 1.0f / sqrtf(t / (float)a.dim + a.eps) : rsqrtf(fmaf(t, a.inv_dim, a.eps));
+            scale = rsqrtf(fmaf(t, a.inv_dim, a.eps));
         }
         MK_STAMP(29);
         const int nq = sp >> 2;
