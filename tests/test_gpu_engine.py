@@ -26,11 +26,13 @@ SMALL = [mc.TINY, mc.TINY_Q4,
 # Every case runs on the engine's default path (the persistent kernel where the model fits it);
 # the cases below run once more on the graph of per-phase kernels, which larger models use.
 KERNELS_PATH = ["tiny", "tiny-q4_0", "tiny-hd64", "tiny-hd128-f16", "qwen-width-2L-q4", "tinyllama-width-2L"]
-# ... and these once more on the persistent kernel with the middle vector of the feed-forward block
-# exchanged between the CTAs (what tensor-parallel ranks run; one GPU keeps it inside each CTA)
-EXCHANGE_PATH = ["tiny", "tiny-q4_0", "tiny-hd128-f16", "tinyllama-width-2L"]
+# ... and these once more on the persistent kernel with each way of running the feed-forward block
+# forced: the middle vector exchanged between the CTAs (what tensor-parallel ranks run), or kept
+# inside each CTA with the down projection's sums meeting in accumulators.  By default the engine
+# picks per model shape (Qwen2.5-0.5B and 7B-class widths: inside the CTA).
+FFN_PATHS = ["tiny", "tiny-q4_0", "tiny-hd128-f16", "tinyllama-width-2L"]
 CASES = ([(c, "") for c in SMALL] + [(c, "kernels") for c in SMALL if c.name in KERNELS_PATH] +
-         [(c, "exchange") for c in SMALL if c.name in EXCHANGE_PATH])
+         [(c, "exchange") for c in SMALL if c.name in FFN_PATHS] + [(c, "fused") for c in SMALL if c.name in FFN_PATHS])
 
 
 @pytest.fixture(params=CASES, ids=lambda p: p[0].name + ("+" + p[1] if p[1] else ""))
@@ -38,8 +40,8 @@ def pair(request, cuda, oracle, mglib, monkeypatch):
     cfg, path = request.param
     if path == "kernels":
         monkeypatch.setenv("MG_NO_MEGA", "1")     # read when the engine is created
-    if path == "exchange":
-        monkeypatch.setenv("MG_FFN_FUSED", "0")   # read when the engine is built
+    if path in ("exchange", "fused"):
+        monkeypatch.setenv("MG_FFN_FUSED", "0" if path == "exchange" else "1")   # read when the engine is built
     eng = CUDAFusedInference(cfg)
     eng.intended_path = path
     om = oracle.OracleModel(cfg)
@@ -57,8 +59,12 @@ def test_the_intended_decode_path_runs(pair):
         assert bits & 1 == 0
     elif eng.intended_path == "exchange":
         assert bits & 3 == 1
-    elif cfg.name != "qwen7b-width-1L" or bits & 1:
-        assert bits & 3 == 3, "one GPU: persistent kernel with the feed-forward block kept inside each CTA"
+    elif eng.intended_path == "fused":
+        assert bits & 3 == 3
+    else:
+        assert bits & 1, "the persistent kernel is the default path"
+        if cfg.name in ("qwen-width-2L-q4", "qwen7b-width-1L"):
+            assert bits & 2, "these shapes keep the feed-forward block inside each CTA"
 
 
 def test_dequantized_weights_bit_exact(pair, oracle):
