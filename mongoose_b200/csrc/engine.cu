@@ -184,12 +184,12 @@ struct mg_engine {
     int mk_nslot = 0, mk_slot = MK_SLOT, mk_xs = 0, mk_sc = 0;
     int mk_prefetch = 0;                // L2 prefetch distance of the tape, bytes
     long long mk_wait = MK_WAIT_CYCLES; // limit of every wait inside the persistent kernel, SM clocks
-    // feed-forward block without a grid-wide exchange (one GPU): accumulators [3][dim] + arrival counter,
-    // and the host's mirror of where the next launch continues
+    // feed-forward block without a grid-wide exchange (one GPU): accumulators [3][dim], and the host's
+    // mirror of which of them the next launch starts with
     bool ffn_fused = false;
     long long* mk_acc = nullptr;
     int mk_buf = 0;
-    unsigned int mk_ctr = 0;
+    int mk_acc_n = 0;                   // additions that complete an accumulator word
     PhaseGeom mk_geom[5] = {};
     size_t mk_smem = 0;
     size_t tape_bytes = 0;
@@ -825,10 +825,11 @@ bool mega_feasible(mg_engine* e, std::string* why) {
         const int kblk = kblock_of(c.layer_fmt), total = c.ffn_dim / kblk;
         const PhaseGeom& gu = e->mk_geom[PH_GU];
         const int units = (c.ffn_dim + (1 << gu.ipg_shift) - 1) >> gu.ipg_shift;
-        int nkt = 0;
+        int nkt = 0, owners = 0;
         for (int cta = 0; cta < G; cta++) {
             const int ub = unit_begin(units, cta, G), n = unit_begin(units, cta + 1, G) - ub;
             if (n == 0) continue;
+            owners++;
             const int lo = ub << gu.ipg_shift, hi = std::min((ub + n) << gu.ipg_shift, c.ffn_dim);
             nkt = std::max(nkt, ((hi - 1) / kblk - lo / kblk + 2) / 2);
         }
@@ -844,7 +845,7 @@ bool mega_feasible(mg_engine* e, std::string* why) {
         const long long fused_tiles = (long long)((c.dim + 7) >> 3) * nkt;
         const bool pays = 200 * (fused_tiles - exch_tiles) + 30ll * c.dim < 13ll * c.ffn_dim;
         const bool want = env ? env[0] != '0' : pays;
-        if (e->sh.size == 1 && want && c.ffn_dim % kblk == 0 && nkt > 0 && total >= 2 * nkt &&
+        if (e->sh.size == 1 && want && owners + 1 <= 255 && c.ffn_dim % kblk == 0 && nkt > 0 && total >= 2 * nkt &&
             Kl <= 2 * MK_CONSUMERS && MK_NW * nkt <= slot / tile_bytes_of(c.layer_fmt)) {
             PhaseGeom g{};
             g.wide = 1; g.S = 1; g.RS = MK_NW; g.nkt = nkt; g.ipg_shift = 3;
@@ -852,6 +853,7 @@ bool mega_feasible(mg_engine* e, std::string* why) {
             g.kblocks = 2 * nkt; g.K = Kl; g.nfull = nkt;
             e->mk_geom[PH_DOWN] = g;
             e->ffn_fused = true;
+            e->mk_acc_n = owners + 1;
             const int stage = c.layer_fmt == FMT_F16 ? 0 : (xs_bytes_of(c.layer_fmt, Kl) + 15) & ~15;
             xs_bytes = std::max(xs_bytes, stage + Kl * 4);
         }
@@ -1080,9 +1082,9 @@ int build_mega(mg_engine* e) {
     MG_CUDA(e, ARENA_MALLOC(e, &e->mk_status, sizeof(MegaStatus)));
     MG_CUDA(e, cudaMemset(e->mk_status, 0, sizeof(MegaStatus)));
     if (e->ffn_fused) {
-        MG_CUDA(e, ARENA_MALLOC(e, &e->mk_acc, ((size_t)3 * c.dim + 2) * 8));
-        MG_CUDA(e, cudaMemset(e->mk_acc, 0, ((size_t)3 * c.dim + 2) * 8));
-        e->mk_buf = 0; e->mk_ctr = 0;
+        MG_CUDA(e, ARENA_MALLOC(e, &e->mk_acc, (size_t)3 * c.dim * 8));
+        MG_CUDA(e, cudaMemset(e->mk_acc, 0, (size_t)3 * c.dim * 8));
+        e->mk_buf = 0;
     }
     e->mega_ok = true;
     return MG_OK;
@@ -1128,12 +1130,11 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
     a.status = e->mk_status;
     a.ffn_fused = e->ffn_fused ? 1 : 0;
     if (e->ffn_fused) {
-        // the accumulators rotate and the arrival counter runs on from launch to launch
+        // the accumulators rotate on from launch to launch
         const unsigned int n = (unsigned)n_steps * (unsigned)(le - ls);
-        a.acc = e->mk_acc; a.ctr = reinterpret_cast<unsigned int*>(e->mk_acc + (size_t)3 * c.dim);
-        a.acc_buf0 = e->mk_buf; a.ctr0 = e->mk_ctr;
+        a.acc = e->mk_acc; a.acc_n = e->mk_acc_n;
+        a.acc_buf0 = e->mk_buf;
         e->mk_buf = (int)((e->mk_buf + n) % 3u);
-        e->mk_ctr += n * (unsigned)e->num_sms;
     }
     a.trace = e->trace_next ? e->mk_trace : nullptr;
     e->trace_next = false;
@@ -1162,9 +1163,9 @@ int check_mega_status(mg_engine* e) {
     if (s.error) {
         cudaMemset(e->mk_status, 0, sizeof s);
         if (e->mk_acc) {
-            // the aborted launch left the accumulators and the arrival counter anywhere: start over
-            cudaMemset(e->mk_acc, 0, ((size_t)3 * e->cfg.dim + 2) * 8);
-            e->mk_buf = 0; e->mk_ctr = 0;
+            // the aborted launch left the accumulators anywhere: start over
+            cudaMemset(e->mk_acc, 0, (size_t)3 * e->cfg.dim * 8);
+            e->mk_buf = 0;
         }
         if (s.error == MK_ERR_POLL && s.who >= 0)
             return fail(e, MG_ERR_TIMEOUT, "persistent kernel: the rows of rank %d never arrived (exchange %u, CTA %d)", s.who, (unsigned)s.where, s.cta);

@@ -40,9 +40,11 @@
 //    projection's input.  The CTA multiplies that window by ALL rows of the
 //    down matrix and adds the row sums, as 64-bit fixed point (associative, so
 //    the result does not depend on arrival order), into one of three rotating
-//    accumulators; an arrival counter tells the next phase when the sums are
-//    complete.  The FFN-wide middle vector never crosses SMs.  Tensor-parallel
-//    ranks keep the exchanged middle vector (their partial sums cross GPUs).
+//    accumulators; the low byte of every word counts the additions it has
+//    received, so the next phase polls data and completion in one load, as
+//    with the tagged words.  The FFN-wide middle vector never crosses SMs.
+//    Tensor-parallel ranks keep the exchanged middle vector (their partial
+//    sums cross GPUs).
 //
 // Every wait (mbarrier, exchange poll) is bounded by a deadline in SM clocks
 // (MegaArgs::wait_cycles, about 1 s by default); on expiry the kernel records
@@ -156,12 +158,11 @@ struct MegaArgs {
     long long* trace;       // optional [grid][(n_layers + 1) * MK_EV] SM-clock stamps of CTA thread 0 (first step)
     int trace_step;         // always 0: the step whose stamps are kept
     // Feed-forward block without a grid-wide exchange of its middle vector (one GPU only; see
-    // mk_down_fused): three rotating accumulators of dim 64-bit fixed-point sums and an arrival counter.
+    // mk_down_fused): three rotating accumulators of dim 64-bit words {fixed-point sum, arrival count}.
     int ffn_fused;
     int acc_buf0;           // accumulator (0..2) of this launch's first layer
-    unsigned int ctr0;      // value of the arrival counter when the launch starts
+    int acc_n;              // additions that complete a word: the CTAs that own gate/up rows + 1 (the residual)
     long long* acc;         // [3][dim]
-    unsigned int* ctr;
 };
 
 // ---------------------------------------------------------------------
@@ -1001,43 +1002,42 @@ __device__ __forceinline__ void xq_store_fast(uint32_t dst, uint32_t sc_addr, bo
 // ---------------------------------------------------------------------
 
 // ---------------------------------------------------------------------
-// Fixed-point accumulators.  Where many CTAs add partial sums into one vector, they add 64-bit
-// integers (value * 2^36, rounded): integer addition is associative, so the sum does not depend on
-// the order in which the CTAs arrive and a decode step stays reproducible bit for bit.  Range
-// +-1.3e8, resolution 1.5e-11: far outside / below anything a hidden state holds.
+// Accumulator words.  Where many CTAs add partial sums into one vector they add 64-bit integers:
+// bits 8..63 the value * 2^32, rounded (integer addition is associative, so the sum does not depend
+// on the order in which the CTAs arrive and a decode step stays reproducible bit for bit), bits
+// 0..7 a 1.  The low byte of a word therefore counts the additions it has received, and a reader
+// that knows how many are due (MegaArgs::acc_n <= 255) sees data and completion in ONE 8-byte
+// load, exactly as with the tagged exchange words: no counter, no fence, no second round trip.
+// Range +-8.4e6, resolution 2.3e-10: far outside / below anything a hidden state holds.
 // ---------------------------------------------------------------------
-constexpr float MK_FIX = 68719476736.0f;          // 2^36
-constexpr float MK_UNFIX = 1.0f / 68719476736.0f;
-// v * 2^36 as a 64-bit integer without the 64-bit conversion (a long instruction sequence): the
-// integer part of v * 2^12 and the remainder * 2^24 are two 32-bit conversions.  Exact for
-// |v| < 2^19 (every fp32 there is a multiple of 2^-36 unless |v| < 2^-12, which rounds to 2^-36).
-__device__ __forceinline__ long long mk_fix(float v) {
-    const float x = v * 4096.0f;
+// v * 2^32 without the 64-bit conversion (a long instruction sequence): the integer part of
+// v * 2^8 and the remainder * 2^24 are two 32-bit conversions.
+__device__ __forceinline__ long long mk_contrib(float v) {
+    const float x = v * 256.0f;
     const int hi = __float2int_rn(x);
     const int lo = __float2int_rn((x - (float)hi) * 16777216.0f);
-    return ((long long)hi << 24) + (long long)lo;
+    return ((((long long)hi << 24) + (long long)lo) << 8) + 1ll;
 }
-__device__ __forceinline__ float mk_unfix(unsigned int lo, unsigned int hi) {
-    return __ll2float_rn((long long)(((unsigned long long)hi << 32) | (unsigned long long)lo)) * MK_UNFIX;
+__device__ __forceinline__ float mk_acc_value(unsigned int lo, unsigned int hi) {
+    const long long w = (long long)(((unsigned long long)hi << 32) | (unsigned long long)lo);
+    return __ll2float_rn(w >> 8) * (1.0f / 4294967296.0f);
 }
 __device__ __forceinline__ void red_add_s64(long long* p, long long v) {
     asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-__device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-// One thread waits until the arrival counter has reached `target` (wrap-safe), bounded like every wait.
-__device__ __noinline__ void mk_wait_ctr(volatile int* abort_flag, MegaStatus* status, long long limit,
-                                         const unsigned int* ctr, unsigned int target) {
-    if ((int)(ld_acquire_u32(ctr) - target) >= 0) return;
+// Re-read a pair of accumulator words (16-byte aligned) until both have received n additions.
+__device__ __noinline__ uint4 mk_pollacc_slow(volatile int* abort_flag, MegaStatus* status, long long limit,
+                                              const Tagged* p, unsigned int n) {
+    uint4 r = make_uint4(0u, 0u, 0u, 0u);
+    if (*abort_flag) return r;
     const long long t0 = global_ns();
     for (;;) {
-        for (int i = 0; i < 64; i++)
-            if ((int)(ld_acquire_u32(ctr) - target) >= 0) return;
-        if (*abort_flag) return;
-        if (global_ns() - t0 > limit) { mk_fail_impl(abort_flag, status, MK_ERR_POLL, (int)target); return; }
+        for (int i = 0; i < 64; i++) {
+            r = ld_poll16(p);
+            if ((r.x & 0xffu) == n && (r.z & 0xffu) == n) return r;
+        }
+        if (*abort_flag) return r;
+        if (global_ns() - t0 > limit) { mk_fail_impl(abort_flag, status, MK_ERR_POLL, 900000 + (int)n); return r; }
     }
 }
 
@@ -1080,7 +1080,7 @@ __device__ __forceinline__ void stage_issue(const MegaArgs& a, const StageSrc& s
             if (s.kind == SRC_POLL) {
                 if (!TP || !NORMED) r[k] = ld_poll16(s.src + i);
             } else if (!TP && s.kind == SRC_ACC) {
-                // two 64-bit sums, complete: the arrival counter was waited for
+                // two accumulator words; stage_finish re-reads them until their counts are complete
                 r[k] = ld_poll16(s.src + i);
             } else {
                 const float2 v = mk_direct_pair(a, s.kind, s.token, i);
@@ -1105,7 +1105,11 @@ __device__ __forceinline__ void stage_finish(const MegaArgs& a, MkCtx& c, const 
         v0[k] = 0.f; v1[k] = 0.f;
         if (i < s.n) {
             if (TP && NORMED && s.kind == SRC_POLL) mk_poll2_sum(c, s.src + i, a.dim, a.tp_n, s.tag, v0[k], v1[k]);
-            else if (!TP && s.kind == SRC_ACC) { v0[k] = mk_unfix(r[k].x, r[k].y); v1[k] = mk_unfix(r[k].z, r[k].w); }
+            else if (!TP && s.kind == SRC_ACC) {
+                if ((r[k].x & 0xffu) != s.tag || (r[k].z & 0xffu) != s.tag)
+                    r[k] = mk_pollacc_slow(c.abort_flag(), c.status(), a.wait_cycles, s.src + i, s.tag);
+                v0[k] = mk_acc_value(r[k].x, r[k].y); v1[k] = mk_acc_value(r[k].z, r[k].w);
+            }
             else { mk_poll2_finish(c, s.src + i, s.tag, r[k]); v0[k] = __uint_as_float(r[k].x); v1[k] = __uint_as_float(r[k].z); }
         }
     }
@@ -1213,11 +1217,6 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
 
     // ---- 2. poll and stage the input, barrier ----
     float ss = 0.f;
-    if (!TP && s.kind == SRC_ACC) {
-        // the hidden state sits in an accumulator that is complete once every CTA has arrived
-        if (tid == 0) mk_wait_ctr(c.abort_flag(), c.status(), a.wait_cycles, a.ctr, s.tag);
-        consumer_sync();
-    }
     if (FMT != FMT_F16 && ((s.n >> 5) & 1) && tid == 0)    // odd number of blocks: the unused half pair's scale must be finite
         *reinterpret_cast<float2*>(mk_smem + c.xs_off + xq_plane_bytes(s.n) + (s.n >> 5) * 8) = make_float2(0.f, 0.f);
     if (s.n <= MK_STRIDE) {
@@ -1365,23 +1364,38 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
     mk_trace(a, 0, trace_base + 2 * (P == PH_HEAD ? 0 : P) + 1);
 }
 
+// Rows [lo, hi) of the hidden state this CTA looks after in the fused feed-forward block (residual,
+// clearing).  The CTAs that run attention are left out where others exist: they are the critical path.
+__device__ __forceinline__ void mk_row_share(const MegaArgs& a, int& lo, int& hi) {
+    int b = (int)blockIdx.x - a.n_heads, nb = (int)gridDim.x - a.n_heads;
+    if (nb <= 0) { b = blockIdx.x; nb = gridDim.x; }
+    lo = hi = 0;
+    if (b < 0) return;
+    lo = unit_begin(a.dim, b, nb);
+    hi = unit_begin(a.dim, b + 1, nb);
+}
+
 // ---------------------------------------------------------------------
 // Down projection without an exchange of the middle vector (one GPU).
 // A CTA's gate/up rows are a contiguous run of FFN features, so the silu(g) * u values it has just
 // produced are exactly a window of the down projection's input.  Instead of publishing them and
 // waiting for everybody else's, the CTA multiplies ITS window (2 nkt blocks of columns, all rows)
 // and adds the partial sums of all rows into the layer's accumulator; the other CTAs do the same
-// for their windows.  What replaces the exchange is an arrival counter: a consumer of the hidden
-// state waits until all CTAs have arrived, then reads the sums.  Three accumulators rotate: while
-// layer q adds into buffer q % 3, every CTA also clears its share of buffer (q + 1) % 3, which was
-// last read while layer q - 1 was staged - and every CTA has passed that point, since this CTA has
-// seen the counter of layer q - 1 complete.  The residual enters the same way (each CTA adds its
-// share of the hidden state that entered the block).
+// for their windows.  Every addition also bumps the count in the word's low byte (see "Accumulator
+// words"), so the next consumer of the hidden state polls the words themselves until their counts
+// are complete: one L2 round trip, and this CTA neither fences nor waits after its additions.
+// Three accumulators rotate.  While layer q adds into buffer q % 3, the rows of buffer (q + 1) % 3
+// are cleared (mk_clear_next, before the wo phase): it was last read while layer q - 1 was staged,
+// and every CTA has passed that point, since this CTA has seen every word of layer q - 1 complete.
+// The clearing threads fence after their stores and the CTA's additions of layer q are issued after
+// a barrier behind that fence; a CTA that adds into the cleared buffer at layer q + 1 has seen those
+// additions, so its own come later than the stores in real time.  The residual enters as one more
+// addition per row, made by the CTA that also clears that row (mk_row_share).
 //   Weights: wide tiles, row-group = 8 rows, nkt k-tiles = the window; warp w takes row-groups
 //   w, w + 15, ...; the sums leave the warp straight from registers (8 lanes x 8 bytes per tile row).
 // ---------------------------------------------------------------------
 template <int FMT>
-__device__ __forceinline__ void mk_down_fused(const MegaArgs& a, MkCtx& c, long long* acc_cur, long long* acc_next, int trace_base) {
+__device__ __forceinline__ void mk_down_fused(const MegaArgs& a, MkCtx& c, long long* acc_cur, int trace_base) {
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const PhaseGeom& g = a.geom[PH_DOWN];
     const int nrg = c.phase_tab()[8 + PH_DOWN];
@@ -1390,13 +1404,10 @@ __device__ __forceinline__ void mk_down_fused(const MegaArgs& a, MkCtx& c, long 
     c.probe_base = MK_PROBE_P == PH_DOWN ? trace_base : -1;
 #endif
     MK_ESTAMP(23);
-    // This CTA's share of the rows, [lo, hi): the residual enters there, and the same rows of the
-    // accumulator of the layer after this one are cleared.
-    const int lo = unit_begin(a.dim, blockIdx.x, gridDim.x), hi = unit_begin(a.dim, blockIdx.x + 1, gridDim.x);
-    for (int i = lo + tid; i < hi; i += MK_CONSUMERS) {
-        asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(acc_next + i), "l"(0ll) : "memory");
-        red_add_s64(acc_cur + i, mk_fix(c.hs()[i]));
-    }
+    // This CTA's share of the rows: the residual enters there.
+    int lo, hi;
+    mk_row_share(a, lo, hi);
+    for (int i = lo + tid; i < hi; i += MK_CONSUMERS) red_add_s64(acc_cur + i, mk_contrib(c.hs()[i]));
     MK_ESTAMP(25);
     consumer_sync();                                  // the window of the middle vector is complete
     MK_ESTAMP(26);
@@ -1455,7 +1466,7 @@ __device__ __forceinline__ void mk_down_fused(const MegaArgs& a, MkCtx& c, long 
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     const int r = row + u * 8 * MK_NW;
-                    if (ok[u] && L.t == 0 && r < a.dim) red_add_s64(acc_cur + r, mk_fix(v[u]));
+                    if (ok[u] && L.t == 0 && r < a.dim) red_add_s64(acc_cur + r, mk_contrib(v[u]));
                 }
             }
             MK_ESTAMP(33 + 2 * (rg0 / per_entry));
@@ -1465,11 +1476,22 @@ __device__ __forceinline__ void mk_down_fused(const MegaArgs& a, MkCtx& c, long 
         }
     }
     mk_trace(a, 0, trace_base + 11 + 3 * PH_DOWN);
-    consumer_sync();                                  // every warp's additions have been issued
+    consumer_sync();                                  // xs is free again for the next phase's staging
     mk_trace(a, 0, trace_base + 12 + 3 * PH_DOWN);
-    if (tid == 0) {
+}
+
+// Clear this CTA's rows of the accumulator the NEXT layer will add into: the same rows whose residual
+// it adds in this layer, so that a complete word of this layer proves the clearing of that row done.
+// Runs where the CTA would otherwise spin on the attention output; the fence keeps the clearing
+// threads until their stores have been performed.
+__device__ __forceinline__ void mk_clear_next(const MegaArgs& a, long long* acc_next) {
+    int lo, hi;
+    mk_row_share(a, lo, hi);
+    const int tid = threadIdx.x;
+    if (lo + tid < hi) {
+        for (int i = lo + tid; i < hi; i += MK_CONSUMERS)
+            asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(acc_next + i), "l"(0ll) : "memory");
         __threadfence();
-        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(a.ctr), "r"(1u) : "memory");
     }
 }
 
@@ -1737,14 +1759,14 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
 
         // tags of layer l: +1 q/kv, +2 attn, +3 h after wo, +4 ffn mid, +5 h after down
         // (fused feed-forward block: no +4 / +5; the hidden state after the block is accumulator
-        //  (acc_buf0 + qn) % 3, complete when the arrival counter reads ctr0 + (qn + 1) * grid)
+        //  (acc_buf0 + qn) % 3, each word complete when its count reads acc_n)
 #define MK_LAYER(FMT)                                                                                              \
         {                                                                                                          \
             StageSrc s0{SRC_POLL, a.xh, tag_prev_h, a.dim, a.norms + (size_t)l * 2 * a.dim, token};                \
             if (fused) {                                                                                           \
                 s0.kind = SRC_ACC;                                                                                 \
                 s0.src = reinterpret_cast<const Tagged*>(a.acc + (size_t)((a.acc_buf0 + qn + 2) % 3) * a.dim); \
-                s0.tag = a.ctr0 + (unsigned)qn * gridDim.x;                                                        \
+                s0.tag = (unsigned)a.acc_n;                                                                        \
             }                                                                                                      \
             if (l == a.ls) s0.kind = a.embed ? SRC_EMBED : SRC_PLAIN;                                              \
             mk_run_phase<PH_QKV, FMT, TP>(a, c, s0, l, base + 1, l * MK_EV, best);                                 \
@@ -1755,13 +1777,13 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
                 else mk_attention<32>(a, c, l, pos, base + 1, base + 2);                                           \
                 mk_trace(a, step, l * MK_EV + 9);                                                                  \
             }                                                                                                      \
+            if (fused) mk_clear_next(a, a.acc + (size_t)((a.acc_buf0 + qn + 1) % 3) * a.dim);                      \
             const StageSrc s1{SRC_POLL, a.xattn, base + 2, a.q_dim, nullptr, token};                               \
             mk_run_phase<PH_WO, FMT, TP>(a, c, s1, l, base + 3, l * MK_EV, best);                                  \
             const StageSrc s2{SRC_POLL, a.xhm, base + 3, a.dim, a.norms + (size_t)l * 2 * a.dim + a.dim, token};   \
             mk_run_phase<PH_GU, FMT, TP>(a, c, s2, l, base + 4, l * MK_EV, best);                                  \
             if (fused) {                                                                                           \
-                mk_down_fused<FMT>(a, c, a.acc + (size_t)((a.acc_buf0 + qn) % 3) * a.dim,           \
-                                   a.acc + (size_t)((a.acc_buf0 + qn + 1) % 3) * a.dim, l * MK_EV); \
+                mk_down_fused<FMT>(a, c, a.acc + (size_t)((a.acc_buf0 + qn) % 3) * a.dim, l * MK_EV);              \
                 mk_trace(a, 0, l * MK_EV + 2 * PH_DOWN + 1);                                                       \
             } else {                                                                                               \
                 const StageSrc s3{SRC_POLL, a.xmid, base + 4, a.ffn_dim, nullptr, token};                          \
@@ -1784,7 +1806,7 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
             if (fused) {
                 sh.kind = SRC_ACC;
                 sh.src = reinterpret_cast<const Tagged*>(a.acc + (size_t)((a.acc_buf0 + qn + 2) % 3) * a.dim);
-                sh.tag = a.ctr0 + (unsigned)qn * gridDim.x;
+                sh.tag = (unsigned)a.acc_n;
             }
             if (a.head_fmt == FMT_Q8_0) mk_run_phase<PH_HEAD, FMT_Q8_0, TP>(a, c, sh, L, base + 5, L * MK_EV, best);
             else if (a.head_fmt == FMT_Q4_0) mk_run_phase<PH_HEAD, FMT_Q4_0, TP>(a, c, sh, L, base + 5, L * MK_EV, best);
@@ -1796,12 +1818,13 @@ __device__ __forceinline__ void mk_consumer(MkCtx& c, const MegaArgs& a) {
             if (blockIdx.x == 0 && a.h_out && step == a.n_steps - 1 && a.le > a.ls) {
                 const unsigned int tag_final_h = ep + (unsigned)(a.le - 1) * MK_EPOCHS_PER_LAYER + 5;
                 if (fused) {
-                    if (tid == 0) mk_wait_ctr(c.abort_flag(), c.status(), a.wait_cycles, a.ctr, a.ctr0 + (unsigned)qn * gridDim.x);
-                    consumer_sync();
                     const Tagged* src = reinterpret_cast<const Tagged*>(a.acc + (size_t)((a.acc_buf0 + qn + 2) % 3) * a.dim);
-                    for (int i = tid; i < a.dim; i += MK_CONSUMERS) {
-                        const uint2 w = ld_poll8(src + i);
-                        c.hs()[i] = mk_unfix(w.x, w.y);
+                    for (int i = 2 * tid; i < a.dim; i += 2 * MK_CONSUMERS) {
+                        uint4 w = ld_poll16(src + i);
+                        if ((w.x & 0xffu) != (unsigned)a.acc_n || (w.z & 0xffu) != (unsigned)a.acc_n)
+                            w = mk_pollacc_slow(c.abort_flag(), c.status(), a.wait_cycles, src + i, (unsigned)a.acc_n);
+                        c.hs()[i] = mk_acc_value(w.x, w.y);
+                        c.hs()[i + 1] = mk_acc_value(w.z, w.w);
                     }
                 } else if (!TP) {
                     mk_gather(c, a.xh, tag_final_h, c.hs(), a.dim);
