@@ -836,14 +836,14 @@ bool mega_feasible(mg_engine* e, std::string* why) {
         const int Kl = 2 * nkt * kblk;
         // Worth it?  Against the exchange, the window costs the busiest CTA extra tiles (whole wide tiles
         // times all rows) and one 64-bit reduction per row; it saves every CTA the poll of the whole
-        // middle vector.  In CTA cycles, fitted to three measurements on B200 (Qwen2.5-0.5B +4 %,
-        // 7B-class widths +7 %, TinyLlama-1.1B -6 % when forced): about 20 per tile, 3 per reduction,
-        // 1.3 per polled word.  MG_FFN_FUSED=1 / 0 overrides the rule.
+        // middle vector.  In CTA cycles, roughly: 20 per tile, 1 per reduction, 1.3 per polled word.
+        // Measured on B200 against the exchange: Qwen2.5-0.5B +10 %, TinyLlama-1.1B +3 %, 7B-class
+        // widths +8 %; a model as wide as its FFN would lose.  MG_FFN_FUSED=1 / 0 overrides the rule.
         const PhaseGeom& gd = e->mk_geom[PH_DOWN];
         const int d_units = (c.dim + (1 << gd.ipg_shift) - 1) >> gd.ipg_shift;
         const long long exch_tiles = (long long)((d_units + G - 1) / G) * gd.nkt;
         const long long fused_tiles = (long long)((c.dim + 7) >> 3) * nkt;
-        const bool pays = 200 * (fused_tiles - exch_tiles) + 30ll * c.dim < 13ll * c.ffn_dim;
+        const bool pays = 200 * (fused_tiles - exch_tiles) + 10ll * c.dim < 13ll * c.ffn_dim;
         const bool want = env ? env[0] != '0' : pays;
         if (e->sh.size == 1 && want && owners + 1 <= 255 && c.ffn_dim % kblk == 0 && nkt > 0 && total >= 2 * nkt &&
             Kl <= 2 * MK_CONSUMERS && MK_NW * nkt <= slot / tile_bytes_of(c.layer_fmt)) {

@@ -1249,6 +1249,17 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
         const int j = e_r0 & (a.head_dim - 1);
         e_cs = c.rope()[j]; e_sn = c.rope()[(a.head_dim >> 1) + j];
     }
+    // RMSNorm factor of the staged vector, for the epilogue: formed here, where its loads overlap the
+    // first tile loads, instead of on the chain behind the phase's last barrier
+    float scale = 1.0f;
+    if (kNormed && (tid & ~31) < nslots) {
+        // (16th entry of a half of red[]: always 0)
+        const uint32_t rr = part_s + (uint32_t)(MK_PART_FLOATS + c.redsel) * 4u;
+        const float4 r0 = lds128f(rr), r1 = lds128f(rr + 16), r2 = lds128f(rr + 32), r3 = lds128f(rr + 48);
+        const float t = ((r0.x + r0.y) + (r0.z + r0.w)) + ((r1.x + r1.y) + (r1.z + r1.w)) +
+                        (((r2.x + r2.y) + (r2.z + r2.w)) + ((r3.x + r3.y) + (r3.z + r3.w)));
+        scale = rsqrtf(fmaf(t, a.inv_dim, a.eps));
+    }
     MK_STAMP(26);
 
     // ---- 3. tiles ----
@@ -1296,15 +1307,6 @@ __device__ __forceinline__ void mk_run_phase(const MegaArgs& a, MkCtx& c, const 
 
     // ---- 4. epilogue: whole warps (the shuffles need every lane) ----
     if ((tid & ~31) < nslots) {
-        float scale = 1.0f;
-        if (kNormed) {
-            // RMSNorm factor of the staged vector (16th entry of a half of red[]: always 0)
-            const uint32_t rr = part_s + (uint32_t)(MK_PART_FLOATS + c.redsel) * 4u;
-            const float4 r0 = lds128f(rr), r1 = lds128f(rr + 16), r2 = lds128f(rr + 32), r3 = lds128f(rr + 48);
-            const float t = ((r0.x + r0.y) + (r0.z + r0.w)) + ((r1.x + r1.y) + (r1.z + r1.w)) +
-                            (((r2.x + r2.y) + (r2.z + r2.w)) + ((r3.x + r3.y) + (r3.z + r3.w)));
-            scale = rsqrtf(fmaf(t, a.inv_dim, a.eps));
-        }
         MK_STAMP(29);
         const int nq = sp >> 2;
         for (int sl = tid; sl < ((nslots + 31) & ~31); sl += MK_CONSUMERS) {

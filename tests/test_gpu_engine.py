@@ -29,7 +29,7 @@ KERNELS_PATH = ["tiny", "tiny-q4_0", "tiny-hd64", "tiny-hd128-f16", "qwen-width-
 # ... and these once more on the persistent kernel with each way of running the feed-forward block
 # forced: the middle vector exchanged between the CTAs (what tensor-parallel ranks run), or kept
 # inside each CTA with the down projection's sums meeting in accumulators.  By default the engine
-# picks per model shape (Qwen2.5-0.5B and 7B-class widths: inside the CTA).
+# picks per model shape (the three benchmark architectures: inside the CTA).
 FFN_PATHS = ["tiny", "tiny-q4_0", "tiny-hd128-f16", "tinyllama-width-2L"]
 CASES = ([(c, "") for c in SMALL] + [(c, "kernels") for c in SMALL if c.name in KERNELS_PATH] +
          [(c, "exchange") for c in SMALL if c.name in FFN_PATHS] + [(c, "fused") for c in SMALL if c.name in FFN_PATHS])
@@ -63,7 +63,7 @@ def test_the_intended_decode_path_runs(pair):
         assert bits & 3 == 3
     else:
         assert bits & 1, "the persistent kernel is the default path"
-        if cfg.name in ("qwen-width-2L-q4", "qwen7b-width-1L"):
+        if cfg.name in ("qwen-width-2L-q4", "qwen7b-width-1L", "tinyllama-width-2L"):
             assert bits & 2, "these shapes keep the feed-forward block inside each CTA"
 
 
