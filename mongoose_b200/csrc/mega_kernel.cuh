@@ -1561,13 +1561,18 @@ __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int la
     const int t_first = w + MK_NW * uq;
 
     // ---- cached rows (positions < pos) into registers ----
+    // Everything below is guarded per warp (a warp's positions of a pass / of a group of four are
+    // known from w and pos alone), so a short context skips the passes it does not have instead of
+    // walking through their predicated-off loads.
+    const int npass = (pos - w + MK_NW * PPP) / (MK_NW * PPP);      // score passes in which this warp has a position <= pos (w <= pos)
+    const int nv = w < pos ? (pos - w + MK_NW - 1) / MK_NW : 0;     // cached positions of this warp for P . V
     uint4 kreg[NPRE][KV4];
 #pragma unroll
     for (int i = 0; i < NPRE; i++) {
         const int t = t_first + i * (MK_NW * PPP);
 #pragma unroll
         for (int j = 0; j < KV4; j++) kreg[i][j] = make_uint4(0u, 0u, 0u, 0u);
-        if (t < pos) {
+        if (w <= pos && i < npass && t < pos) {
             const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)t * a.kv_dim + qp * DPL);
 #pragma unroll
             for (int j = 0; j < KV4; j++) kreg[i][j] = __ldcg(kp + j);
@@ -1575,10 +1580,16 @@ __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int la
     }
     uint2 vreg[NV];
 #pragma unroll
-    for (int j = 0; j < NV; j++) {
-        const int t = w + j * MK_NW;
-        vreg[j] = make_uint2(0u, 0u);
-        if (t < pos) vreg[j] = ldcg_v<VPL>(vc + (size_t)t * a.kv_dim + lane * VPL);
+    for (int j0 = 0; j0 < NV; j0 += 4) {
+#pragma unroll
+        for (int j = j0; j < j0 + 4; j++) vreg[j] = make_uint2(0u, 0u);
+        if (j0 < nv) {
+#pragma unroll
+            for (int j = j0; j < j0 + 4; j++) {
+                const int t = w + j * MK_NW;
+                if (t < pos) vreg[j] = ldcg_v<VPL>(vc + (size_t)t * a.kv_dim + lane * VPL);
+            }
+        }
     }
     MK_ESTAMP(40);
 
@@ -1603,7 +1614,6 @@ __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int la
     const float scale = rsqrtf((float)HD);
     const uint32_t q_s = xs_s + (uint32_t)(qp * DPL) * 4u;
     float mx = -INFINITY;
-    const int npass = (pos - w + MK_NW * PPP) / (MK_NW * PPP);      // passes in which this warp has a position <= pos (w <= pos)
 #pragma unroll
     for (int i = 0; i < NPRE; i++) {
         if (i == 0 || (w <= pos && i < npass)) {                   // uniform over the warp
@@ -1667,13 +1677,18 @@ __device__ __forceinline__ void mk_attention(const MegaArgs& a, MkCtx& c, int la
     float lsum = 0.f;
     const int last = max(pos - 1, 0);
 #pragma unroll
-    for (int j = 0; j < NV; j++) {
-        const int t = w + j * MK_NW;
-        // straight-line: positions beyond the context contribute p = 0 (their V registers hold zeros)
-        float p = __expf(c.sc()[min(t, last)] - mx);
-        p = t < pos ? p : 0.f;
-        lsum += p;
-        fma_v<VPL>(acc, p, vreg[j]);
+    for (int j0 = 0; j0 < NV; j0 += 4) {
+        if (j0 < nv) {
+            // a group of four, straight-line: positions beyond the context contribute p = 0 (their V registers hold zeros)
+#pragma unroll
+            for (int j = j0; j < j0 + 4; j++) {
+                const int t = w + j * MK_NW;
+                float p = __expf(c.sc()[min(t, last)] - mx);
+                p = t < pos ? p : 0.f;
+                lsum += p;
+                fma_v<VPL>(acc, p, vreg[j]);
+            }
+        }
     }
     for (int t0 = w + NV * MK_NW; t0 < pos; t0 += 4 * MK_NW) {   // remainder, four loads in flight
         uint2 vv[4];
