@@ -844,7 +844,11 @@ bool mega_feasible(mg_engine* e, std::string* why) {
         const long long exch_tiles = (long long)((d_units + G - 1) / G) * gd.nkt;
         const long long fused_tiles = (long long)((c.dim + 7) >> 3) * nkt;
         const bool pays = 200 * (fused_tiles - exch_tiles) + 10ll * c.dim < 13ll * c.ffn_dim;
-        const bool want = env ? env[0] != '0' : pays;
+        // The rotation of the accumulators is proven for shapes in which every CTA owns gate/up rows (a
+        // complete word then shows that EVERY CTA has passed the previous layer); narrower shapes keep
+        // the exchange unless the switch forces the fused block (tests do, on tiny models, where a CTA
+        // without rows would have to fall a whole layer behind for the difference to matter).
+        const bool want = env ? env[0] != '0' : (pays && owners == G);
         if (e->sh.size == 1 && want && owners + 1 <= 255 && c.ffn_dim % kblk == 0 && nkt > 0 && total >= 2 * nkt &&
             Kl <= 2 * MK_CONSUMERS && MK_NW * nkt <= slot / tile_bytes_of(c.layer_fmt)) {
             PhaseGeom g{};
