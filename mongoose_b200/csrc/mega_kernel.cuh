@@ -1016,7 +1016,7 @@ __device__ __forceinline__ long long mk_contrib(float v) {
     const float x = v * 256.0f;
     const int hi = __float2int_rn(x);
     const int lo = __float2int_rn((x - (float)hi) * 16777216.0f);
-    return ((((long long)hi << 24) + (long long)lo) << 8) + 1ll;
+    return ((long long)hi * 16777216ll + (long long)lo) * 256ll + 1ll;
 }
 __device__ __forceinline__ float mk_acc_value(unsigned int lo, unsigned int hi) {
     const long long w = (long long)(((unsigned long long)hi << 32) | (unsigned long long)lo);
