@@ -694,5 +694,16 @@ def main():
     run_b200_arm(args, cfg, rank, world, local_rank)
 
 
+def _one_line_stdout():
+    """Libraries (NCCL's version banner, for one) write to file descriptor 1.  The contract is ONE
+    JSON line on stdout, so everything written to fd 1 while the benchmark runs goes to stderr and
+    only what this module prints through `print` reaches the real stdout."""
+    sys.stdout.flush()
+    real = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(real, "w", buffering=1)
+
+
 if __name__ == "__main__":
+    _one_line_stdout()
     main()
