@@ -401,7 +401,7 @@ def run_b200_arm(args, cfg, rank, world, local_rank):
                        "timing": "CUDA events on the engine stream, max over ranks"},
             "e2e": {"value": multi.aggregate_rate(jobs, K, e2e_ms_max), "unit": "tok/s",
                     "h2d_bytes_per_step": cfg.dim * 4 + 8, "d2h_bytes_per_step": cfg.vocab * 4,
-                    "api": "PartialStep(hiddenIn, pos, 0, L, nil, logitsOut) with pinned host buffers",
+                    "api": "PartialStep(hiddenIn, pos, 0, L, nil, logitsOut) with pinned host buffers (the logits cross PCIe as stores of the kernel into logitsOut)",
                     "last_token_matches_device_loop": bool(e2e_last_tok == tok_last)},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",

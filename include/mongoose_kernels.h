@@ -198,7 +198,9 @@ MG_API int mg_build(mg_engine* e);
 MG_API int mg_reset_kv(mg_engine* e);
 /* PartialStep (cuda_fused_infer.go:392-459): HOST hidden_in[dim] -> layers [layer_start, layer_end)
  * at position pos -> HOST logits_out[vocab] when the range reaches the last layer and logits_out is
- * not NULL, else HOST hidden_out[dim] when not NULL.  Blocks until the outputs are on the host. */
+ * not NULL, else HOST hidden_out[dim] when not NULL.  Blocks until the outputs are on the host.
+ * A page-locked logits_out (cudaHostAlloc / cudaHostRegister) is filled by the kernel's own stores;
+ * pageable memory gets the reference's copy (ToHost, cuda_tensor.go:622). */
 MG_API int mg_partial_step(mg_engine* e, const float* hidden_in, int pos, int layer_start, int layer_end,
                     float* hidden_out, float* logits_out);
 /* ExportHidden (cuda_fused_infer.go:235-239). */

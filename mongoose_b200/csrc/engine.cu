@@ -165,8 +165,10 @@ struct mg_engine {
     int* out_tokens = nullptr;
     int out_cap = 0;
     // pinned staging
-    int* pin_i = nullptr;               // [0..3] cursor, [4..] prompt ids
+    int* pin_i = nullptr;               // [0..3] cursor, [4..] prompt ids, then 16 ints for the kernels' status words
     int pin_i_cap = 0;
+    float* logits_direct = nullptr;     // this launch writes its logits here (caller's pinned host buffer) instead of e->logits
+    bool zero_copy = true;
     std::map<GraphKey, CachedGraph> graphs;
     // persistent-kernel path (mega_kernel.cuh)
     bool use_mega = true;               // allowed by the environment
@@ -1130,7 +1132,7 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
             a.xbest_peer[p] = reinterpret_cast<Tagged*>(xchg_best(e, e->xchg_peer[p]));
         }
     }
-    a.h_in = e->h; a.h_out = e->h; a.logits = e->logits; a.st = e->st; a.out_tokens = e->out_tokens;
+    a.h_in = e->h; a.h_out = e->h; a.logits = e->logits_direct ? e->logits_direct : e->logits; a.st = e->st; a.out_tokens = e->out_tokens;
     a.status = e->mk_status;
     a.ffn_fused = e->ffn_fused ? 1 : 0;
     if (e->ffn_fused) {
@@ -1150,11 +1152,18 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
     return MG_OK;
 }
 
-// After a synchronisation: did any wait inside the persistent kernel give up?
+// Did any wait inside the kernels give up?  The status words are copied to pinned memory behind
+// whatever is still queued on the engine's stream, followed by ONE synchronisation (callers need not
+// synchronise first).
 int check_mega_status(mg_engine* e) {
+    MegaStatus* hs = reinterpret_cast<MegaStatus*>(e->pin_i + e->pin_i_cap);
+    XchgStatus* hx = reinterpret_cast<XchgStatus*>(e->pin_i + e->pin_i_cap + 8);
+    static_assert(sizeof(MegaStatus) <= 32 && sizeof(XchgStatus) <= 32, "status words must fit their pinned slots");
+    if (e->tp_fused) MG_CUDA(e, cudaMemcpyAsync(hx, e->xchg_status, sizeof(XchgStatus), cudaMemcpyDeviceToHost, e->stream));
+    if (e->mega_ok) MG_CUDA(e, cudaMemcpyAsync(hs, e->mk_status, sizeof(MegaStatus), cudaMemcpyDeviceToHost, e->stream));
+    MG_CUDA(e, cudaStreamSynchronize(e->stream));
     if (e->tp_fused) {
-        XchgStatus x{};
-        MG_CUDA(e, cudaMemcpy(&x, e->xchg_status, sizeof x, cudaMemcpyDeviceToHost));
+        const XchgStatus x = *hx;
         if (x.error) {
             cudaMemset(e->xchg_status, 0, sizeof x);
             return fail(e, MG_ERR_TIMEOUT, "tensor-parallel exchange: rows of rank %d never arrived (slot %d, exchange %u, last seen %u)",
@@ -1162,8 +1171,7 @@ int check_mega_status(mg_engine* e) {
         }
     }
     if (!e->mega_ok) return MG_OK;
-    MegaStatus s{};
-    MG_CUDA(e, cudaMemcpy(&s, e->mk_status, sizeof s, cudaMemcpyDeviceToHost));
+    const MegaStatus s = *hs;
     if (s.error) {
         cudaMemset(e->mk_status, 0, sizeof s);
         if (e->mk_acc) {
@@ -1352,7 +1360,8 @@ int mg_create(const mg_config* cfg, mg_engine** out) {
     if (cudaMemcpy(e->st, &s0, sizeof s0, cudaMemcpyHostToDevice) != cudaSuccess) return bail(MG_ERR_CUDA);
 
     e->pin_i_cap = 8 + e->out_cap;
-    if (cudaMallocHost((void**)&e->pin_i, (size_t)e->pin_i_cap * sizeof(int)) != cudaSuccess) return bail(MG_ERR_NOMEM);
+    if (cudaMallocHost((void**)&e->pin_i, (size_t)(e->pin_i_cap + 16) * sizeof(int)) != cudaSuccess) return bail(MG_ERR_NOMEM);
+    { const char* zc = getenv("MG_ZERO_COPY"); e->zero_copy = !(zc && zc[0] == '0'); }
 
     if ((rc = set_kernel_attrs(e))) return bail(rc);
     const char* env = getenv("MG_NO_GRAPH");
@@ -1536,13 +1545,25 @@ int mg_partial_step(mg_engine* e, const float* hidden_in, int pos, int layer_sta
     MG_CUDA(e, cudaMemcpyAsync(e->st, e->pin_i, 8, cudaMemcpyHostToDevice, e->stream));
     MG_CUDA(e, cudaMemcpyAsync(e->h, hidden_in, (size_t)c.dim * 4, cudaMemcpyHostToDevice, e->stream));
     const bool want_logits = layer_end >= c.n_layers && logits_out;
-    if ((rc = run_step(e, layer_start, layer_end, MODE_HIDDEN, want_logits ? HEAD_LOGITS : HEAD_NONE))) return rc;
-    if (want_logits)
+    // A caller's page-locked logits buffer is written by lm_head's epilogue itself (the stores cross
+    // PCIe while the phase streams its weights), which saves the 600 KB copy behind the kernel.
+    float* direct = nullptr;
+    if (want_logits && e->zero_copy && e->sh.size == 1 && e->mega_ok && layer_end > layer_start) {
+        cudaPointerAttributes at{};
+        if (cudaPointerGetAttributes(&at, logits_out) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer)
+            direct = static_cast<float*>(at.devicePointer);
+        else
+            cudaGetLastError();
+    }
+    e->logits_direct = direct;
+    rc = run_step(e, layer_start, layer_end, MODE_HIDDEN, want_logits ? HEAD_LOGITS : HEAD_NONE);
+    e->logits_direct = nullptr;
+    if (rc) return rc;
+    if (want_logits && !direct)
         MG_CUDA(e, cudaMemcpyAsync(logits_out, e->sh.size > 1 ? e->logits_all : e->logits, (size_t)c.vocab * 4,
                                    cudaMemcpyDeviceToHost, e->stream));
-    else if (hidden_out)
+    else if (!want_logits && hidden_out)
         MG_CUDA(e, cudaMemcpyAsync(hidden_out, e->h, (size_t)c.dim * 4, cudaMemcpyDeviceToHost, e->stream));
-    MG_CUDA(e, cudaStreamSynchronize(e->stream));
     return check_mega_status(e);
 }
 
