@@ -192,6 +192,7 @@ struct mg_engine {
     long long* mk_acc = nullptr;
     int mk_buf = 0;
     int mk_acc_n = 0;                   // additions that complete an accumulator word
+    int mk_qkv_cta0 = 0;                // first CTA that owns QKV rows
     PhaseGeom mk_geom[5] = {};
     size_t mk_smem = 0;
     size_t tape_bytes = 0;
@@ -816,6 +817,13 @@ bool mega_feasible(mg_engine* e, std::string* why) {
         }
         e->mk_geom[p] = choose_geom(s.fmt, s.K, s.items, s.rpi, G, MK_NW, slot, p == PH_HEAD, fw, fs);
         if (e->mk_geom[p].nkt == 0) { *why = "no tile layout for a phase"; return false; }
+        if (p == PH_QKV) {
+            // Leave the CTAs that run attention without QKV rows where the busiest CTA gets no more rows
+            // for it: they then fetch their cached K/V rows while the others multiply.  MG_QKV_ALL=1 keeps them in.
+            const int sh = e->mk_geom[p].ipg_shift, units = (s.items + (1 << sh) - 1) >> sh, rest = G - c.n_heads;
+            const char* all = getenv("MG_QKV_ALL");
+            e->mk_qkv_cta0 = (rest > 0 && !(all && all[0] == '1') && (units + rest - 1) / rest == (units + G - 1) / G) ? c.n_heads : 0;
+        }
         xs_bytes = std::max(xs_bytes, xs_bytes_of(s.fmt, s.K));
     }
     // Down projection on each CTA's own window of the middle vector (no exchange between gate/up and
@@ -920,9 +928,11 @@ int build_mega(mg_engine* e) {
         const PhaseShape s = phase_shape_of(p, c.dim, q_dim, c.kv_dim, c.ffn_dim, c.vocab, c.layer_fmt, c.head_fmt);
         const int sh = e->mk_geom[p].ipg_shift;
         const int units = (s.items + (1 << sh) - 1) >> sh;
-        const int ub = unit_begin(units, cta, G);
+        const int off = p == PH_QKV ? e->mk_qkv_cta0 : 0;
+        if (cta < off) { if (first) *first = 0; return 0; }
+        const int ub = unit_begin(units, cta - off, G - off);
         if (first) *first = ub;
-        return unit_begin(units, cta + 1, G) - ub;
+        return unit_begin(units, cta - off + 1, G - off) - ub;
     };
     // fused feed-forward block: a CTA with gate/up items multiplies ALL rows of the down projection
     // by its own window of columns (first block: down_window_block)
@@ -1135,6 +1145,7 @@ int launch_mega(mg_engine* e, int ls, int le, int mode, int head, int n_steps) {
     a.h_in = e->h; a.h_out = e->h; a.logits = e->logits_direct ? e->logits_direct : e->logits; a.st = e->st; a.out_tokens = e->out_tokens;
     a.status = e->mk_status;
     a.ffn_fused = e->ffn_fused ? 1 : 0;
+    a.qkv_cta0 = e->mk_qkv_cta0;
     if (e->ffn_fused) {
         // the accumulators rotate on from launch to launch
         const unsigned int n = (unsigned)n_steps * (unsigned)(le - ls);

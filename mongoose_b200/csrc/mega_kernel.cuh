@@ -161,6 +161,8 @@ struct MegaArgs {
     // mk_down_fused): three rotating accumulators of dim 64-bit words {fixed-point sum, arrival count}.
     int ffn_fused;
     int acc_buf0;           // accumulator (0..2) of this launch's first layer
+    int qkv_cta0;           // the QKV rows are dealt to CTAs qkv_cta0 .. grid-1 (n_heads where that keeps the balance: the
+                            // CTAs that run attention then load their cached K/V rows while the others multiply)
     int acc_n;              // additions that complete a word: the CTAs that own gate/up rows + 1 (the residual)
     long long* acc;         // [3][dim]
 };
@@ -1929,9 +1931,11 @@ __global__ void __launch_bounds__(MK_THREADS, 1) mega_decode_kernel(const __grid
             const PhaseShape sh = phase_shape_of(p, a.dim, a.q_dim, a.kv_dim, a.ffn_dim, a.vocab, a.layer_fmt, a.head_fmt);
             const int ipg = 1 << a.geom[p].ipg_shift;
             const int units = (sh.items + ipg - 1) >> a.geom[p].ipg_shift;
-            const int ub = unit_begin(units, blockIdx.x, gridDim.x);
+            const int off = p == PH_QKV ? a.qkv_cta0 : 0;
+            const int me = (int)blockIdx.x - off, ng = (int)gridDim.x - off;
+            const int ub = me < 0 ? 0 : unit_begin(units, me, ng);
             c.phase_tab()[p] = ub;
-            c.phase_tab()[8 + p] = unit_begin(units, blockIdx.x + 1, gridDim.x) - ub;
+            c.phase_tab()[8 + p] = me < 0 ? 0 : unit_begin(units, me + 1, ng) - ub;
             for (int w = 0; w < 16; w++) {
                 const int S = a.geom[p].S, rs = w / S;
                 c.warp_tab()[p * 16 + w] = (unsigned short)(rs < a.geom[p].RS ? (rs | ((w - rs * S) << 8)) : 255);
