@@ -444,35 +444,51 @@ def run_tp_leg(torch, dist, rank, world, local_rank, steps=48):
     kw = {}
     if world > 1:
         kw = dict(tp_rank=rank, tp_size=world, tp_id=multi.share_unique_id(dist, rank))
-    eng = CUDAFusedInference(cfg, device=local_rank, **kw)
-    synthetic.load_engine(eng, cfg, seed=0)
-    eng.BuildFusedDispatch()
-    note = eng._lib.mg_last_error(eng._h).decode()
-    prompt = synthetic.prompt_ids(0, PROMPT_LEN, cfg.vocab)
-    stream = torch.cuda.ExternalStream(eng.stream, device=local_rank)
+    # A rank whose engine fails must still meet the others in every collective below, or they would
+    # wait for it: engine work sits in guarded sections, the collectives run unconditionally.
+    err, eng, note, stream, ms, tok_last = None, None, "", None, 0.0, -1
+    try:
+        eng = CUDAFusedInference(cfg, device=local_rank, **kw)
+        synthetic.load_engine(eng, cfg, seed=0)
+        eng.BuildFusedDispatch()
+        note = eng._lib.mg_last_error(eng._h).decode()
+        prompt = synthetic.prompt_ids(0, PROMPT_LEN, cfg.vocab)
+        stream = torch.cuda.ExternalStream(eng.stream, device=local_rank)
 
-    def feed():
-        eng.ResetKV()
-        tok = -1
-        for pos, t in enumerate(prompt):
-            tok = eng.StepToken(int(t), pos)
-        eng.SetCursor(tok, PROMPT_LEN)
+        def feed():
+            eng.ResetKV()
+            tok = -1
+            for pos, t in enumerate(prompt):
+                tok = eng.StepToken(int(t), pos)
+            eng.SetCursor(tok, PROMPT_LEN)
 
-    feed()
-    eng.EnqueueGreedy(8)
-    eng.Sync()
-    feed()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
+        feed()
+        eng.EnqueueGreedy(8)
+        eng.Sync()
+        feed()
+        torch.cuda.synchronize()
+    except Exception as ex:
+        err = ex
     if dist is not None:
         dist.barrier()
-    ev0.record(stream)
-    eng.EnqueueGreedy(steps)
-    ev1.record(stream)
-    eng.Sync()
-    ms, = multi.reduce_max([ev0.elapsed_time(ev1)], dist, device="cuda")
-    tok_last, _ = eng.GetCursor()
-    eng.close()
+    if err is None:
+        try:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record(stream)
+            eng.EnqueueGreedy(steps)
+            ev1.record(stream)
+            eng.Sync()
+            ms = ev0.elapsed_time(ev1)
+            tok_last, _ = eng.GetCursor()
+        except Exception as ex:
+            err = ex
+    ms, failed = multi.reduce_max([ms, 0.0 if err is None else 1.0], dist, device="cuda")
+    if eng is not None:
+        eng.close()
+    if err is not None:
+        raise err
+    if failed:
+        raise RuntimeError("the tensor-parallel leg failed on another rank")
     bytes_tok = (mc.weight_bytes_per_token(cfg) + mc.kv_bytes_per_position(cfg) * (PROMPT_LEN + steps / 2.0)) / world
     peak, _ = measured_peak_gbs()
     return {"workload": f"{cfg.name}-q8_0 tensor parallel x{world}", "value": steps / (ms / 1e3), "unit": "tok/s",
@@ -488,26 +504,40 @@ def run_seqs_leg(torch, dist, rank, world, local_rank, sequences=16, prompt_len=
     sequence is decoded with batch-1 semantics (prompt through the decode path).  Strong scaling."""
     from mongoose_b200.fused_infer import CUDAFusedInference
     cfg = SEQ_LEG_CFG.with_(max_seq=prompt_len + steps)
-    eng = CUDAFusedInference(cfg, device=local_rank)
-    synthetic.load_engine(eng, cfg, seed=0)
-    eng.BuildFusedDispatch()
     mine = multi.sequences_for_rank(sequences, rank, world)
-    stream = torch.cuda.ExternalStream(eng.stream, device=local_rank)
-    for _ in range(3):
-        eng.StepToken(1, 0)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
+    # (guarded sections + unconditional collectives, as in the tensor-parallel leg)
+    err, eng, ms, tails = None, None, 0.0, []
+    try:
+        eng = CUDAFusedInference(cfg, device=local_rank)
+        synthetic.load_engine(eng, cfg, seed=0)
+        eng.BuildFusedDispatch()
+        stream = torch.cuda.ExternalStream(eng.stream, device=local_rank)
+        for _ in range(3):
+            eng.StepToken(1, 0)
+        torch.cuda.synchronize()
+    except Exception as ex:
+        err = ex
     if dist is not None:
         dist.barrier()
-    ev0.record(stream)
-    tails = []
-    for sidx in mine:
-        eng.ResetKV()
-        tails.append(int(eng.Generate(synthetic.prompt_ids(sidx, prompt_len, cfg.vocab), steps)[-1]))
-    ev1.record(stream)
-    torch.cuda.synchronize()
-    ms, = multi.reduce_max([ev0.elapsed_time(ev1)], dist, device="cuda")
-    eng.close()
+    if err is None:
+        try:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record(stream)
+            for sidx in mine:
+                eng.ResetKV()
+                tails.append(int(eng.Generate(synthetic.prompt_ids(sidx, prompt_len, cfg.vocab), steps)[-1]))
+            ev1.record(stream)
+            torch.cuda.synchronize()
+            ms = ev0.elapsed_time(ev1)
+        except Exception as ex:
+            err = ex
+    ms, failed = multi.reduce_max([ms, 0.0 if err is None else 1.0], dist, device="cuda")
+    if eng is not None:
+        eng.close()
+    if err is not None:
+        raise err
+    if failed:
+        raise RuntimeError("the sequences leg failed on another rank")
     tokens_total = sequences * (prompt_len + steps - 1)
     return {"workload": f"tinyllama-1.1b-q8_0, {sequences} sequences x ({prompt_len} prompt + {steps} decode), i mod {world}",
             "value": tokens_total / (ms / 1e3), "unit": "tok/s", "scaling": "strong", "sequences_per_gpu": len(mine),
