@@ -250,3 +250,30 @@ def test_in_kernel_exchange_wait_runs_out_and_returns(cuda, oracle, mglib):
         assert_close(logits, om.step_token(1, 0), 1e-4, "a fresh engine after the timeout")
     finally:
         eng.close(); om.close()
+
+
+def test_decode_is_reproducible_bit_for_bit(cuda, mglib):
+    """The fused feed-forward block adds the CTAs' partial sums in whatever order they arrive; they are
+    64-bit integers, so the result must not depend on that order: two passes over the same positions
+    give bit-identical logits (and so do two engines)."""
+    cfg = mc.QWEN25_05B.with_(name="qwen-width-3L", n_layers=3, vocab=3000, max_seq=40)
+    runs = []
+    engines = [CUDAFusedInference(cfg), CUDAFusedInference(cfg)]
+    try:
+        for eng in engines:
+            fill_models(cfg, seed=5, jitter=0.1, engine=eng)
+            eng.BuildFusedDispatch()
+            assert eng.DecodePath() & 3 == 3, "this shape runs the fused feed-forward block"
+        for eng in (engines[0], engines[0], engines[1]):
+            eng.ResetKV()
+            out = []
+            for pos in range(24):
+                logits = np.empty(cfg.vocab, np.float32)
+                eng.StepToken(17 + 5 * pos, pos, logitsOut=logits)
+                out.append(logits)
+            runs.append(np.stack(out))
+        assert np.array_equal(runs[0], runs[1]), "same engine, second pass"
+        assert np.array_equal(runs[0], runs[2]), "second engine"
+    finally:
+        for eng in engines:
+            eng.close()
