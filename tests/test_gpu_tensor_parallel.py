@@ -69,6 +69,13 @@ def test_two_ranks_with_nccl_exchange_match_the_oracle():
     check(run_ranks(2, cases, nccl_exchange=True), cases, nccl_exchange=True, persistent=False)
 
 
+def test_two_ranks_share_a_kv_head_and_split_its_q_heads_unevenly():
+    """What eight ranks do with 28 Q / 4 KV heads (4 + 3 Q heads of a KV head held twice), on two."""
+    cases = ["kv1-uneven"]
+    check(run_ranks(2, cases), cases)
+    check(run_ranks(2, cases, kernels_path=True), cases, persistent=False)
+
+
 def test_four_ranks_with_replicated_kv_heads_match_the_oracle():
     # 2 KV heads over 4 ranks: every KV head is held by two ranks that split its Q heads
     cases = ["tiny", "tiny-bias-ragged", "hd128-gqa"]

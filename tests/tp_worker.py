@@ -31,6 +31,10 @@ CASES = {
     "tiny-q4": (mc.TINY_Q4, False),
     # one KV head for four Q heads: with two ranks the KV head (rows, bias, cache) is held by both
     "tiny-kv1": (mc.TINY.with_(name="tiny-kv1", n_kv_heads=1), True),
+    # one KV head held by both of two ranks, which take 2 + 1 of its three Q heads (and 192 + 160 FFN
+    # features): the mechanism of the 8-rank 28 Q / 4 KV split - a replicated KV head, ranks with
+    # different numbers of Q heads - on two GPUs
+    "kv1-uneven": (mc.TINY.with_(name="kv1-uneven", dim=96, n_heads=3, n_kv_heads=1, head_dim=32, ffn_dim=352), True),
     "hd128-gqa": (mc.TINY.with_(name="hd128-gqa", dim=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn_dim=1184,
                                vocab=1500, n_layers=2), True),
     # the 7B-class head geometry on a small model: 28 Q heads over 4 KV heads; with 8 ranks every KV head is
