@@ -1466,12 +1466,12 @@ __device__ __forceinline__ void mk_down_fused(const MegaArgs& a, MkCtx& c, long 
                 for (int u = 0; u < 4; u++) v[u] += __shfl_xor_sync(MG_FULL_MASK, v[u], 1);
 #pragma unroll
                 for (int u = 0; u < 4; u++) v[u] += __shfl_xor_sync(MG_FULL_MASK, v[u], 2);
-                const int row = ((rg0 + j) << 3) + (lane >> 2);
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int r = row + u * 8 * MK_NW;
-                    if (ok[u] && L.t == 0 && r < a.dim) red_add_s64(acc_cur + r, mk_contrib(v[u]));
-                }
+                // every lane of a quad now holds the four sums: lane t sends the one of row-group u = t, so the
+                // four row-groups leave in one conversion and one reduction instruction
+                const float mine = L.t == 0 ? v[0] : L.t == 1 ? v[1] : L.t == 2 ? v[2] : v[3];
+                const bool okm = L.t == 0 ? ok[0] : L.t == 1 ? ok[1] : L.t == 2 ? ok[2] : ok[3];
+                const int r = ((rg0 + j + L.t * MK_NW) << 3) + (lane >> 2);
+                if (okm && r < a.dim) red_add_s64(acc_cur + r, mk_contrib(mine));
             }
             MK_ESTAMP(33 + 2 * (rg0 / per_entry));
             __syncwarp();
