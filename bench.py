@@ -109,18 +109,20 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.idx = gpu_index
         self.proc = None
-        self.t0 = self.t1 = None
+        self.windows = []          # [begin, end] pairs: the timed regions
 
     # nvidia-smi needs a few hundred ms to come up, longer than a short timed region: start it
-    # early (start), then bracket the timed region (begin / end); stop() keeps the samples whose
-    # timestamps fall inside the bracket (widened by one sampling period).
+    # early (start), then bracket every timed region (begin / end; the device-resident loop and the
+    # host-buffer loop are both bracketed); stop() keeps the samples whose timestamps fall inside a
+    # bracket.  A query takes nvidia-smi 20-100 ms, so a bracket of 80 ms can fall between two
+    # samples: the brackets are then widened step by step (and the line says by how much).
     def begin(self):
         import datetime
-        self.t0 = datetime.datetime.now()
+        self.windows.append([datetime.datetime.now(), None])
 
     def end(self):
         import datetime
-        self.t1 = datetime.datetime.now()
+        self.windows[-1][1] = datetime.datetime.now()
 
     def start(self):
         try:
@@ -140,29 +142,38 @@ class ClockSampler:
             self.proc.kill()
             out, _ = self.proc.communicate()
         import datetime
-        sm, mx, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        slack = datetime.timedelta(milliseconds=25)
+        rows = []
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
-            if self.t0 is not None and self.t1 is not None:
-                try:
-                    ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f")
-                except ValueError:
-                    continue
-                if ts < self.t0 - slack or ts > self.t1 + slack:
-                    continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f")
+                rows.append((ts, float(f[1]), float(f[2]), float(f[3]), f[5:9]))
             except ValueError:
                 continue
-            for n, v in zip(names, f[5:9]):
+        windows = [w for w in self.windows if w[1] is not None]
+        picked, used_slack = rows if not windows else [], None
+        for slack_ms in (25, 100, 300, 1000):
+            if picked or not windows:
+                break
+            slack = datetime.timedelta(milliseconds=slack_ms)
+            picked = [r for r in rows if any(w[0] - slack <= r[0] <= w[1] + slack for w in windows)]
+            used_slack = slack_ms
+        sm = [r[1] for r in picked]
+        mx = [r[2] for r in picked]
+        power = [r[3] for r in picked]
+        reasons = set()
+        for r in picked:
+            for n, v in zip(names, r[4]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+        res = {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+               "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+        if used_slack is not None and used_slack > 25:
+            res["window"] = f"timed regions widened by {used_slack} ms (nvidia-smi answered slower than they are long)"
+        return res
 
 
 # ---------------------------------------------------------------------------
@@ -335,7 +346,6 @@ def run_b200_arm(args, cfg, rank, world, local_rank):
     eng.Sync()
     sampler.end()
     barrier()
-    clocks = sampler.stop()
     ms = ev0.elapsed_time(ev1)
     launches = eng.LaunchCount() - launches0
     tok_last, pos_last = eng.GetCursor()
@@ -357,13 +367,16 @@ def run_b200_arm(args, cfg, rank, world, local_rank):
         for i in range(PROMPT_LEN):
             eng.PartialStep(hid[i], i, 0, cfg.n_layers, None, logits_host)
         barrier()
+        sampler.begin()
         t0 = time.perf_counter()
         for i in range(PROMPT_LEN, PROMPT_LEN + K):
             eng.PartialStep(hid[i], i, 0, cfg.n_layers, None, logits_host)
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
+        sampler.end()
         e2e_last_tok = int(torch.argmax(logits_host))
         barrier()
+    clocks = sampler.stop()
 
     # max over ranks
     ms_max, e2e_ms_max = multi.reduce_max([ms, e2e_s * 1e3], dist, device="cuda")
@@ -657,11 +670,13 @@ def run_matvec_workload(args):
 
     sampler = ClockSampler(0)
     sampler.start()
-    timed(warm * copies // 8, False)
+    t_up = time.perf_counter()
+    while time.perf_counter() - t_up < 0.8:              # warm-up under load while nvidia-smi comes up
+        timed(max(warm, 1) * copies, False)
     sampler.begin()
     ms_hbm = timed(steps, False)
-    sampler.end()
     ms_hot = timed(steps, True)
+    sampler.end()
     clocks = sampler.stop()
     y = out.cpu().numpy()
     # end to end: host x in, host y out, through the same call

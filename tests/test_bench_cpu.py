@@ -48,10 +48,22 @@ def test_clock_samples_are_kept_only_inside_the_timed_region():
                        smi_line(ms(-40), 1965, 405.0),
                        smi_line(ms(+400), 300, 80.0),                       # after the region
                        "garbage line"])
-    cs.t0, cs.t1 = ms(-90), ms(-30)
+    cs.windows = [[ms(-90), ms(-30)]]
     got = cs.stop()
     assert got["samples"] == 3 and got["sm_mhz"] == 1965.0 and got["sm_max_mhz"] == 1965.0
     assert got["power_w_max"] == 410.0 and got["reasons"] == ["sw_power_cap"]
+    assert "window" not in got
+
+
+def test_clock_brackets_widen_when_nvidia_smi_is_slower_than_the_timed_region():
+    now = datetime.datetime.now()
+    ms = lambda d: now + datetime.timedelta(milliseconds=d)   # noqa: E731
+    cs = bench.ClockSampler(0)
+    cs.proc = FakeSmi([smi_line(ms(-900), 345, 90.0), smi_line(ms(-160), 1965, 300.0), smi_line(ms(+60), 1935, 310.0),
+                       smi_line(ms(+2500), 300, 80.0)])
+    cs.windows = [[ms(-90), ms(-30)], [ms(-20), ms(0)]]       # two timed regions, no sample inside either
+    got = cs.stop()
+    assert got["samples"] == 2 and got["sm_mhz"] == 1950.0 and "widened by 100 ms" in got["window"]
 
 
 def test_clock_sampler_without_nvidia_smi_reports_so():
