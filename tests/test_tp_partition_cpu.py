@@ -171,3 +171,17 @@ def test_sharded_layer_equals_the_unsplit_layer_on_the_oracle(fmt, size):
     assert np.array_equal(np.concatenate(q_parts), q_full)
     for got, want in ((o_sum, o_full), (d_sum, d_full)):
         assert np.abs(got - want).max() <= 2e-6 * np.abs(want).max()
+
+
+def test_every_gpu_test_case_has_a_partition_for_its_rank_count():
+    """The multi-GPU tests name (ranks, model) pairs; a pair without a partition would only show on
+    a box with that many GPUs."""
+    from mongoose_b200 import multi
+    from tests import tp_worker
+    from tests.test_gpu_tensor_parallel import RANK_CASES
+    for world, names in RANK_CASES.items():
+        for name in names:
+            cfg, _ = tp_worker.CASES[name]
+            for rank in range(world):
+                part = multi.tp_partition(cfg, rank, world)
+                assert part["q_heads"][1] > part["q_heads"][0], (world, name, rank, part)
