@@ -1396,7 +1396,8 @@ __device__ __forceinline__ void mk_row_share(const MegaArgs& a, int& lo, int& hi
 // additions, so its own come later than the stores in real time.  The residual enters as one more
 // addition per row, made by the CTA that also clears that row (mk_row_share).
 //   Weights: wide tiles, row-group = 8 rows, nkt k-tiles = the window; warp w takes row-groups
-//   w, w + 15, ...; the sums leave the warp straight from registers (8 lanes x 8 bytes per tile row).
+//   w, w + 15, ..., four of them in flight; their sums leave the warp straight from registers in one
+//   reduction instruction (lane t of a quad sends the row of row-group t).
 // ---------------------------------------------------------------------
 template <int FMT>
 __device__ __forceinline__ void mk_down_fused(const MegaArgs& a, MkCtx& c, long long* acc_cur, int trace_base) {
